@@ -1,0 +1,186 @@
+"""ctypes bindings of the kernel libraries: torch tensors in, launches on torch's current stream.
+
+`KernelSet(dtype)` gives the launchers of one element type (float32: the true 32-bit set;
+bfloat16: the serving set). Every wrapper checks device, dtype and contiguity before it passes a
+pointer on, and raises on a non-zero return code. There is no CPU path: a tensor that is not on a
+CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import load_library
+
+PAGE = 64  # tokens per cache page (SLLM_PAGE in common.cuh)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(t: torch.Tensor | None, dtype=None, name="tensor"):
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on a CUDA device only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: arguments refused by the launcher (code {code})")
+    raise KernelError(f"{what}: CUDA error {code} ({_cuda_error_name(code)})")
+
+
+def _cuda_error_name(code: int) -> str:
+    try:
+        rt = ctypes.CDLL("libcudart.so")
+        rt.cudaGetErrorString.restype = ctypes.c_char_p
+        return rt.cudaGetErrorString(code).decode()
+    except OSError:
+        return "see cudaError_t"
+
+
+_SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+
+
+class KernelSet:
+    """Launchers for activations and weights of one element type."""
+
+    def __init__(self, dtype: torch.dtype):
+        if dtype not in _SUFFIX:
+            raise KernelError(f"no kernels for {dtype}; supported: float32, bfloat16")
+        self.dtype = dtype
+        self.suffix = _SUFFIX[dtype]
+        self.lib = load_library(self.suffix)
+
+    def _fn(self, name):
+        fn = getattr(self.lib, f"sllm_{name}_{self.suffix}")
+        fn.restype = c_int
+        return fn
+
+    # ------------------------------------------------------------------ embedding
+    def embed_rows(self, ids, table, out, err_flag):
+        T, d = out.shape
+        _check(self._fn("embed_rows")(_ptr(ids, torch.int32, "ids"), _ptr(table, self.dtype, "table"),
+                                      _ptr(out, torch.float32, "out"), c_int(T), c_int(d), c_int(table.shape[0]),
+                                      _ptr(err_flag, torch.int32, "err"), _stream()), "embed_rows")
+
+    # ------------------------------------------------------------------ norm
+    def add_rmsnorm(self, x, delta, rows, weight, y, eps, n_rows=None):
+        """x float32 [T,d] residual (+= delta when rows is None); y [n_rows,d] normed output."""
+        d = x.shape[-1]
+        n = y.shape[0] if n_rows is None else n_rows
+        if weight.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"norm weight has dtype {weight.dtype}")
+        _check(self._fn("add_rmsnorm")(_ptr(x, torch.float32, "x"), _ptr(delta, self.dtype, "delta"),
+                                       _ptr(rows, torch.int32, "rows"), _ptr(weight, None, "weight"),
+                                       c_int(1 if weight.dtype == torch.float32 else 0), _ptr(y, self.dtype, "y"),
+                                       c_int(n), c_int(d), c_float(eps), _stream()), "add_rmsnorm")
+
+    def residual_add(self, x, delta):
+        _check(self._fn("residual_add")(_ptr(x, torch.float32, "x"), _ptr(delta, self.dtype, "delta"),
+                                        c_longlong(delta.numel()), _stream()), "residual_add")
+
+    # ------------------------------------------------------------------ matrix products
+    def gemm_nt(self, a, w, out):
+        """out[M,N] = a[M,K] @ w[N,K]^T; `out` is of this set's dtype or float32."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N):
+            raise KernelError(f"gemm_nt shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        out_f32 = 1 if (out.dtype == torch.float32 and self.dtype != torch.float32) else 0
+        _check(self._fn("gemm_nt")(_ptr(a, self.dtype, "a"), _ptr(w, self.dtype, "w"),
+                                   _ptr(out, torch.float32 if out_f32 else self.dtype, "out"), c_int(M), c_int(N),
+                                   c_int(K), c_int(K), c_int(K), c_int(N), c_int(out_f32), _stream()), "gemm_nt")
+
+    # ------------------------------------------------------------------ rotary + cache write
+    def rope_kv_write(self, qkv, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv, head_dim, rot,
+                      interleaved):
+        T, ld = qkv.shape
+        _check(self._fn("rope_kv_write")(_ptr(qkv, self.dtype, "qkv"), c_int(ld), _ptr(tok_pos, torch.int32, "tok_pos"),
+                                         _ptr(tok_seq, torch.int32, "tok_seq"),
+                                         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
+                                         _ptr(cos_sin, torch.float32, "cos_sin"),
+                                         _ptr(kpages, self.dtype if kpages is not None else None, "kpages"),
+                                         _ptr(vpages, self.dtype if vpages is not None else None, "vpages"), c_int(T),
+                                         c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(rot),
+                                         c_int(1 if interleaved else 0), _stream()), "rope_kv_write")
+
+    # ------------------------------------------------------------------ attention
+    def attn_paged(self, q, out, seq_start, seq_pos0, block_table, kpages, vpages, n_seqs, max_new, n_heads, n_kv,
+                   head_dim, window, scale):
+        _check(self._fn("attn_paged")(_ptr(q, self.dtype, "q"), c_int(q.shape[1]), _ptr(out, self.dtype, "out"),
+                                      _ptr(seq_start, torch.int32, "seq_start"), _ptr(seq_pos0, torch.int32, "seq_pos0"),
+                                      _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
+                                      _ptr(kpages, self.dtype, "kpages"), _ptr(vpages, self.dtype, "vpages"),
+                                      c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+                                      c_int(window or 0), c_float(scale), _stream()), "attn_paged")
+
+    # ------------------------------------------------------------------ feed-forward
+    def swiglu(self, gate_up, out):
+        T, F = out.shape
+        if tuple(gate_up.shape) != (T, 2 * F):
+            raise KernelError(f"swiglu shapes: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+        _check(self._fn("swiglu")(_ptr(gate_up, self.dtype, "gate_up"), _ptr(out, self.dtype, "out"), c_int(T), c_int(F),
+                                  _stream()), "swiglu")
+
+
+class CastKernels:
+    """bfloat16 <-> float32 copies (a matrix stored in 32-bit inside a bfloat16 model)."""
+
+    def __init__(self):
+        self.lib = load_library("bf16")
+
+    def to_f32(self, src, dst):
+        fn = self.lib.sllm_cast_bf16_to_f32
+        fn.restype = c_int
+        _check(fn(_ptr(src, torch.bfloat16, "src"), _ptr(dst, torch.float32, "dst"), c_longlong(src.numel()), _stream()),
+               "cast_bf16_to_f32")
+
+    def to_bf16(self, src, dst):
+        fn = self.lib.sllm_cast_f32_to_bf16
+        fn.restype = c_int
+        _check(fn(_ptr(src, torch.float32, "src"), _ptr(dst, torch.bfloat16, "dst"), c_longlong(src.numel()), _stream()),
+               "cast_f32_to_bf16")
+
+
+class SamplingKernels:
+    STRATEGIES = {"greedy": 0, "temperature": 1, "top_k": 2, "top_p": 3}
+    PARAM_WORDS = 8   # int32 words per row: strategy, temperature, top_k, top_p, seed lo/hi, draw lo/hi
+
+    def __init__(self):
+        self.lib = load_library("sampling")
+
+    def sample_rows(self, logits, params, out):
+        """logits float32 [n, V] (row stride = logits.stride(0)); params int32 [n, 8]; out int32 [n]."""
+        if logits.dim() != 2 or logits.stride(1) != 1:
+            raise KernelError("logits must be [rows, vocab] with unit column stride")
+        n, V = logits.shape
+        fn = self.lib.sllm_sample_rows
+        fn.restype = c_int
+        if not logits.is_cuda or logits.dtype != torch.float32:
+            raise KernelError("logits must be float32 on a CUDA device")
+        _check(fn(c_void_p(logits.data_ptr()), c_int(logits.stride(0)), c_int(n), c_int(V),
+                  _ptr(params, torch.int32, "params"), _ptr(out, torch.int32, "out"), _stream()), "sample_rows")
+
+    def repeat_penalty(self, logits, recent, counts, penalty, last_n):
+        n, V = logits.shape
+        fn = self.lib.sllm_repeat_penalty
+        fn.restype = c_int
+        _check(fn(c_void_p(logits.data_ptr()), c_int(logits.stride(0)), c_int(n), c_int(V),
+                  _ptr(recent, torch.int32, "recent"), c_int(recent.shape[1]), _ptr(counts, torch.int32, "counts"),
+                  _ptr(penalty, torch.float32, "penalty"), c_int(last_n), _stream()), "repeat_penalty")

@@ -1,0 +1,232 @@
+"""The engine and its one step function.
+
+The reference's step is Forward(tokenIDs, startPos): one sequence, its new tokens, logits of the
+last position (model_f32.go:377-380). Here a step takes a batch of sequences with the next tokens
+of each (a whole prompt, or one token), runs exactly those tokens as one packed batch against
+the cache that earlier steps left, and returns float32 logits at the places asked for. A
+sequence's rows see only that sequence's keys, so neither its batch mates nor padding change its
+numbers.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..cache import PAGE, CacheFull, SequenceCache, pages_for
+from ..config.registry import load_config
+from ..csrc.bindings import CastKernels, KernelSet
+from ..weights.loader import load_weights
+from .layout import ModelLayout
+from .model import DecoderModel
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class StepError(ValueError):
+    """A step that cannot run; raised before anything is launched or changed."""
+
+
+class Sequence:
+    """A live request: a cache slot and the number of tokens it holds."""
+
+    def __init__(self, engine: "Engine", slot: int):
+        self.engine, self.slot, self.closed = engine, slot, False
+
+    @property
+    def length(self) -> int:
+        return self.engine.cache.length[self.slot]
+
+    def close(self) -> None:
+        if not self.closed:
+            self.engine.cache.close(self.slot)
+            self.closed = True
+
+
+@dataclass
+class StepEntry:
+    sequence: Sequence
+    tokens: list[int]
+    want: list[int] | None = None      # places among `tokens` whose logits are wanted; None: the last
+
+
+class StepContext:
+    """What the parts see of a step: the kernels, the packed batch's index arrays, the cache."""
+
+    def __init__(self, engine: "Engine"):
+        self.engine = engine
+        self.kernels = engine.kernels
+        self.dtype = engine.dtype
+        self.cache = engine.cache
+        self.err_flag = engine.err_flag
+        self.n_tokens = self.n_seqs = self.max_new = 0
+        self.token_ids = self.tok_pos = self.tok_seq = self.seq_start = self.seq_pos0 = self.slots = None
+        self.block_tables: list[torch.Tensor] = []
+
+    @property
+    def kernels_f32(self):
+        return self.engine.kernels_f32
+
+    @property
+    def casts(self):
+        return self.engine.casts
+
+    def unit_kv(self, unit: int):
+        g = self.cache.group_of_unit[unit]
+        k, v = self.cache.groups[g].unit_storage(unit)
+        return k, v, self.block_tables[g]
+
+    def unit_state(self, unit: int):
+        """State tensor [n_slots, ...] of the unit; index it with `self.slots`."""
+        return self.cache.state[unit]
+
+
+class Engine:
+    """One model on one GPU: weights, cache and the step function."""
+
+    def __init__(self, layout: ModelLayout, tensors: dict, dtype, max_tokens: int, max_seqs: int | None = None,
+                 device="cuda:0"):
+        self.dtype = DTYPES[dtype]
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise StepError(f"the engine runs on a CUDA device, not on {self.device}")
+        self.layout = layout
+        self.kernels = KernelSet(self.dtype)
+        self._kernels_f32 = self.kernels if self.dtype == torch.float32 else None
+        self._casts = None
+        self.model = DecoderModel(layout)
+        self.model.bind(tensors, self.dtype, self.device)
+        self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.cache = None
+        self.resize_cache(max_tokens, max_seqs)
+
+    def resize_cache(self, max_tokens: int, max_seqs: int | None = None) -> None:
+        """(Re)build the cache for `max_tokens` tokens held at once (each sequence's count rounded up
+        to whole pages) and `max_seqs` live sequences. Only while no sequence is open."""
+        if self.cache is not None and self.cache.slots.n_held:
+            raise StepError("the cache cannot be resized while sequences are open")
+        self.cache = None
+        n_pages = max(1, pages_for(max_tokens))
+        n_slots = max_seqs if max_seqs is not None else min(n_pages, 1024)
+        self.cache = SequenceCache(self.model.cache_needs(), self.model.state_needs(), n_slots, n_pages, self.dtype,
+                                   self.device)
+        self.max_positions = min(self.layout.max_positions, n_pages * PAGE)
+        self.model.prepare(self.max_positions, self.device)
+
+    def bytes_per_page(self) -> int:
+        """Device bytes one page of PAGE tokens costs over all cache units."""
+        width = torch.empty((), dtype=self.dtype).element_size()
+        return sum(2 * len(units) * need.kv_heads * PAGE * need.head_dim * width
+                   for need, units in ((g.need, g.units) for g in self.cache.groups))
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, model_dir, dtype="bfloat16", max_tokens: int = 4096, max_seqs: int | None = None,
+                    device="cuda:0") -> "Engine":
+        from .. import models  # noqa: F401  (registers the architectures)
+        arch, cfg = load_config(model_dir)
+        layout = arch.layout(cfg)
+        specs = DecoderModel(layout).tensor_specs()
+        tensors = load_weights(model_dir, specs, torch.device(device), DTYPES[dtype], ignore=layout.ignorable_tensors)
+        eng = cls(layout, tensors, dtype, max_tokens, max_seqs, device)
+        eng.config = cfg
+        return eng
+
+    @property
+    def kernels_f32(self):
+        if self._kernels_f32 is None:
+            self._kernels_f32 = KernelSet(torch.float32)
+        return self._kernels_f32
+
+    @property
+    def casts(self):
+        if self._casts is None:
+            self._casts = CastKernels()
+        return self._casts
+
+    # ------------------------------------------------------------------ sequences
+    def open(self) -> Sequence:
+        return Sequence(self, self.cache.open())
+
+    def new_event(self):
+        return torch.cuda.Event(enable_timing=True)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Run the given tokens of every entry; returns float32 logits [wanted places, vocab] in the
+        order of the entries and of each entry's `want`."""
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        V = self.layout.vocab_size
+        seen, growth, want_rows = set(), [], []
+        lens, pos0 = [], []
+        row = 0
+        for e in entries:
+            s = e.sequence
+            if s.closed or s.engine is not self:
+                raise StepError("a step entry names a sequence that is closed or belongs to another engine")
+            if s.slot in seen:
+                raise StepError(f"the sequence in slot {s.slot} appears twice in one step")
+            seen.add(s.slot)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError("a step entry brings no tokens")
+            if s.length + n > self.max_positions:
+                raise StepError(f"sequence would reach {s.length + n} tokens; the engine holds at most "
+                                f"{self.max_positions} per sequence")
+            want = [n - 1] if e.want is None else list(e.want)
+            for w in want:
+                if not 0 <= w < n:
+                    raise StepError(f"wanted place {w} is outside the entry's {n} tokens")
+                want_rows.append(row + w)
+            lens.append(n)
+            pos0.append(s.length)
+            growth.append((s.slot, n))
+            row += n
+        ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=row)
+        if ids.min() < 0 or ids.max() >= V:
+            bad = int(ids[(ids < 0) | (ids >= V)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary (0..{V - 1})")
+        self.cache.reserve(growth)                      # CacheFull leaves everything as it was
+
+        B, T = len(entries), row
+        ctx = self._context(entries, ids, lens, pos0, want_rows)
+        residual = self.model.embedding.forward(ctx.token_ids, ctx)
+        delta = None
+        for e in self.layout.schedule:
+            delta = self.model.blocks[e.layer].forward(residual, delta, ctx, e.cache_unit, e.writes_cache)
+        logits = None
+        if want_rows:
+            normed = self.model.final_norm.forward(residual, delta, ctx, rows=ctx.want_rows)
+            logits = self.model.head.forward(normed, ctx)
+        self.cache.advance(growth)
+        return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
+
+    def _context(self, entries, ids, lens, pos0, want_rows) -> StepContext:
+        B, T = len(lens), int(ids.shape[0])
+        lens_a = np.asarray(lens, dtype=np.int32)
+        pos0_a = np.asarray(pos0, dtype=np.int32)
+        seq_start = np.zeros(B + 1, dtype=np.int32)
+        np.cumsum(lens_a, out=seq_start[1:])
+        tok_seq = np.repeat(np.arange(B, dtype=np.int32), lens_a)
+        tok_pos = (np.arange(T, dtype=np.int32) - seq_start[tok_seq] + pos0_a[tok_seq]).astype(np.int32)
+        slots = [e.sequence.slot for e in entries]
+        tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
+        pieces = [ids.astype(np.int32), tok_pos, tok_seq, seq_start, pos0_a, np.asarray(slots, dtype=np.int32),
+                  np.asarray(want_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
+        sizes = [p.shape[0] for p in pieces]
+        host = torch.from_numpy(np.concatenate(pieces)).pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        views, off = [], 0
+        for n in sizes:
+            views.append(dev[off:off + n])
+            off += n
+        ctx = StepContext(self)
+        ctx.n_tokens, ctx.n_seqs, ctx.max_new = T, B, int(lens_a.max())
+        ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows = views[:7]
+        ctx.block_tables = [v.view(B, t.shape[1]) for v, t in zip(views[7:], tables)]
+        ctx.is_decode = bool((lens_a == 1).all())
+        ctx._host_keepalive = host
+        return ctx

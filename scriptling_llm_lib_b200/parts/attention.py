@@ -1,0 +1,65 @@
+"""Grouped-query causal attention over the paged cache.
+
+q = x Wq^T, k = x Wk^T, v = x Wv^T; Q and K rotated by the position encoding; K, V appended to
+the cache; query head h reads key/value head h // (H/G); score = (q.k) / sqrt(head_dim); keys
+after the query are masked; max-subtracted softmax; out = sum p v; y = out Wo^T
+(model_f32.go:391-470, float32_ops.go:190-235, :252-260). A `window` (absent in the reference)
+also masks keys `window` or more positions behind the query and lets the cache give old pages
+back. With `writes=False` the layer projects queries only and reads the unit another layer wrote.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.needs import CacheNeed
+from .base import MIXERS, POSITION_ENCODINGS, Mixer, PartSpec
+from .linear import Linear
+
+
+class Attention(Mixer):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec,
+                 q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
+                 scale: float | None = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
+        if head_dim % 16:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take head widths in steps of 16")
+        self.hidden, self.n_heads, self.n_kv_heads, self.head_dim, self.window = hidden, n_heads, n_kv_heads, head_dim, window
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.position = POSITION_ENCODINGS.build(position)
+        qw, kw = n_heads * head_dim, n_kv_heads * head_dim
+        self.qkv = Linear([q_name, k_name, v_name], [qw, kw, kw], hidden)
+        self.out = Linear([o_name], [hidden], qw)
+        self.q_only: Linear | None = None
+
+    def tensor_specs(self):
+        return self.qkv.tensor_specs() + self.out.tensor_specs()
+
+    def bind(self, tensors, dtype, device):
+        self.qkv.bind(tensors, dtype, device)
+        self.out.bind(tensors, dtype, device)
+        self.q_only = self.qkv.rows(0, self.n_heads * self.head_dim)
+
+    def prepare(self, max_positions, device):
+        self.position.prepare(max_positions, device)
+
+    def cache_need(self):
+        return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, x, ctx, unit, writes):
+        kpages, vpages, block_table = ctx.unit_kv(unit)
+        if writes:
+            qkv = self.qkv.forward(x, ctx)
+            self.position.apply(qkv, ctx, self.n_heads, self.n_kv_heads, kpages, vpages, block_table)
+        else:
+            qkv = self.q_only.forward(x, ctx)
+            self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
+        attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
+        ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
+                               ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
+        return self.out.forward(attn, ctx)
+
+
+MIXERS.register("attention", Attention)

@@ -1,0 +1,100 @@
+"""The parts a layer is put together from, and the registries that name them.
+
+A layer is {norm, mixer, norm, feed-forward} in some arrangement. Each part takes its sizes and
+constants as parameters, publishes the tensors it wants (`tensor_specs`), takes them (`bind`) and
+runs on the rows it is given (`forward`). No part knows which model it is in: tensor names, widths,
+eps, theta and head counts all arrive through the constructor. A model's layout names a part by
+its registered kind, layer by layer, so different layers can have different mixers and
+feed-forwards.
+
+Interfaces (duck-typed; the base classes document them):
+
+  Mixer.cache_need() -> CacheNeed | None      keys/values the layer keeps per position
+  Mixer.state_need() -> StateNeed | None      per-sequence state of fixed size
+  Mixer.forward(x, ctx, unit, writes) -> y    x, y: [T, hidden] in the engine's dtype; `unit` is the
+                                              cache unit to read, `writes` whether to append to it
+  FeedForward.forward(x, ctx) -> y
+  Norm.forward(residual, delta, ctx, rows=None) -> normed
+                                              residual float32 [T, hidden], updated in place by
+                                              += delta when rows is None; rows picks rows to norm
+  PositionEncoding.prepare(max_positions, device); .apply(...)   see rotary.py
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+from ..cache.needs import CacheNeed, StateNeed
+from ..weights.spec import TensorSpec
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part chosen by name with its parameters: pure data, part of a model's layout."""
+    kind: str
+    params: dict[str, Any] = field(default_factory=dict)
+
+
+class Part:
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def bind(self, tensors: dict, dtype, device) -> None:
+        """Take this part's tensors (by the names it published) for an engine of `dtype`."""
+
+    def prepare(self, max_positions: int, device) -> None:
+        """Build host-made tables once the engine knows its longest sequence."""
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, x, ctx, unit: int, writes: bool):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, residual, delta, ctx, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._items: dict[str, type] = {}
+
+    def register(self, kind: str, cls: type, replace: bool = False) -> type:
+        if kind in self._items and not replace:
+            raise ValueError(f"{self.what} {kind!r} is already registered")
+        self._items[kind] = cls
+        return cls
+
+    def build(self, part: PartSpec, **extra):
+        try:
+            cls = self._items[part.kind]
+        except KeyError:
+            raise ValueError(f"unknown {self.what} {part.kind!r}; registered: {', '.join(sorted(self._items))}") from None
+        return cls(**part.params, **extra)
+
+    def kinds(self) -> list[str]:
+        return sorted(self._items)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+ARRANGEMENTS = Registry("block arrangement")

@@ -1,0 +1,52 @@
+"""y = x W^T for one or several weight tensors stacked along the output dimension.
+
+The reference runs Q, K, V (and gate, up) as separate products over the same input
+(model_f32.go:391-396, :479-482); stacking their rows into one matrix gives the same numbers from
+one pass over the input. Weights are [out, in] row-major as in the file (float32_ops.go:462-482).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..weights.spec import TensorSpec
+
+
+class Linear:
+    def __init__(self, names: list[str], out_features: list[int], in_features: int):
+        self.names, self.out_features, self.in_features = list(names), list(out_features), in_features
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(n, (o, self.in_features)) for n, o in zip(self.names, self.out_features)]
+
+    def bind(self, tensors: dict, dtype, device) -> None:
+        parts = [tensors[n] for n in self.names]
+        if len({p.dtype for p in parts}) != 1:
+            raise ValueError(f"tensors {self.names} are stored in different precisions and cannot be stacked")
+        self.weight = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0).contiguous()
+
+    def rows(self, first: int, count: int) -> "Linear":
+        """A view of `count` output rows from `first` (the query rows of a stacked q|k|v)."""
+        sub = Linear([f"{self.names[0]}[{first}:{first + count}]"], [count], self.in_features)
+        sub.weight = self.weight[first:first + count]
+        return sub
+
+    def forward(self, x: torch.Tensor, ctx, out_dtype=None) -> torch.Tensor:
+        w = self.weight
+        out_dtype = out_dtype or x.dtype
+        if w.dtype == x.dtype:
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+            ctx.kernels.gemm_nt(x, w, out)
+            return out
+        if w.dtype == torch.float32 and x.dtype == torch.bfloat16:
+            # a matrix kept in 32-bit inside a bfloat16 model: widen the rows, multiply in 32-bit
+            x32 = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            ctx.casts.to_f32(x, x32)
+            out32 = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+            ctx.kernels_f32.gemm_nt(x32, w, out32)
+            if out_dtype == torch.float32:
+                return out32
+            out = torch.empty(out32.shape, dtype=torch.bfloat16, device=x.device)
+            ctx.casts.to_bf16(out32, out)
+            return out
+        raise ValueError(f"weight {self.names} is {w.dtype} but the engine runs in {x.dtype}")

@@ -1,0 +1,88 @@
+"""Choosing the next token of every sequence of a batch from its logits, on the device.
+
+Strategies and option names are the reference's (model.go:701-851; `llm.generate` keywords,
+model.go:868-946): "greedy", "temperature", "top_k", "top_p", with `temperature`, `top_k`, `top_p`,
+`repeat_penalty`, `repeat_last_n`. Greedy ignores temperature and penalty (model_f32.go:610-615);
+a temperature of 0 means greedy. The reference draws from one clock-seeded generator
+(sampling.go:14-18); here each sequence has its own seed and a draw counter (its fixed-size
+sampling state), so a sequence's tokens do not depend on its batch mates.
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..csrc.bindings import SamplingKernels
+
+STRATEGIES = ("greedy", "temperature", "top_k", "top_p")
+
+
+@dataclass(frozen=True)
+class SamplingOptions:
+    strategy: str = "greedy"
+    temperature: float = 1.0
+    top_k: int = 50
+    top_p: float = 0.9
+    repeat_penalty: float = 0.0      # 0 or 1 disables; applied on the sampling strategies only
+    repeat_last_n: int = 64
+
+    def __post_init__(self):
+        if self.strategy not in STRATEGIES:
+            raise ValueError(f"unknown sampling strategy {self.strategy!r}; supported: {', '.join(STRATEGIES)}")
+        if self.temperature < 0:
+            raise ValueError("temperature must not be negative")
+        if not 0.0 < self.top_p <= 1.0:
+            raise ValueError("top_p must be in (0, 1]")
+
+    @property
+    def is_greedy(self) -> bool:
+        return self.strategy == "greedy" or self.temperature == 0.0
+
+    @property
+    def penalises(self) -> bool:
+        return (not self.is_greedy) and self.repeat_penalty > 0.0 and self.repeat_penalty != 1.0
+
+
+def pack_params(options: SamplingOptions, seeds: list[int], draws: list[int]) -> np.ndarray:
+    """Rows of 8 int32 words for the sampling kernel: strategy, temperature, top_k, top_p, seed
+    (low, high), draw index (low, high)."""
+    n = len(seeds)
+    out = np.zeros((n, SamplingKernels.PARAM_WORDS), dtype=np.int32)
+    strat = 0 if options.is_greedy else SamplingKernels.STRATEGIES[options.strategy]
+    f2i = lambda f: struct.unpack("<i", struct.pack("<f", f))[0]
+    u2i = lambda u: struct.unpack("<i", struct.pack("<I", u & 0xFFFFFFFF))[0]
+    out[:, 0], out[:, 1], out[:, 2], out[:, 3] = strat, f2i(options.temperature), options.top_k, f2i(options.top_p)
+    for i, (s, d) in enumerate(zip(seeds, draws)):
+        out[i, 4], out[i, 5], out[i, 6], out[i, 7] = u2i(s), u2i(s >> 32), u2i(d), u2i(d >> 32)
+    return out
+
+
+class Sampler:
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.kernels = SamplingKernels()
+
+    def sample(self, logits: torch.Tensor, options: SamplingOptions, seeds: list[int], draws: list[int],
+               recent: list[list[int]] | None = None) -> torch.Tensor:
+        """logits float32 [n, V] on the device -> int32 token ids [n] on the device.
+        `recent`: each sequence's prompt and generated tokens so far (for the repeat penalty)."""
+        n = logits.shape[0]
+        if options.penalises and recent is not None:
+            last_n = max(1, options.repeat_last_n)
+            win = np.full((n, last_n), -1, dtype=np.int32)
+            counts = np.zeros(n, dtype=np.int32)
+            for i, r in enumerate(recent):
+                tail = r[-last_n:]
+                win[i, :len(tail)] = tail
+                counts[i] = len(tail)
+            logits = logits.clone()
+            self.kernels.repeat_penalty(
+                logits, torch.from_numpy(win).to(self.device), torch.from_numpy(counts).to(self.device),
+                torch.full((n,), float(options.repeat_penalty), dtype=torch.float32, device=self.device), last_n)
+        params = torch.from_numpy(pack_params(options, seeds, draws)).to(self.device)
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        self.kernels.sample_rows(logits, params, out)
+        return out
