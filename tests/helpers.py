@@ -83,3 +83,73 @@ def rel_err(got, want) -> float:
 # stores them (8 mantissa bits: 2^-9 relative per rounding, a few dozen roundings deep)
 TOL_F32 = 1e-4
 TOL_BF16 = 3e-2
+
+
+# --------------------------------------------------------------------------- trace replay client
+class Replay:
+    """Drives bin/trace_run as a user would: one JSON line per step, waits for `done <step>`."""
+
+    def __init__(self, model_dir, dtype: str, out_dir, max_tokens: int, vocab: int):
+        import subprocess
+        root = Path(__file__).resolve().parent.parent
+        self.out_dir, self.vocab, self.step_no = Path(out_dir), vocab, 0
+        self.proc = subprocess.Popen(
+            [sys.executable, str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out",
+             str(out_dir), "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+
+    def step(self, entries: list[tuple[str, list[int], list[int]]], end=()) -> np.ndarray | None:
+        """entries: (request id, tokens, want). Returns the logits rows written for this step."""
+        rec = {"step": self.step_no, "entries": [{"id": i, "tokens": t, "want": w} for i, t, w in entries], "end": list(end)}
+        self.proc.stdin.write(json.dumps(rec) + "\n")
+        self.proc.stdin.flush()
+        line = self.proc.stdout.readline().strip()
+        if line != f"done {self.step_no}":
+            raise AssertionError(f"trace_run answered {line!r} to step {self.step_no} (exit code {self.proc.poll()})")
+        n_want = sum(len(w) for _, _, w in entries)
+        path = self.out_dir / f"{self.step_no}.f32"
+        self.step_no += 1
+        if n_want == 0:
+            assert not path.exists()
+            return None
+        return np.fromfile(path, dtype="<f4").reshape(n_want, self.vocab)
+
+    def close(self) -> int:
+        self.proc.stdin.close()
+        return self.proc.wait(timeout=120)
+
+
+def replay_whole(rp: Replay, rid: str, ids: list[int]) -> np.ndarray:
+    return rp.step([(rid, ids, list(range(len(ids))))], end=[rid])
+
+
+def replay_tail_stepwise(rp: Replay, rid: str, ids: list[int], tail: int = 32) -> np.ndarray:
+    head = len(ids) - tail
+    rows = []
+    if head > 0:
+        rows.append(rp.step([(rid, ids[:head], list(range(head)))]))
+    for j in range(max(head, 0), len(ids)):
+        rows.append(rp.step([(rid, [ids[j]], [0])], end=[rid] if j == len(ids) - 1 else []))
+    return np.concatenate(rows)
+
+
+def replay_batch(rp: Replay, reqs: dict[str, list[int]], prompt_lens: dict[str, int]) -> dict[str, np.ndarray]:
+    """The requests start together with prompts of `prompt_lens`, then go on by one token each;
+    shorter requests end earlier. Returns every request's logits at all its places."""
+    got = {r: [] for r in reqs}
+    order = list(reqs)
+    ends = [r for r in order if prompt_lens[r] == len(reqs[r])]
+    out = rp.step([(r, reqs[r][:prompt_lens[r]], list(range(prompt_lens[r]))) for r in order], end=ends)
+    off = 0
+    for r in order:
+        got[r].append(out[off:off + prompt_lens[r]])
+        off += prompt_lens[r]
+    pos = dict(prompt_lens)
+    live = [r for r in order if r not in ends]
+    while live:
+        ends = [r for r in live if pos[r] + 1 == len(reqs[r])]
+        out = rp.step([(r, [reqs[r][pos[r]]], [0]) for r in live], end=ends)
+        for i, r in enumerate(live):
+            got[r].append(out[i:i + 1])
+            pos[r] += 1
+        live = [r for r in live if r not in ends]
+    return {r: np.concatenate(v) for r, v in got.items()}

@@ -1,0 +1,128 @@
+"""Safetensors reading/writing, the loader's one error, random-weights mode (no GPU)."""
+import json
+import struct
+
+import pytest
+import torch
+
+from helpers import TINY_A, TINY_B, make_model_dir
+import plain_llama as plain
+from scriptling_llm_lib_b200 import models  # noqa: F401
+from scriptling_llm_lib_b200.config import LlamaConfig
+from scriptling_llm_lib_b200.engine.model import DecoderModel
+from scriptling_llm_lib_b200.models.llama import llama_layout
+from scriptling_llm_lib_b200.weights import (SafetensorsError, SafetensorsFile, WeightError, load_weights,
+                                              write_safetensors)
+
+
+def specs_of(raw):
+    return DecoderModel(llama_layout(LlamaConfig.from_dict(raw))).tensor_specs()
+
+
+def test_safetensors_round_trip(tmp_path):
+    t = {"a": torch.randn(3, 5).to(torch.bfloat16), "b": torch.arange(7, dtype=torch.int32),
+         "c": torch.randn(2, 2, 2), "empty": torch.zeros(0, 4)}
+    write_safetensors(tmp_path / "x.safetensors", t, {"note": "hi"})
+    with SafetensorsFile(tmp_path / "x.safetensors") as f:
+        assert set(f.names()) == set(t)
+        assert f.metadata["note"] == "hi"
+        for k, v in t.items():
+            got = f.tensor(k).clone()
+            assert got.dtype == v.dtype and got.shape == v.shape and torch.equal(got, v)
+    # the plain implementation's own parse reads the same numbers
+    other = plain.read_safetensors(tmp_path / "x.safetensors")
+    assert torch.equal(other["a"], t["a"].double()) and torch.equal(other["c"], t["c"].double())
+
+
+def test_malformed_files(tmp_path):
+    p = tmp_path / "bad.safetensors"
+    p.write_bytes(b"\x01\x02")
+    with pytest.raises(SafetensorsError, match="too short"):
+        SafetensorsFile(p)
+    p.write_bytes(struct.pack("<Q", 1 << 40) + b"{}")
+    with pytest.raises(SafetensorsError, match="exceeds"):
+        SafetensorsFile(p)
+    p.write_bytes(struct.pack("<Q", 4) + b"nope")
+    with pytest.raises(SafetensorsError, match="JSON"):
+        SafetensorsFile(p)
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 8)
+    with pytest.raises(SafetensorsError, match="claims bytes"):
+        SafetensorsFile(p)
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},
+                      "v": {"dtype": "F32", "shape": [2], "data_offsets": [4, 12]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 12)
+    with pytest.raises(SafetensorsError, match="overlap"):
+        SafetensorsFile(p)
+    hdr = json.dumps({"w": {"dtype": "Q4", "shape": [2], "data_offsets": [0, 1]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0")
+    with pytest.raises(SafetensorsError, match="unsupported dtype"):
+        SafetensorsFile(p)
+
+
+def test_random_mode_writes_a_loadable_folder_and_is_seeded(tmp_path):
+    d0 = make_model_dir(tmp_path / "a0", TINY_A, 0)
+    d0b = make_model_dir(tmp_path / "a0b", TINY_A, 0)
+    d1 = make_model_dir(tmp_path / "a1", TINY_A, 1)
+    assert (d0 / "config.json").is_file() and (d0 / "model.safetensors").is_file()
+    assert LlamaConfig.from_dict(json.loads((d0 / "config.json").read_text())) == LlamaConfig.from_dict(TINY_A)
+    w0 = load_weights(d0, specs_of(TINY_A), "cpu", torch.bfloat16)
+    w0b = load_weights(d0b, specs_of(TINY_A), "cpu", torch.bfloat16)
+    w1 = load_weights(d1, specs_of(TINY_A), "cpu", torch.bfloat16)
+    assert set(w0) == {s.name for s in specs_of(TINY_A)} and "lm_head.weight" not in w0    # tied
+    for k in w0:
+        assert w0[k].dtype == torch.bfloat16 and torch.equal(w0[k], w0b[k])
+    assert not torch.equal(w0["model.layers.0.mlp.up_proj.weight"], w1["model.layers.0.mlp.up_proj.weight"])
+    q = w0["model.layers.1.self_attn.q_proj.weight"].float()
+    assert q.shape == (64, 64) and abs(float(q.std()) - 0.02) < 0.003 and abs(float(q.mean())) < 0.002
+    n = w0["model.layers.0.input_layernorm.weight"].float()
+    assert abs(float(n.mean()) - 1.0) < 0.02                                               # 1 + N(0, 0.02)
+
+
+def test_precision_kept_as_stored(tmp_path):
+    d = make_model_dir(tmp_path / "f", TINY_B, 1, dtype=torch.float32)
+    w = load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    assert all(t.dtype == torch.float32 for t in w.values())           # stored in 32-bit: stays so
+    d = make_model_dir(tmp_path / "b", TINY_B, 1, dtype=torch.bfloat16)
+    w16 = load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    w32 = load_weights(d, specs_of(TINY_B), "cpu", torch.float32)
+    for k in w16:
+        assert w16[k].dtype == torch.bfloat16 and w32[k].dtype == torch.float32
+        assert torch.equal(w16[k].float(), w32[k])                     # widening is exact
+
+
+def test_one_error_lists_missing_unexpected_and_misshapen(tmp_path):
+    d = make_model_dir(tmp_path / "m", TINY_B, 1)
+    with SafetensorsFile(d / "model.safetensors") as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    del tensors["model.layers.2.mlp.down_proj.weight"]
+    del tensors["lm_head.weight"]
+    tensors["model.layers.0.self_attn.k_proj.weight"] = torch.zeros(32, 95, dtype=torch.bfloat16)
+    tensors["model.layers.9.extra.weight"] = torch.zeros(3, dtype=torch.bfloat16)
+    tensors["model.norm.weight"] = torch.zeros(96, dtype=torch.int32)
+    write_safetensors(d / "model.safetensors", tensors)
+    with pytest.raises(WeightError) as e:
+        load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    err = e.value
+    assert set(err.missing) == {"model.layers.2.mlp.down_proj.weight", "lm_head.weight"}
+    assert err.unexpected == ["model.layers.9.extra.weight"]
+    assert err.misshapen == [("model.layers.0.self_attn.k_proj.weight", (32, 95), (32, 96))]
+    assert err.bad_dtype == [("model.norm.weight", "int32")]
+    msg = str(err)
+    for word in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes (1)", "is [32, 95], expected [32, 96]",
+                 "model.layers.9.extra.weight", "lm_head.weight"):
+        assert word in msg
+
+
+def test_tied_model_tolerates_a_head_in_the_file_and_missing_file_is_an_error(tmp_path):
+    d = make_model_dir(tmp_path / "t", TINY_A, 0)
+    with SafetensorsFile(d / "model.safetensors") as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    write_safetensors(d / "model.safetensors", tensors)
+    layout = llama_layout(LlamaConfig.from_dict(TINY_A))
+    w = load_weights(d, specs_of(TINY_A), "cpu", torch.bfloat16, ignore=layout.ignorable_tensors)
+    assert "lm_head.weight" not in w
+    (d / "model.safetensors").unlink()
+    with pytest.raises(WeightError, match="missing tensors"):
+        load_weights(d, specs_of(TINY_A), "cpu", torch.bfloat16)
