@@ -81,14 +81,15 @@ class SequenceCache:
         self.groups: list[KVGroup] = []
         self.group_of_unit: dict[int, int] = {}
         for need, units in by_need.items():
-            shape = (len(units), n_pages, need.kv_heads, PAGE, need.head_dim)
+            # one page more than the pool hands out: padded rows of a replayed decode step write there
+            shape = (len(units), n_pages + 1, need.kv_heads, PAGE, need.head_dim)
             g = KVGroup(need, units, FreeList(n_pages, f"cache page ({need.kind})"),
                         torch.empty(shape, dtype=dtype, device=device), torch.empty(shape, dtype=dtype, device=device))
             for u in units:
                 self.group_of_unit[u] = len(self.groups)
             self.groups.append(g)
         self.state: dict[int, torch.Tensor] = {
-            unit: torch.zeros((n_slots, *need.shape), dtype=need.dtype, device=device)
+            unit: torch.zeros((n_slots + 1, *need.shape), dtype=need.dtype, device=device)   # last: spare, for padding
             for unit, need in state_needs.items() if need is not None}
 
     # ------------------------------------------------------------------ slots

@@ -84,14 +84,22 @@ class KernelSet:
                                       _ptr(err_flag, torch.int32, "err"), _stream()), "embed_rows")
 
     # ------------------------------------------------------------------ norm
-    def add_rmsnorm(self, x, delta, rows, weight, y, eps, n_rows=None):
-        """x float32 [T,d] residual (+= delta when rows is None); y [n_rows,d] normed output."""
+    def add_rmsnorm(self, x, delta, rows, weight, y, eps):
+        """x float32 [T,d] residual (+= delta when rows is None); y [n,d] normed output. delta: None,
+        [T,d] of this set's dtype, or float32 [P,T,d] partial sums that add up to the addend."""
         d = x.shape[-1]
-        n = y.shape[0] if n_rows is None else n_rows
+        n = y.shape[0]
         if weight.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError(f"norm weight has dtype {weight.dtype}")
-        _check(self._fn("add_rmsnorm")(_ptr(x, torch.float32, "x"), _ptr(delta, self.dtype, "delta"),
-                                       _ptr(rows, torch.int32, "rows"), _ptr(weight, None, "weight"),
+        n_parts, stride = 0, 0
+        if delta is not None and delta.dim() == 3:
+            if delta.dtype != torch.float32 or tuple(delta.shape[1:]) != tuple(x.shape):
+                raise KernelError(f"partial sums must be float32 [P, {x.shape[0]}, {d}], found {delta.dtype} {tuple(delta.shape)}")
+            n_parts, stride = delta.shape[0], x.shape[0] * d
+        elif delta is not None and (delta.dtype != self.dtype or tuple(delta.shape) != tuple(x.shape)):
+            raise KernelError(f"addend must be {self.dtype} {tuple(x.shape)}, found {delta.dtype} {tuple(delta.shape)}")
+        _check(self._fn("add_rmsnorm")(_ptr(x, torch.float32, "x"), _ptr(delta, None, "delta"), c_int(n_parts),
+                                       c_longlong(stride), _ptr(rows, torch.int32, "rows"), _ptr(weight, None, "weight"),
                                        c_int(1 if weight.dtype == torch.float32 else 0), _ptr(y, self.dtype, "y"),
                                        c_int(n), c_int(d), c_float(eps), _stream()), "add_rmsnorm")
 
@@ -135,12 +143,75 @@ class KernelSet:
                                       c_int(window or 0), c_float(scale), _stream()), "attn_paged")
 
     # ------------------------------------------------------------------ feed-forward
-    def swiglu(self, gate_up, out):
+    def swiglu(self, gate_up, out, tiled=False):
         T, F = out.shape
         if tuple(gate_up.shape) != (T, 2 * F):
             raise KernelError(f"swiglu shapes: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
         _check(self._fn("swiglu")(_ptr(gate_up, self.dtype, "gate_up"), _ptr(out, self.dtype, "out"), c_int(T), c_int(F),
-                                  _stream()), "swiglu")
+                                  c_int(1 if tiled else 0), _stream()), "swiglu")
+
+    # ------------------------------------------------------------------ fast bfloat16 kernels
+    @property
+    def decode(self) -> "DecodeKernels":
+        if self.dtype != torch.bfloat16:
+            raise KernelError("the decode kernels are bfloat16 only")
+        if getattr(self, "_decode", None) is None:
+            self._decode = DecodeKernels()
+        return self._decode
+
+
+class DecodeKernels:
+    """Weight-streaming small-M product and split-key attention for the bfloat16 decode step."""
+    HEAD_DIMS = (16, 32, 64, 128, 256)
+    MAX_M = 64
+
+    def __init__(self):
+        self.lib = load_library("decode_bf16")
+        for n in ("sllm_gemm_small_m_bf16", "sllm_attn_decode_bf16"):
+            getattr(self.lib, n).restype = c_int
+        self.lib.sllm_attn_decode_scratch_bytes.restype = c_longlong
+
+    @staticmethod
+    def takes(a, w) -> bool:
+        K = a.shape[1]
+        return (a.shape[0] <= DecodeKernels.MAX_M and K % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+    def gemm_small_m(self, a, w, out, swiglu=False):
+        """out[M,N] = a @ w^T (bfloat16 or float32 out); swiglu: out[M,N/2] = silu(gate)*up for w rows
+        tiled 8 gate / 8 up; out float32 [P,M,N]: K split P ways, out receives the partial sums."""
+        M, K = a.shape
+        N = w.shape[0]
+        ksplit = out.shape[0] if out.dim() == 3 else 1
+        want = (M, N // 2) if swiglu else ((ksplit, M, N) if out.dim() == 3 else (M, N))
+        if out.dim() == 3 and out.dtype != torch.float32:
+            raise KernelError("partial sums are written in float32")
+        if tuple(out.shape) != want or w.shape[1] != K:
+            raise KernelError(f"gemm_small_m shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"gemm_small_m output dtype {out.dtype}")
+        _check(self.lib.sllm_gemm_small_m_bf16(
+            _ptr(a, torch.bfloat16, "a") if a.is_contiguous() else c_void_p(a.data_ptr()),
+            _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+            c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
+            c_int(1 if swiglu else 0), c_int(ksplit), _stream()), "gemm_small_m")
+
+    def split_for(self, n_out: int, k: int, sm_count: int) -> int:
+        """Over how many blocks to split K so that a product with few output rows still fills the GPU."""
+        tiles = -(-n_out // 16)
+        return max(1, min(8, (4 * sm_count) // tiles, k // 512))
+
+    def attn_decode(self, q, out, seq_pos0, block_table, kpages, vpages, scratch, n_seqs, n_heads, n_kv, head_dim,
+                    window, scale, n_split):
+        need = self.lib.sllm_attn_decode_scratch_bytes(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_split))
+        if scratch.numel() * scratch.element_size() < need:
+            raise KernelError(f"attn_decode scratch holds {scratch.numel() * scratch.element_size()} bytes, needs {need}")
+        _check(self.lib.sllm_attn_decode_bf16(
+            _ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), _ptr(out, torch.bfloat16, "out"),
+            _ptr(seq_pos0, torch.int32, "seq_pos0"), _ptr(block_table, torch.int32, "block_table"),
+            c_int(block_table.shape[1]), _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"),
+            _ptr(scratch, torch.float32, "scratch"), c_int(n_seqs), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+            c_int(window or 0), c_float(scale), c_int(n_split), _stream()), "attn_decode")
 
 
 class CastKernels:

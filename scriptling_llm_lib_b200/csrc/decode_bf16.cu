@@ -1,0 +1,358 @@
+// bfloat16 kernels for the decode step (one token per sequence): everything here is bound by the
+// bytes it must read once -- the weights, and the cached keys and values of the live sequences.
+//
+//   gemm_small_m: y[M,N] = x[M,K] W[N,K]^T for a few rows M. Each weight element is loaded from
+//     HBM exactly once (16-byte loads straight into tensor-core fragments, no shared memory); the
+//     weights are the 16-row operand of mma.sync.m16n8k16 and the tokens its 8 columns, float
+//     accumulation. The warps of a block split K and add their partial sums in a fixed order.
+//     Replaces the reference's row matmul for one token (float32_ops.go:779-794) and its dense
+//     matmul for a few (float32_ops.go:462-482). An epilogue can apply the SiLU gate
+//     (model_f32.go:484-490) when gate and up rows are interleaved 8 and 8.
+//   attn_decode: grouped-query attention of one query per sequence over the paged cache, keys
+//     split over blocks (each block streams a contiguous run of pages once and serves all query
+//     heads of its key/value head), online softmax in float, partial results merged by a second
+//     small kernel. Same mathematics as fusedAttentionHeadF32 with one query row
+//     (float32_ops.go:190-235).
+#include "common.cuh"
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached16(const void* p) { return __ldg((const uint4*)p); }
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ------------------------------------------------------------------ small-M GEMM
+// Thread (g = lane/4, t = lane%4) loads 8 consecutive k of weight rows g and g+8 and of token g.
+// The 8 values fill the k-slots (2t, 2t+1, 2t+8, 2t+9) of two MMAs; weights and tokens use the
+// same assignment, and a sum over k does not care which slot a k sits in.
+#define SM_EPI_STORE 0
+#define SM_EPI_SWIGLU 1
+
+template <int NT, int WARPS, int EPI, int UN>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ y, int M, int N, int K,
+                    int ldx, int ldw, int ldy, int out_f32) {
+  __shared__ float red[WARPS][NT][4][32];
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  int n0 = blockIdx.x * 16;
+  const bf16* w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
+  const bf16* w1 = W + (size_t)min(n0 + g + 8, N - 1) * ldw;
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++)
+#pragma unroll
+    for (int r = 0; r < 4; r++) acc[i][r] = 0.f;
+
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  int nchunks = (K + 63) >> 6;
+  // gridDim.y blocks share a tile's K range (their partial sums are kept apart in y); within a
+  // block the warps take chunks of 64 k in turn, UN chunks in flight per warp
+  int stride = gridDim.y * WARPS;
+  for (int c = blockIdx.y * WARPS + warp; c < nchunks; c += stride * UN) {
+    uint4 a[UN][4];
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+      int k0 = ((c + u * stride) << 6) + 8 * t, k1 = k0 + 32;
+      bool ok0 = k0 < K, ok1 = k1 < K;
+      a[u][0] = ok0 ? ld_stream16(w0 + k0) : zero;
+      a[u][1] = ok0 ? ld_stream16(w1 + k0) : zero;
+      a[u][2] = ok1 ? ld_stream16(w0 + k1) : zero;
+      a[u][3] = ok1 ? ld_stream16(w1 + k1) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+      int k0 = ((c + u * stride) << 6) + 8 * t, k1 = k0 + 32;
+      bool ok0 = k0 < K, ok1 = k1 < K;
+      uint4 b0[NT], b1[NT];
+#pragma unroll
+      for (int i = 0; i < NT; i++) {
+        int tok = i * 8 + g;
+        const bf16* xr = x + (size_t)tok * ldx;
+        b0[i] = (tok < M && ok0) ? ld_cached16(xr + k0) : zero;
+        b1[i] = (tok < M && ok1) ? ld_cached16(xr + k1) : zero;
+      }
+#pragma unroll
+      for (int i = 0; i < NT; i++) {
+        mma_16816(acc[i], a[u][0].x, a[u][1].x, a[u][0].y, a[u][1].y, b0[i].x, b0[i].y);
+        mma_16816(acc[i], a[u][0].z, a[u][1].z, a[u][0].w, a[u][1].w, b0[i].z, b0[i].w);
+        mma_16816(acc[i], a[u][2].x, a[u][3].x, a[u][2].y, a[u][3].y, b1[i].x, b1[i].y);
+        mma_16816(acc[i], a[u][2].z, a[u][3].z, a[u][2].w, a[u][3].w, b1[i].z, b1[i].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NT; i++)
+#pragma unroll
+    for (int r = 0; r < 4; r++) red[warp][i][r][lane] = acc[i][r];
+  __syncthreads();
+  // acc slot r of lane (g,t): feature n0 + g + 8*(r>>1), token 8*i + 2t + (r&1)
+  for (int v = threadIdx.x; v < NT * 4 * 32; v += WARPS * 32) {
+    int i = v / 128, r = (v >> 5) & 3, ln = v & 31;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) s += red[w][i][r][ln];
+    if (EPI == SM_EPI_STORE) {
+      int feat = n0 + (ln >> 2) + 8 * (r >> 1), tok = 8 * i + 2 * (ln & 3) + (r & 1);
+      if (feat < N && tok < M) {
+        if (out_f32) ((float*)y)[((size_t)blockIdx.y * M + tok) * ldy + feat] = s;
+        else ((bf16*)y)[(size_t)tok * ldy + feat] = __float2bfloat16_rn(s);
+      }
+    } else {
+      red[0][i][r][ln] = s;       // slot (i, r, ln) is read by this thread only in the loop above
+    }
+  }
+  if (EPI == SM_EPI_SWIGLU) {
+    // rows g (< 8) of the tile are gate rows, rows g + 8 the matching up rows
+    __syncthreads();
+    for (int v = threadIdx.x; v < NT * 2 * 32; v += WARPS * 32) {
+      int i = v / 64, r = (v >> 5) & 1, ln = v & 31;
+      float gate = red[0][i][r][ln], up = red[0][i][r + 2][ln];
+      int feat = (n0 >> 1) + (ln >> 2), tok = 8 * i + 2 * (ln & 3) + r;
+      if (feat < (N >> 1) && tok < M) {
+        float sg = 1.0f / (1.0f + __expf(-gate));
+        ((bf16*)y)[(size_t)tok * ldy + feat] = __float2bfloat16_rn(gate * sg * up);
+      }
+    }
+  }
+}
+
+template <int NT, int EPI>
+static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
+                          int out_f32, int ksplit, cudaStream_t stream) {
+  constexpr int UN = NT <= 2 ? 4 : 2;
+  dim3 grid((N + 15) / 16, ksplit);
+  int chunks_per_block = ((K + 63) / 64 + ksplit - 1) / ksplit;
+  if (grid.x * grid.y >= 1184 || chunks_per_block <= 16)
+    gemm_small_m_kernel<NT, 4, EPI, UN><<<grid, 128, 0, stream>>>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
+  else
+    gemm_small_m_kernel<NT, 8, EPI, UN><<<grid, 256, 0, stream>>>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
+  SLLM_RETURN_LAST();
+}
+
+// epilogue 0: y[M,N] in bfloat16 (or float when out_f32); epilogue 1: y[M,N/2] = silu(gate)*up with
+// the rows of W interleaved 8 gate rows, 8 up rows. ksplit > 1 (float output only): K is split over
+// ksplit blocks and y receives their partial sums as y[ksplit][M][ldy]; the reader adds them.
+SLLM_EXPORT int sllm_gemm_small_m_bf16(const void* x, const void* W, void* y, int M, int N, int K, int ldx, int ldw,
+                                       int ldy, int out_f32, int epilogue, int ksplit, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return SLLM_ERR_ARG;
+  if (epilogue == SM_EPI_SWIGLU && ((N & 15) || out_f32 || ksplit != 1)) return SLLM_ERR_ARG;
+  if (ksplit < 1 || ksplit > 64 || (ksplit > 1 && !out_f32)) return SLLM_ERR_ARG;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+#define SM_CASE(NT)                                                                                                     \
+  return epilogue == SM_EPI_SWIGLU ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, stream) \
+                                   : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, stream)
+  if (M <= 8) { SM_CASE(1); }
+  if (M <= 16) { SM_CASE(2); }
+  if (M <= 32) { SM_CASE(4); }
+  SM_CASE(8);
+#undef SM_CASE
+}
+
+// ------------------------------------------------------------------ decode attention, split over keys
+#define AD_WARPS 4
+#define AD_UN 4   // keys each lane group has in flight
+#define AD_LOG2E 1.4426950408889634f
+
+struct AttnDecodeArgs {
+  const bf16* q;        // [B, q_ld] rotated queries of this step, head h at columns h*HD
+  int q_ld;
+  const int* seq_pos0;  // [B] position of the query = number of keys cached before this step
+  const int* block_table;
+  int max_pages;
+  const bf16* kpages;   // [pages][G][PAGE][HD]
+  const bf16* vpages;
+  float* part;          // [B][H][n_split][HD + 2]: unnormalised sum, running max (log2 units), running sum
+  int H, G, window, n_split;
+  float scale;
+};
+
+template <int HD, int NREP>
+__global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDecodeArgs p) {
+  constexpr int LPK = HD / 8;        // lanes that share one key (8 dims = 16 bytes each)
+  constexpr int KPW = 32 / LPK;      // keys a warp reads per load
+  __shared__ float sm_acc[AD_WARPS][NREP][HD];
+  __shared__ float sm_ml[AD_WARPS][NREP][2];
+  int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int slot = lane / LPK, dl = (lane % LPK) * 8;
+  int pos = p.seq_pos0[b];
+  int k_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  int pb = k_begin / SLLM_PAGE, pe = pos / SLLM_PAGE;
+  int pps = (pe - pb + 1 + p.n_split - 1) / p.n_split;
+  int p0 = pb + split * pps, p1 = min(pe + 1, p0 + pps);
+  int k_lo = max(k_begin, p0 * SLLM_PAGE), k_hi = min(pos + 1, p1 * SLLM_PAGE);
+  const int* bt = p.block_table + (size_t)b * p.max_pages;
+  int nrep = p.H / p.G;
+
+  for (int r0 = 0; r0 < nrep; r0 += NREP) {
+    float q[NREP][8], acc[NREP][8], m[NREP], l[NREP];
+#pragma unroll
+    for (int r = 0; r < NREP; r++) {
+      int h = g * nrep + r0 + r;
+      uint4 raw = ld_cached16(p.q + (size_t)b * p.q_ld + (size_t)h * HD + dl);
+      const bf16* e = (const bf16*)&raw;
+#pragma unroll
+      for (int j = 0; j < 8; j++) { q[r][j] = __bfloat162float(e[j]) * (p.scale * AD_LOG2E); acc[r][j] = 0.f; }
+      m[r] = -INFINITY;
+      l[r] = 0.f;
+    }
+    for (int kb = k_lo + warp * KPW * AD_UN; kb < k_hi; kb += AD_WARPS * KPW * AD_UN) {
+      uint4 kr[AD_UN], vr[AD_UN];
+      bool ok[AD_UN];
+#pragma unroll
+      for (int u = 0; u < AD_UN; u++) {
+        int key = kb + u * KPW + slot;
+        ok[u] = key < k_hi;
+        int kk = ok[u] ? key : k_lo;
+        int page = bt[kk / SLLM_PAGE];
+        size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * HD + dl;
+        kr[u] = ld_stream16(p.kpages + off);
+        vr[u] = ld_stream16(p.vpages + off);
+      }
+      float s[AD_UN][NREP];
+#pragma unroll
+      for (int u = 0; u < AD_UN; u++) {
+        const bf16* ke = (const bf16*)&kr[u];
+        float kf[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) kf[j] = __bfloat162float(ke[j]);
+#pragma unroll
+        for (int r = 0; r < NREP; r++) {
+          float d = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; j++) d = fmaf(q[r][j], kf[j], d);
+#pragma unroll
+          for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          s[u][r] = ok[u] ? d : -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < NREP; r++) {
+        float m_new = m[r];
+#pragma unroll
+        for (int u = 0; u < AD_UN; u++) m_new = fmaxf(m_new, s[u][r]);
+        if (m_new == -INFINITY) continue;
+        float corr = exp2f(m[r] - m_new);
+        m[r] = m_new;
+        float lsum = l[r] * corr;
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[r][j] *= corr;
+#pragma unroll
+        for (int u = 0; u < AD_UN; u++) {
+          float pr = exp2f(s[u][r] - m_new);
+          lsum += pr;
+          const bf16* ve = (const bf16*)&vr[u];
+#pragma unroll
+          for (int j = 0; j < 8; j++) acc[r][j] = fmaf(pr, __bfloat162float(ve[j]), acc[r][j]);
+        }
+        l[r] = lsum;
+      }
+    }
+    // merge the key slots of the warp, then the warps
+#pragma unroll
+    for (int r = 0; r < NREP; r++) {
+#pragma unroll
+      for (int o = LPK; o < 32; o <<= 1) {
+        float mo = __shfl_xor_sync(0xffffffffu, m[r], o), lo = __shfl_xor_sync(0xffffffffu, l[r], o);
+        float mn = fmaxf(m[r], mo);
+        float c1 = mn == -INFINITY ? 0.f : exp2f(m[r] - mn), c2 = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+        l[r] = l[r] * c1 + lo * c2;
+        m[r] = mn;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float ao = __shfl_xor_sync(0xffffffffu, acc[r][j], o);
+          acc[r][j] = acc[r][j] * c1 + ao * c2;
+        }
+      }
+      if (lane < LPK) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) sm_acc[warp][r][dl + j] = acc[r][j];
+        if (lane == 0) { sm_ml[warp][r][0] = m[r]; sm_ml[warp][r][1] = l[r]; }
+      }
+    }
+    __syncthreads();
+    for (int v = threadIdx.x; v < NREP * HD; v += AD_WARPS * 32) {
+      int r = v / HD, dd = v % HD;
+      float mn = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < AD_WARPS; w++) mn = fmaxf(mn, sm_ml[w][r][0]);
+      float a = 0.f, ls = 0.f;
+#pragma unroll
+      for (int w = 0; w < AD_WARPS; w++) {
+        float c = mn == -INFINITY ? 0.f : exp2f(sm_ml[w][r][0] - mn);
+        a += sm_acc[w][r][dd] * c;
+        ls += sm_ml[w][r][1] * c;
+      }
+      int h = g * nrep + r0 + r;
+      float* dst = p.part + (((size_t)b * p.H + h) * p.n_split + split) * (HD + 2);
+      dst[dd] = a;
+      if (dd == 0) { dst[HD] = mn; dst[HD + 1] = ls; }
+    }
+    __syncthreads();
+  }
+}
+
+// out[b, h*HD + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, int H, int HD,
+                                         int n_split) {
+  int h = blockIdx.x, b = blockIdx.y;
+  const float* src = part + ((size_t)b * H + h) * n_split * (HD + 2);
+  float mn = -INFINITY;
+  for (int s = 0; s < n_split; s++) mn = fmaxf(mn, src[(size_t)s * (HD + 2) + HD]);
+  for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
+    float a = 0.f, ls = 0.f;
+    for (int s = 0; s < n_split; s++) {
+      const float* ps = src + (size_t)s * (HD + 2);
+      float c = (mn == -INFINITY || ps[HD] == -INFINITY) ? 0.f : exp2f(ps[HD] - mn);
+      a += ps[dd] * c;
+      ls += ps[HD + 1] * c;
+    }
+    out[((size_t)b * H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+  }
+}
+
+template <int HD>
+static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStream_t stream) {
+  dim3 grid(a.n_split, a.G, B);
+  int nrep = a.H / a.G;
+  if (nrep % 4 == 0) attn_decode_split_kernel<HD, 4><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+  else if (nrep % 2 == 0) attn_decode_split_kernel<HD, 2><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+  else attn_decode_split_kernel<HD, 1><<<grid, AD_WARPS * 32, 0, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  attn_decode_merge_kernel<<<dim3(a.H, B), HD < 32 ? 32 : HD, 0, stream>>>(a.part, out, a.H, HD, a.n_split);
+  SLLM_RETURN_LAST();
+}
+
+// Bytes of scratch `part` must have: B * H * n_split * (hd + 2) floats.
+SLLM_EXPORT long long sllm_attn_decode_scratch_bytes(int B, int H, int hd, int n_split) {
+  return (long long)B * H * n_split * (hd + 2) * (long long)sizeof(float);
+}
+
+SLLM_EXPORT int sllm_attn_decode_bf16(const void* q, int q_ld, void* out, const int* seq_pos0, const int* block_table,
+                                      int max_pages, const void* kpages, const void* vpages, void* scratch, int B, int H,
+                                      int G, int hd, int window, float scale, int n_split, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (G < 1 || H % G != 0 || n_split < 1 || (q_ld & 7) || ((uintptr_t)q & 15)) return SLLM_ERR_ARG;
+  AttnDecodeArgs a{(const bf16*)q, q_ld, seq_pos0, block_table, max_pages, (const bf16*)kpages, (const bf16*)vpages,
+                   (float*)scratch, H, G, window, n_split, scale};
+  switch (hd) {
+    case 16: return attn_decode_launch<16>(a, (bf16*)out, B, stream);
+    case 32: return attn_decode_launch<32>(a, (bf16*)out, B, stream);
+    case 64: return attn_decode_launch<64>(a, (bf16*)out, B, stream);
+    case 128: return attn_decode_launch<128>(a, (bf16*)out, B, stream);
+    case 256: return attn_decode_launch<256>(a, (bf16*)out, B, stream);
+    default: return SLLM_ERR_ARG;   // other head widths go through the generic kernel
+  }
+}

@@ -28,29 +28,38 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const W* __restri
 
 // ------------------------------------------------------------------ residual add + RMSNorm
 // v = x[row] + delta[row]; y = (v * 1/sqrt(mean(v^2) + eps)) * w.
+// delta is either one array of the element type (n_parts == 0) or n_parts float arrays
+// `part_stride` elements apart whose sum is the addend (the partial sums of a product whose K
+// range was split over blocks); they are added in a fixed order.
 // rows == nullptr: row r of y comes from row r of x, and x is updated in place (the residual sum).
 // rows != nullptr: row r of y comes from row rows[r]; x is left alone.
 template <typename A>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const A* __restrict__ delta,
-                                   const int* __restrict__ rows, const void* __restrict__ w, int w_f32,
-                                   A* __restrict__ y, int d, float eps) {
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta, int n_parts,
+                                   size_t part_stride, const int* __restrict__ rows, const void* __restrict__ w,
+                                   int w_f32, A* __restrict__ y, int d, float eps) {
   extern __shared__ float sm_row[];
   __shared__ float red[32];
   int r = blockIdx.x;
   size_t in = rows ? (size_t)rows[r] : (size_t)r;
   float* xr = x + in * d;
-  const A* dr = delta ? delta + in * d : nullptr;
+  const A* dr = (delta && n_parts == 0) ? (const A*)delta + in * d : nullptr;
+  const float* pr = (delta && n_parts > 0) ? (const float*)delta + in * d : nullptr;
   float ss = 0.f;
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = xr[j];
     if (dr) v += to_f32(dr[j]);
+    if (pr) {
+      float a = 0.f;
+      for (int p = 0; p < n_parts; p++) a += pr[(size_t)p * part_stride + j];
+      v += a;
+    }
     sm_row[j] = v;
     ss += v * v;
   }
   ss = block_sum(ss, red);
   float inv = 1.0f / sqrtf(ss / (float)d + eps);
   A* yr = y + (size_t)r * d;
-  bool update = (rows == nullptr) && (dr != nullptr);
+  bool update = (rows == nullptr) && (delta != nullptr);
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = sm_row[j];
     if (update) xr[j] = v;
@@ -318,15 +327,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_paged_kernel(AttnArgs p) {
 }
 
 // ------------------------------------------------------------------ SiLU-gated product
-// gu [T, 2F]: gate in columns [0,F), up in [F,2F). h = g * (1/(1+exp(-g))) * u, left to right.
+// gu [T, 2F]. tiled == 0: gate in columns [0,F), up in [F,2F). tiled != 0: columns come in tiles
+// of 16, 8 gate columns then the 8 matching up columns (the row order the stacked weight is kept
+// in, so that a tensor-core tile holds both halves of a pair).
+// h = g * (1/(1+exp(-g))) * u, left to right.
 template <typename A>
-__global__ void swiglu_kernel(const A* __restrict__ gu, A* __restrict__ h, int F, size_t n) {
+__global__ void swiglu_kernel(const A* __restrict__ gu, A* __restrict__ h, int F, size_t n, int tiled) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   size_t t = i / F;
   int j = (int)(i % F);
-  float g = to_f32(gu[t * 2 * F + j]);
-  float u = to_f32(gu[t * 2 * F + F + j]);
+  int gc = tiled ? (j >> 3) * 16 + (j & 7) : j;
+  int uc = tiled ? gc + 8 : F + j;
+  float g = to_f32(gu[t * 2 * F + gc]);
+  float u = to_f32(gu[t * 2 * F + uc]);
   float s = 1.0f / (1.0f + expf(-g));
   h[i] = from_f32<A>(g * s * u);
 }

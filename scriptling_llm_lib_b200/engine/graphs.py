@@ -1,0 +1,125 @@
+"""CUDA graphs of the decode step.
+
+A decode step launches a few hundred small kernels whose sizes depend only on the batch size, so
+it is captured once per (padded batch size, block-table width) and replayed: the step's index
+arrays live in one static device buffer that is refreshed from pinned host memory before each
+replay. Rows added to fill the batch up to its padded size read and write a spare cache page and a
+spare state slot of their own, so they change nothing a real row sees.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.needs import PAGE
+
+
+def _next_pow2(n: int) -> int:
+    p = 1
+    while p < n:
+        p <<= 1
+    return p
+
+
+class DecodeGraph:
+    def __init__(self, engine, batch: int, width: int):
+        from .step import StepContext
+        self.engine, self.batch, self.width = engine, batch, width
+        n_groups = len(engine.cache.groups)
+        B = batch
+        # layout of the index buffer (int32): ids, pos, seq, seq_start, pos0, slots, want_rows, block tables
+        self.sizes = [B, B, B, B + 1, B, B, B] + [B * width] * n_groups
+        total = sum(self.sizes)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
+        self.copied = torch.cuda.Event()
+        views, off = [], 0
+        for n in self.sizes:
+            views.append(self.dev[off:off + n])
+            off += n
+        ctx = StepContext(engine)
+        ctx.n_tokens = ctx.n_seqs = B
+        ctx.max_new = 1
+        ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows = views[:7]
+        ctx.block_tables = [v.view(B, width) for v in views[7:]]
+        ctx.is_decode = True
+        ctx.max_pages = width
+        self.ctx = ctx
+        self._fill_host([], [], [], [])
+        self.dev.copy_(self.host)
+        # warm-up outside capture (lazy attribute calls, allocator growth), then capture
+        side = torch.cuda.Stream(device=engine.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            engine._forward(ctx, want=True)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        from ..csrc import bindings
+        before = bindings.LAUNCHES[0]
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = engine._forward(ctx, want=True)
+        self.kernels_per_replay = bindings.LAUNCHES[0] - before
+
+    def _fill_host(self, ids, pos0, slots, tables):
+        B, W, eng = self.batch, self.width, self.engine
+        n = len(ids)
+        h = self.host.numpy()
+        off = 0
+        h[off:off + B] = 0
+        h[off:off + n] = ids
+        off += B
+        h[off:off + B] = 0
+        h[off:off + n] = pos0
+        off += B
+        h[off:off + B] = np.arange(B)
+        off += B
+        h[off:off + B + 1] = np.arange(B + 1)
+        off += B + 1
+        h[off:off + B] = 0
+        h[off:off + n] = pos0
+        off += B
+        h[off:off + B] = eng.cache.n_slots            # the spare state slot
+        h[off:off + n] = slots
+        off += B
+        h[off:off + B] = np.arange(B)
+        off += B
+        for g in range(len(eng.cache.groups)):
+            tab = h[off:off + B * W].reshape(B, W)
+            tab[:] = eng.cache.n_pages               # the spare page
+            if n:
+                t = tables[g]
+                tab[:n, :t.shape[1]] = np.where(t >= 0, t, eng.cache.n_pages)
+            off += B * W
+
+    def run(self, ids, pos0, slots, tables) -> torch.Tensor:
+        self.copied.synchronize()
+        self._fill_host(ids, pos0, slots, tables)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self.graph.replay()
+        from ..csrc import bindings
+        bindings.LAUNCHES[0] += self.kernels_per_replay
+        return self.logits[:len(ids)]
+
+
+class DecodeGraphs:
+    """The graphs of one engine, captured on first use."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.graphs: dict[tuple[int, int], DecodeGraph] = {}
+
+    def clear(self):
+        self.graphs.clear()
+
+    def run(self, ids, pos0, slots, tables) -> torch.Tensor:
+        need = max(1, max(t.shape[1] for t in tables)) if tables else 1
+        cap = -(-self.engine.max_positions // PAGE)
+        width = min(max(8, _next_pow2(need)), max(cap, need))
+        batch = _next_pow2(len(ids))
+        key = (batch, width)
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = DecodeGraph(self.engine, batch, width)
+        return g.run(ids, pos0, slots, tables)

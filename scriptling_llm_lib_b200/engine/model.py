@@ -47,6 +47,11 @@ class DecoderModel:
             for p in b.parts():
                 p.prepare(max_positions, device)
 
+    def graph_safe(self) -> bool:
+        """True when every part says its decode step launches the same work whatever the values
+        (no host reads, no shapes that depend on data), so the step can be captured and replayed."""
+        return all(getattr(p, "graph_safe", False) for b in self.blocks for p in (b.mixer, b.feed_forward))
+
     def cache_needs(self) -> dict[int, CacheNeed | None]:
         """Need of every cache unit, taken from the mixer of the entry that writes it."""
         return {e.cache_unit: self.blocks[e.layer].mixer.cache_need() for e in self.layout.schedule if e.writes_cache}

@@ -18,6 +18,7 @@ from ..cache import PAGE, CacheFull, SequenceCache, pages_for
 from ..config.registry import load_config
 from ..csrc.bindings import CastKernels, KernelSet
 from ..weights.loader import load_weights
+from .graphs import DecodeGraphs
 from .layout import ModelLayout
 from .model import DecoderModel
 
@@ -73,6 +74,12 @@ class StepContext:
     def casts(self):
         return self.engine.casts
 
+    def decode_splits(self, n_kv_heads: int) -> int:
+        """Over how many blocks a decode step splits each sequence's keys: enough blocks to fill the
+        GPU a few times over, never more than the longest sequence has pages."""
+        want = -(-6 * self.engine.sm_count // max(1, self.n_seqs * n_kv_heads))
+        return max(1, min(self.max_pages, want))
+
     def unit_kv(self, unit: int):
         g = self.cache.group_of_unit[unit]
         k, v = self.cache.groups[g].unit_storage(unit)
@@ -87,7 +94,7 @@ class Engine:
     """One model on one GPU: weights, cache and the step function."""
 
     def __init__(self, layout: ModelLayout, tensors: dict, dtype, max_tokens: int, max_seqs: int | None = None,
-                 device="cuda:0"):
+                 device="cuda:0", use_graphs: bool = True):
         self.dtype = DTYPES[dtype]
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -98,7 +105,11 @@ class Engine:
         self._casts = None
         self.model = DecoderModel(layout)
         self.model.bind(tensors, self.dtype, self.device)
+        # decode steps are replayed as CUDA graphs when every mixer and feed-forward allows it
+        self.use_graphs = use_graphs and self.model.graph_safe()
+        self.decode_graphs = DecodeGraphs(self)
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.cache = None
         self.resize_cache(max_tokens, max_seqs)
 
@@ -108,6 +119,7 @@ class Engine:
         if self.cache is not None and self.cache.slots.n_held:
             raise StepError("the cache cannot be resized while sequences are open")
         self.cache = None
+        self.decode_graphs.clear()
         n_pages = max(1, pages_for(max_tokens))
         n_slots = max_seqs if max_seqs is not None else min(n_pages, 1024)
         self.cache = SequenceCache(self.model.cache_needs(), self.model.state_needs(), n_slots, n_pages, self.dtype,
@@ -192,17 +204,29 @@ class Engine:
         self.cache.reserve(growth)                      # CacheFull leaves everything as it was
 
         B, T = len(entries), row
-        ctx = self._context(entries, ids, lens, pos0, want_rows)
+        if self.use_graphs and T == B:
+            slots = [e.sequence.slot for e in entries]
+            tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
+            logits = self.decode_graphs.run(ids, pos0, slots, tables)
+            if want_rows != list(range(B)):
+                logits = logits[torch.as_tensor(want_rows, dtype=torch.long, device=self.device)] if want_rows else None
+        else:
+            ctx = self._context(entries, ids, lens, pos0, want_rows)
+            logits = self._forward(ctx, want=bool(want_rows))
+        self.cache.advance(growth)
+        return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
+
+    def _forward(self, ctx: StepContext, want: bool):
+        """The model on the rows of `ctx`: embedding, the scheduled blocks, and for the wanted rows the
+        final norm and the output head."""
         residual = self.model.embedding.forward(ctx.token_ids, ctx)
         delta = None
         for e in self.layout.schedule:
             delta = self.model.blocks[e.layer].forward(residual, delta, ctx, e.cache_unit, e.writes_cache)
-        logits = None
-        if want_rows:
-            normed = self.model.final_norm.forward(residual, delta, ctx, rows=ctx.want_rows)
-            logits = self.model.head.forward(normed, ctx)
-        self.cache.advance(growth)
-        return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
+        if not want:
+            return None
+        normed = self.model.final_norm.forward(residual, delta, ctx, rows=ctx.want_rows)
+        return self.model.head.forward(normed, ctx)
 
     def _context(self, entries, ids, lens, pos0, want_rows) -> StepContext:
         B, T = len(lens), int(ids.shape[0])
@@ -228,5 +252,6 @@ class Engine:
         ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows = views[:7]
         ctx.block_tables = [v.view(B, t.shape[1]) for v, t in zip(views[7:], tables)]
         ctx.is_decode = bool((lens_a == 1).all())
+        ctx.max_pages = int(-(-(int((pos0_a + lens_a).max())) // PAGE))
         ctx._host_keepalive = host
         return ctx

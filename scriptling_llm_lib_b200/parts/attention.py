@@ -19,6 +19,8 @@ from .linear import Linear
 
 
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
                  scale: float | None = None):
@@ -57,9 +59,16 @@ class Attention(Mixer):
             qkv = self.q_only.forward(x, ctx)
             self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
         attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
-                               ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
-        return self.out.forward(attn, ctx)
+        if ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in ctx.kernels.decode.HEAD_DIMS:
+            n_split = ctx.decode_splits(self.n_kv_heads)
+            scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
+                                  device=x.device)
+            ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
+                                           self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
+        else:
+            ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
+                                   ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
+        return self.out.forward(attn, ctx, partials_ok=True)
 
 
 MIXERS.register("attention", Attention)

@@ -12,11 +12,14 @@ Interfaces (duck-typed; the base classes document them):
   Mixer.cache_need() -> CacheNeed | None      keys/values the layer keeps per position
   Mixer.state_need() -> StateNeed | None      per-sequence state of fixed size
   Mixer.forward(x, ctx, unit, writes) -> y    x, y: [T, hidden] in the engine's dtype; `unit` is the
-                                              cache unit to read, `writes` whether to append to it
-  FeedForward.forward(x, ctx) -> y
+                                              cache unit to read, `writes` whether to append to it.
+                                              y may also be float32 [P, T, hidden]: partial sums
+                                              that add up to the output (the next norm adds them)
+  FeedForward.forward(x, ctx) -> y            the same two forms of y
   Norm.forward(residual, delta, ctx, rows=None) -> normed
                                               residual float32 [T, hidden], updated in place by
-                                              += delta when rows is None; rows picks rows to norm
+                                              += delta when rows is None; rows picks rows to norm;
+                                              delta: None or either form of y
   PositionEncoding.prepare(max_positions, device); .apply(...)   see rotary.py
 """
 from __future__ import annotations

@@ -1,5 +1,8 @@
 """Dense SiLU-gated feed-forward: y = (silu(x Wg^T) * (x Wu^T)) Wd^T, no biases
-(model_f32.go:476-493). Gate and up rows are stacked so one product serves both."""
+(model_f32.go:476-493). Gate and up rows are stacked so one product serves both; when the
+intermediate width is a multiple of 8 the stacked rows are kept in tiles of 16 (8 gate rows, the 8
+matching up rows), so that one tensor-core tile holds both halves of a pair and the gate can be
+applied before anything is written."""
 from __future__ import annotations
 
 import torch
@@ -9,6 +12,8 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden: int, intermediate: int, gate_name: str, up_name: str, down_name: str):
         self.hidden, self.intermediate = hidden, intermediate
         self.gate_up = Linear([gate_name, up_name], [intermediate, intermediate], hidden)
@@ -20,12 +25,21 @@ class SwiGLU(FeedForward):
     def bind(self, tensors, dtype, device):
         self.gate_up.bind(tensors, dtype, device)
         self.down.bind(tensors, dtype, device)
+        F = self.intermediate
+        self.tiled = F % 8 == 0
+        if self.tiled:
+            w = self.gate_up.weight
+            self.gate_up.weight = w.view(2, F // 8, 8, self.hidden).permute(1, 0, 2, 3).reshape(2 * F, self.hidden).contiguous()
 
     def forward(self, x, ctx):
-        gu = self.gate_up.forward(x, ctx)
         h = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        ctx.kernels.swiglu(gu, h)
-        return self.down.forward(h, ctx)
+        w = self.gate_up.weight
+        if self.tiled and x.dtype == torch.bfloat16 and w.dtype == x.dtype and ctx.kernels.decode.takes(x, w):
+            ctx.kernels.decode.gemm_small_m(x, w, h, swiglu=True)
+        else:
+            gu = self.gate_up.forward(x, ctx)
+            ctx.kernels.swiglu(gu, h, tiled=self.tiled)
+        return self.down.forward(h, ctx, partials_ok=True)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

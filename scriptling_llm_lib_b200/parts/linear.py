@@ -31,10 +31,19 @@ class Linear:
         sub.weight = self.weight[first:first + count]
         return sub
 
-    def forward(self, x: torch.Tensor, ctx, out_dtype=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, out_dtype=None, partials_ok: bool = False) -> torch.Tensor:
+        """y [T, out] in `out_dtype` (default: x's). With `partials_ok` the result may instead be
+        float32 [P, T, out] partial sums that add up to y (the reader, a norm, adds them): a product
+        with few rows and few columns is split over K to fill the GPU."""
         w = self.weight
         out_dtype = out_dtype or x.dtype
         if w.dtype == x.dtype:
+            if x.dtype == torch.bfloat16 and ctx.kernels.decode.takes(x, w):
+                split = ctx.kernels.decode.split_for(w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
+                shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
+                out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
+                ctx.kernels.decode.gemm_small_m(x, w, out)
+                return out
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
             ctx.kernels.gemm_nt(x, w, out)
             return out

@@ -47,11 +47,11 @@ def test_groups_have_storage_of_their_own():
     assert len(c.groups) == 2
     full, win = c.groups[c.group_of_unit[0]], c.groups[c.group_of_unit[2]]
     assert c.group_of_unit[0] == c.group_of_unit[1] != c.group_of_unit[2]
-    assert full.k.shape == (2, 8, 2, PAGE, 16) and win.k.shape == (1, 8, 1, PAGE, 32)
+    assert full.k.shape == (2, 8 + 1, 2, PAGE, 16) and win.k.shape == (1, 8 + 1, 1, PAGE, 32)   # + the spare page
     k0, _ = full.unit_storage(0)
     k1, _ = full.unit_storage(1)
-    assert k0.data_ptr() != k1.data_ptr() and k0.shape == (8, 2, PAGE, 16)
-    assert c.state[1].shape == (4, 3) and 0 not in c.state
+    assert k0.data_ptr() != k1.data_ptr() and k0.shape == (9, 2, PAGE, 16)
+    assert c.state[1].shape == (4 + 1, 3) and 0 not in c.state
 
 
 def test_pages_follow_each_sequences_own_length():
