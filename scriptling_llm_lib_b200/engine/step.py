@@ -136,13 +136,13 @@ class Engine:
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, model_dir, dtype="bfloat16", max_tokens: int = 4096, max_seqs: int | None = None,
-                    device="cuda:0") -> "Engine":
+                    device="cuda:0", use_graphs: bool = True) -> "Engine":
         from .. import models  # noqa: F401  (registers the architectures)
         arch, cfg = load_config(model_dir)
         layout = arch.layout(cfg)
         specs = DecoderModel(layout).tensor_specs()
         tensors = load_weights(model_dir, specs, torch.device(device), DTYPES[dtype], ignore=layout.ignorable_tensors)
-        eng = cls(layout, tensors, dtype, max_tokens, max_seqs, device)
+        eng = cls(layout, tensors, dtype, max_tokens, max_seqs, device, use_graphs)
         eng.config = cfg
         return eng
 

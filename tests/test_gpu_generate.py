@@ -1,0 +1,185 @@
+"""Generation on the GPU through the Python entry point and the command line: greedy and sampled
+tokens against the plain implementation, unequal batches with stop tokens, batch after batch on
+reused slots, long decoding, the first tokens of a sequence, stale cache contents."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_llama as plain
+from helpers import TINY, TOL_BF16, TOL_F32, make_model_dir, plain_model, random_ids, rel_err
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(autouse=True)
+def fresh_model_cache():
+    from scriptling_llm_lib_b200 import llm
+    llm.unload()
+    yield
+    llm.unload()
+
+
+def near_maximum(model, prompt, out, tol):
+    """Every generated token is a maximum of the plain logits on the generated path, within rounding."""
+    for i, t in enumerate(out):
+        lg = model.logits(list(prompt) + list(out[:i]))[-1]
+        if float(lg.max() - lg[t]) > tol * float(lg.abs().max()):
+            return False
+    return True
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_through_the_entry_point(tmp_path, name):
+    from scriptling_llm_lib_b200 import llm
+    raw, seed = TINY[name]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm = plain_model(d)
+    V = raw["vocab_size"]
+    prompts = [random_ids(n, V, 10 + n) for n in (5, 17, 31, 1)]
+    want = [plain.generate(pm, p, 12, stop_ids=()) for p in prompts]
+    got = llm.generate(d, prompts, 12, "greedy", temperature=0.0, stop_ids=[], dtype="float32")
+    assert got == want
+    one = llm.generate(d, prompts[1], 12, "greedy", temperature=0.0, stop_ids=[], dtype="float32")
+    assert one == want[1]                                                # alone == in the batch; a flat list in, a flat list out
+    got16 = llm.generate(d, prompts, 12, "greedy", temperature=0.0, stop_ids=[], dtype="bfloat16")
+    assert all(len(g) == 12 and near_maximum(pm, p, g, TOL_BF16) for p, g in zip(prompts, got16))
+
+
+def test_stop_tokens_unequal_ends_and_batches_on_reused_slots(tmp_path):
+    from scriptling_llm_lib_b200 import llm
+    raw, seed = TINY["A"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm = plain_model(d)
+    prompts = [random_ids(n, 256, 30 + n) for n in (5, 17, 31, 9, 2, 40, 3)]
+    # greedy on random weights soon repeats one token, so sample (seeded; request i draws from stream seed + i)
+    kw = dict(strategy="temperature", temperature=1.0, repeat_penalty=0.0)
+    free_run = [plain.generate(pm, p, 16, stop_ids=(), seed=3 + i, **kw) for i, p in enumerate(prompts)]
+
+    def lengths(stop):   # a stop token cuts a run short and changes nothing before it
+        return [next((i + 1 for i, t in enumerate(r) if t in stop), len(r)) for r in free_run]
+    tokens = sorted({t for r in free_run for t in r})
+    stops = max(([a, b] for a in tokens for b in tokens if a < b), key=lambda st: len(set(lengths(st))))
+    want = [plain.generate(pm, p, 16, stop_ids=stops, seed=3 + i, **kw) for i, p in enumerate(prompts)]
+    assert [len(w) for w in want] == lengths(stops) and len({len(w) for w in want}) > 2
+    got, st = llm.generate(d, prompts, 16, kw["strategy"], temperature=1.0, repeat_penalty=0.0, seed=3, stop_ids=stops,
+                           dtype="float32", max_batch=3, stats=True)
+    assert got == want                                                   # three batches on three slots
+    assert st["generated_tokens"] == [len(w) for w in want] and st["prompt_tokens"] == [len(p) for p in prompts]
+    assert st["finish_reason"] == ["stop" if w[-1] in stops else "length" for w in want]
+    eng, _ = llm.load(d, "float32")
+    assert eng.cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in eng.cache.groups)
+    # greedy: config.json's eos id (7) is the default stop set; max_tokens counts the first token
+    dflt = llm.generate(d, prompts[:2], 16, dtype="float32")
+    assert dflt == [plain.generate(pm, p, 16, stop_ids=(7,)) for p in prompts[:2]]
+    assert llm.generate(d, prompts[0], 1, dtype="float32") == plain.generate(pm, prompts[0], 1)
+
+
+def test_sampling_strategies_match_the_plain_samplers_in_32_bit(tmp_path):
+    from scriptling_llm_lib_b200 import llm
+    raw, seed = TINY["B"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm = plain_model(d)
+    prompts = [random_ids(n, 384, 50 + n) for n in (1, 8, 40, 63)]
+    for kw in [dict(strategy="temperature", temperature=0.8), dict(strategy="top_k", temperature=1.0, top_k=20),
+               dict(strategy="top_p", temperature=0.9, top_p=0.8),
+               dict(strategy="temperature", temperature=0.8, repeat_penalty=1.3, repeat_last_n=16)]:
+        strategy = kw.pop("strategy")
+        kw.setdefault("repeat_penalty", 0.0)
+        got = llm.generate(d, prompts, 10, strategy, seed=11, stop_ids=[], dtype="float32", **kw)
+        for i, p in enumerate(prompts):
+            want = plain.generate(pm, p, 10, strategy, stop_ids=(), seed=11 + i, **kw)
+            assert got[i] == want, f"{strategy} {kw} request {i}"
+        alone = llm.generate(d, [prompts[2]], 10, strategy, seed=11, stop_ids=[], dtype="float32", **kw)
+        again = llm.generate(d, prompts[:1] + [prompts[2]], 10, strategy, seed=11, stop_ids=[], dtype="float32", **kw)
+        assert alone[0] != got[2] or True                                # (stream of request index 0 vs 2: may differ)
+        assert again[0] == got[0]                                        # same request index, same seed: same tokens
+    a = llm.generate(d, prompts[3], 10, "temperature", temperature=0.8, seed=1, stop_ids=[], dtype="float32")
+    b = llm.generate(d, prompts[3], 10, "temperature", temperature=0.8, seed=2, stop_ids=[], dtype="float32")
+    assert a != b
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_the_first_tokens(tmp_path, dtype):
+    """A prompt of one token (positions 0, 1, 2, ... all decoded), then a long run past several page
+    boundaries; every step's logits against the plain implementation."""
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    raw = dict(TINY["B"][0], max_position_embeddings=512)
+    d = make_model_dir(tmp_path / "m", raw, 1)
+    ids = random_ids(300, 384, 77)
+    want = plain_model(d).logits(ids)
+    eng = Engine.from_folder(d, dtype, max_tokens=1024)
+    s, other = eng.open(), eng.open()
+    eng.step([StepEntry(other, random_ids(130, 384, 78))])               # a neighbour in the cache
+    rows = [eng.step([StepEntry(s, [t], [0])]).cpu().to(torch.float64) for t in ids]
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    got = torch.cat(rows)
+    assert rel_err(got[:8], want[:8]) < tol                             # the first tokens of a sequence
+    assert rel_err(got, want) < tol
+
+
+def test_stale_cache_contents_change_nothing(tmp_path):
+    """Pages and slots that are used again hold the last owner's keys; fill all cache memory with
+    NaN between two runs: the tokens are the same."""
+    from scriptling_llm_lib_b200 import llm
+    raw, seed = TINY["C"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    prompts = [random_ids(n, 1003, 90 + n) for n in (70, 3, 129)]
+    for dtype in ("float32", "bfloat16"):
+        first = llm.generate(d, prompts, 20, stop_ids=[], dtype=dtype)
+        eng, _ = llm.load(d, dtype)
+        for g in eng.cache.groups:
+            g.k.fill_(float("nan"))
+            g.v.fill_(float("nan"))
+        assert llm.generate(d, prompts, 20, stop_ids=[], dtype=dtype) == first
+        assert llm.generate(d, prompts[::-1], 20, stop_ids=[], dtype=dtype) == first[::-1]
+
+
+def test_errors_before_anything_runs(tmp_path):
+    from scriptling_llm_lib_b200.cache import CacheFull
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry, StepError
+    raw, seed = TINY["A"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    eng = Engine.from_folder(d, "float32", max_tokens=128, max_seqs=2)
+    s = eng.open()
+    with pytest.raises(StepError, match="vocabulary"):
+        eng.step([StepEntry(s, [1, 256])])
+    with pytest.raises(StepError, match="no tokens"):
+        eng.step([StepEntry(s, [])])
+    with pytest.raises(StepError, match="twice"):
+        eng.step([StepEntry(s, [1]), StepEntry(s, [2])])
+    with pytest.raises(StepError, match="outside the entry"):
+        eng.step([StepEntry(s, [1, 2], [2])])
+    with pytest.raises(StepError, match="at most"):
+        eng.step([StepEntry(s, [1] * 129)])
+    assert s.length == 0
+    s2 = eng.open()
+    with pytest.raises(CacheFull):
+        eng.open()
+    eng.step([StepEntry(s, [1] * 100)])
+    with pytest.raises(CacheFull):
+        eng.step([StepEntry(s2, [1] * 30)])                              # 2 pages hold 128 tokens: 1 page is left
+    assert s2.length == 0 and s.length == 100
+    s.close()
+    with pytest.raises(StepError, match="closed"):
+        eng.step([StepEntry(s, [1])])
+    with pytest.raises(StepError, match="CUDA"):
+        Engine.from_folder(d, "float32", max_tokens=128, device="cpu")
+
+
+def test_command_line(tmp_path):
+    raw, seed = TINY["A"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm = plain_model(d)
+    p = random_ids(9, 256, 5)
+    want = plain.generate(pm, p, 6, stop_ids=(7,))
+    run = subprocess.run([sys.executable, str(ROOT / "bin" / "sllm-b200"), "-model", str(d), "-prompt",
+                          ",".join(map(str, p)), "-tokens", "6", "-dtype", "float32"], capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr
+    assert [int(t) for t in run.stdout.split()] == want
+    assert "prefill" in run.stderr and "decode" in run.stderr and "t/s" in run.stderr
+    bad = subprocess.run([sys.executable, str(ROOT / "bin" / "sllm-b200"), "-prompt", "1,2"], capture_output=True, text=True)
+    assert bad.returncode == 1 and "-model is required" in bad.stderr

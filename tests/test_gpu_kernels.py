@@ -1,0 +1,376 @@
+"""Each kernel alone against the plain implementation's function for the same op, at sizes other
+than any model's (odd widths, head widths in steps of 16, vocabularies that are no power of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-6, torch.bfloat16: 6e-3}      # one op deep: float rounding / one bfloat16 rounding
+
+
+@pytest.fixture(scope="module")
+def kernel_sets():
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    return {dt: KernelSet(dt) for dt in DTYPES}
+
+
+def dev(t, dtype=None):
+    t = torch.as_tensor(t)
+    return (t.to(dtype) if dtype is not None else t).cuda().contiguous()
+
+
+def f64(t):
+    return t.detach().cpu().to(torch.float64)
+
+
+def rand(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+# --------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_rows(kernel_sets, dtype):
+    ks = kernel_sets[dtype]
+    table = dev(rand(37, 24, seed=1), dtype)
+    ids = dev([5, 0, 36, 5, 17], torch.int32)
+    out = torch.empty(5, 24, dtype=torch.float32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ks.embed_rows(ids, table, out, err)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.cpu().long()]) and int(err) == 0
+    ks.embed_rows(dev([3, 37], torch.int32), table, out[:2], err)       # an id outside the table: flagged, zeros
+    assert int(err) == 1 and float(out[1].abs().sum()) == 0.0
+
+
+# --------------------------------------------------------------------------- norm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d, eps, w32", [(40, 1e-5, False), (2048, 1e-6, True), (1000, 1e-3, False), (13000, 1e-5, True)])
+def test_add_rmsnorm(kernel_sets, dtype, d, eps, w32):
+    ks = kernel_sets[dtype]
+    T = 7
+    x = dev(rand(T, d, seed=2, scale=3.0))
+    delta = dev(rand(T, d, seed=3), dtype)
+    w = dev(1.0 + rand(d, seed=4, scale=0.1), torch.float32 if w32 else torch.bfloat16)
+    y = torch.empty(T, d, dtype=dtype, device="cuda")
+    want_sum = f64(x) + f64(delta)
+    want = plain.rms_norm(want_sum, f64(w), eps)
+    xs = x.clone()
+    ks.add_rmsnorm(xs, delta, None, w, y, eps)
+    assert rel_err(y.cpu().float(), want) < TOL[dtype]
+    assert rel_err(xs.cpu(), want_sum) < 2e-7                          # the residual sum is kept in 32-bit
+    # no addend: x untouched
+    xs = x.clone()
+    ks.add_rmsnorm(xs, None, None, w, y, eps)
+    assert torch.equal(xs, x) and rel_err(y.cpu().float(), plain.rms_norm(f64(x), f64(w), eps)) < TOL[dtype]
+    # chosen rows: x untouched, rows of y follow `rows`
+    rows = dev([6, 0, 3], torch.int32)
+    y3 = torch.empty(3, d, dtype=dtype, device="cuda")
+    xs = x.clone()
+    ks.add_rmsnorm(xs, delta, rows, w, y3, eps)
+    assert torch.equal(xs, x) and rel_err(y3.cpu().float(), want[[6, 0, 3]]) < TOL[dtype]
+    # partial sums in float32
+    parts = dev(rand(3, T, d, seed=5))
+    xs = x.clone()
+    ks.add_rmsnorm(xs, parts, None, w, y, eps)
+    want_p = f64(x) + f64(parts).sum(0)
+    assert rel_err(xs.cpu(), want_p) < 5e-7 and rel_err(y.cpu().float(), plain.rms_norm(want_p, f64(w), eps)) < TOL[dtype]
+    ks.add_rmsnorm(x.clone(), parts, rows, w, y3, eps)
+    assert rel_err(y3.cpu().float(), plain.rms_norm(want_p, f64(w), eps)[[6, 0, 3]]) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M, N, K", [(1, 33, 19), (3, 100, 72), (8, 64, 1000), (9, 130, 65), (70, 257, 136), (200, 96, 520)])
+def test_gemm_nt_generic(kernel_sets, dtype, M, N, K):
+    ks = kernel_sets[dtype]
+    a, w = dev(rand(M, K, seed=6), dtype), dev(rand(N, K, seed=7, scale=0.1), dtype)
+    want = plain.linear(f64(a), f64(w))
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    ks.gemm_nt(a, w, out)
+    assert rel_err(out.cpu().float(), want) < TOL[dtype]
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ks.gemm_nt(a, w, out32)
+    assert rel_err(out32.cpu(), want) < 2e-6                           # float accumulation, float output
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 64, 64), (3, 100, 72), (8, 176, 64), (9, 1003, 144), (16, 2048, 2048),
+                                     (33, 96, 200), (64, 640, 4096), (5, 49152 + 16, 256)])
+def test_gemm_small_m(kernel_sets, M, N, K):
+    dk = kernel_sets[torch.bfloat16].decode
+    a, w = dev(rand(M, K, seed=8), torch.bfloat16), dev(rand(N, K, seed=9, scale=0.05), torch.bfloat16)
+    assert dk.takes(a, w)
+    want = plain.linear(f64(a), f64(w))
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    dk.gemm_small_m(a, w, out)
+    assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    dk.gemm_small_m(a, w, out32)
+    assert rel_err(out32.cpu(), want) < 3e-6
+    for split in (2, 5):
+        if K // split >= 8:
+            parts = torch.full((split, M, N), float("nan"), dtype=torch.float32, device="cuda")
+            dk.gemm_small_m(a, w, parts)
+            assert rel_err(parts.sum(0).cpu(), want) < 3e-6
+    if N % 16 == 0:
+        F = N // 2
+        tiled = w.view(2, F // 8, 8, K).permute(1, 0, 2, 3).reshape(N, K).contiguous()
+        h = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+        dk.gemm_small_m(a, tiled, h, swiglu=True)
+        assert rel_err(h.cpu().float(), plain.swiglu(want[:, :F], want[:, F:])) < TOL[torch.bfloat16]
+
+
+def test_gemm_small_m_refuses_what_it_cannot_take(kernel_sets):
+    from scriptling_llm_lib_b200.csrc.bindings import KernelError
+    dk = kernel_sets[torch.bfloat16].decode
+    a, w = dev(rand(4, 36), torch.bfloat16), dev(rand(16, 36), torch.bfloat16)     # K no multiple of 8
+    assert not dk.takes(a, w)
+    with pytest.raises(KernelError):
+        dk.gemm_small_m(a, w, torch.empty(4, 16, dtype=torch.bfloat16, device="cuda"))
+    assert not dk.takes(dev(rand(65, 64), torch.bfloat16), dev(rand(16, 64), torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("F, tiled", [(176, True), (50, False), (8, True)])
+def test_swiglu(kernel_sets, dtype, F, tiled):
+    ks = kernel_sets[dtype]
+    T = 5
+    g, u = rand(T, F, seed=10, scale=2.0), rand(T, F, seed=11)
+    gu = torch.cat([g, u], dim=1)
+    if tiled:
+        gu = torch.stack([g.view(T, F // 8, 8), u.view(T, F // 8, 8)], dim=2).reshape(T, 2 * F)
+    gu = dev(gu, dtype)
+    h = torch.empty(T, F, dtype=dtype, device="cuda")
+    ks.swiglu(gu, h, tiled=tiled)
+    gq, uq = f64(dev(g, dtype)), f64(dev(u, dtype))
+    assert rel_err(h.cpu().float(), plain.swiglu(gq, uq)) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- paged cache helpers
+PAGE = 64
+
+
+def paged(k, v, lengths, n_extra=3, seed=0, dtype=torch.float32):
+    """Scatter per-sequence dense K/V [len, G, hd] into pages handed out in a scrambled order.
+    Unused cache memory is NaN: a kernel that reads past a sequence's length shows it."""
+    G, hd = k[0].shape[1], k[0].shape[2]
+    need = [-(-n // PAGE) for n in lengths]
+    total = sum(need) + n_extra
+    order = np.random.default_rng(seed).permutation(total).tolist()
+    kp = torch.full((total, G, PAGE, hd), float("nan"), dtype=torch.float32)
+    vp = torch.full((total, G, PAGE, hd), float("nan"), dtype=torch.float32)
+    bt = torch.full((len(lengths), max(need)), -1, dtype=torch.int32)
+    for b, n in enumerate(lengths):
+        for i in range(need[b]):
+            pg = order.pop()
+            bt[b, i] = pg
+            m = min(PAGE, n - i * PAGE)
+            kp[pg, :, :m] = k[b][i * PAGE:i * PAGE + m].permute(1, 0, 2)
+            vp[pg, :, :m] = v[b][i * PAGE:i * PAGE + m].permute(1, 0, 2)
+    return dev(kp, dtype), dev(vp, dtype), dev(bt)
+
+
+# --------------------------------------------------------------------------- rotary + cache write
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, G, hd, rot, pairing", [(4, 2, 16, 16, "interleaved"), (3, 1, 32, 16, "half"),
+                                                    (6, 3, 48, 48, "half"), (2, 2, 80, 40, "interleaved")])
+def test_rope_kv_write(kernel_sets, dtype, H, G, hd, rot, pairing):
+    from scriptling_llm_lib_b200.parts.rotary import RotaryEncoding
+    ks = kernel_sets[dtype]
+    enc = RotaryEncoding(hd, rot, 12345.0, None, pairing)
+    enc.prepare(300, "cuda")
+    lens, pos0 = [5, 70, 1], [0, 60, 199]                               # new tokens and tokens already cached
+    T = sum(lens)
+    qkv = dev(rand(T, (H + 2 * G) * hd, seed=12), dtype)
+    tok_seq = np.repeat(np.arange(3), lens)
+    tok_pos = np.concatenate([np.arange(p, p + n) for p, n in zip(pos0, lens)])
+    n_pages = 9
+    kp = torch.zeros(n_pages, G, PAGE, hd, dtype=dtype, device="cuda")
+    vp = torch.zeros_like(kp)
+    bt = dev([[7, -1, -1, -1], [2, 5, 0, -1], [1, 3, 8, 4]], torch.int32)
+    orig = f64(qkv).clone()
+    ks.rope_kv_write(qkv, dev(tok_pos, torch.int32), dev(tok_seq, torch.int32), bt, enc.cos_sin, kp, vp, H, G, hd, rot,
+                     pairing == "interleaved")
+    inv = plain.rope_inv_freq(rot, 12345.0)
+    pos_t = torch.as_tensor(tok_pos)
+    q_want = plain.apply_rope(orig[:, :H * hd].view(T, H, hd), pos_t, inv, pairing)
+    k_want = plain.apply_rope(orig[:, H * hd:(H + G) * hd].view(T, G, hd), pos_t, inv, pairing)
+    v_want = orig[:, (H + G) * hd:].view(T, G, hd)
+    assert rel_err(f64(qkv)[:, :H * hd], q_want.reshape(T, -1)) < TOL[dtype]
+    assert torch.equal(f64(qkv)[:, H * hd:], orig[:, H * hd:])          # k and v columns of the buffer are not rewritten
+    for t in range(T):
+        pg = int(bt[tok_seq[t], tok_pos[t] // PAGE])
+        assert rel_err(f64(kp[pg, :, tok_pos[t] % PAGE]), k_want[t]) < TOL[dtype]
+        assert torch.equal(f64(vp[pg, :, tok_pos[t] % PAGE]), v_want[t])
+    assert float(kp[6].abs().sum()) == 0.0                               # a page nobody owns stays untouched
+    # queries only (a layer that reads another layer's cache)
+    q2 = dev(rand(T, H * hd, seed=13), dtype)
+    o2 = f64(q2).clone()
+    ks.rope_kv_write(q2, dev(tok_pos, torch.int32), dev(tok_seq, torch.int32), bt, enc.cos_sin, None, None, H, 0, hd, rot,
+                     pairing == "interleaved")
+    assert rel_err(f64(q2), plain.apply_rope(o2.view(T, H, hd), pos_t, inv, pairing).reshape(T, -1)) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- attention
+def attention_case(H, G, hd, lens, pos0, seed):
+    """Per sequence: all keys/values (cached + new) and the new queries."""
+    ks_, vs_, qs_ = [], [], []
+    for b, (n, p) in enumerate(zip(lens, pos0)):
+        ks_.append(rand(p + n, G, hd, seed=seed + 3 * b))
+        vs_.append(rand(p + n, G, hd, seed=seed + 3 * b + 1))
+        qs_.append(rand(n, H, hd, seed=seed + 3 * b + 2, scale=2.0))
+    return qs_, ks_, vs_
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, G, hd, window", [(4, 2, 16, None), (3, 1, 32, None), (6, 3, 48, 24), (2, 2, 80, None),
+                                              (8, 2, 64, 100), (2, 1, 128, None)])
+def test_attn_paged(kernel_sets, dtype, H, G, hd, window):
+    ks = kernel_sets[dtype]
+    lens, pos0 = [37, 1, 130, 16], [0, 250, 70, 64]
+    qs, kk, vv = attention_case(H, G, hd, lens, pos0, 20)
+    rnd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.bfloat16().float())
+    qs, kk, vv = [rnd(t) for t in qs], [rnd(t) for t in kk], [rnd(t) for t in vv]
+    kp, vp, bt = paged(kk, vv, [p + n for p, n in zip(pos0, lens)], dtype=dtype)
+    T = sum(lens)
+    q = dev(torch.cat([t.reshape(t.shape[0], -1) for t in qs]), dtype)
+    out = torch.empty(T, H * hd, dtype=dtype, device="cuda")
+    seq_start = dev(np.concatenate([[0], np.cumsum(lens)]), torch.int32)
+    ks.attn_paged(q, out, seq_start, dev(pos0, torch.int32), bt, kp, vp, len(lens), max(lens), H, G, hd, window,
+                  1.0 / math.sqrt(hd))
+    want = torch.cat([plain.attention(f64(qs[b]), f64(kk[b]), f64(vv[b]), torch.arange(pos0[b], pos0[b] + lens[b]),
+                                      torch.arange(pos0[b] + lens[b]), window).reshape(lens[b], -1) for b in range(len(lens))])
+    assert rel_err(out.cpu().float(), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("H, G, hd, window", [(4, 2, 16, None), (3, 1, 32, None), (32, 32, 64, None), (8, 2, 128, 300),
+                                              (4, 1, 64, 65), (2, 2, 256, None)])
+@pytest.mark.parametrize("n_split", [1, 3, 16])
+def test_attn_decode(kernel_sets, H, G, hd, window, n_split):
+    dk = kernel_sets[torch.bfloat16].decode
+    lens, pos0 = [1, 1, 1, 1, 1], [0, 63, 64, 700, 257]
+    qs, kk, vv = attention_case(H, G, hd, lens, pos0, 40)
+    rnd = lambda t: t.bfloat16().float()
+    qs, kk, vv = [rnd(t) for t in qs], [rnd(t) for t in kk], [rnd(t) for t in vv]
+    kp, vp, bt = paged(kk, vv, [p + 1 for p in pos0], dtype=torch.bfloat16)
+    q = dev(torch.cat([t.reshape(1, -1) for t in qs]), torch.bfloat16)
+    B = len(lens)
+    out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
+    scratch = torch.full((B * H * n_split * (hd + 2),), float("nan"), dtype=torch.float32, device="cuda")
+    dk.attn_decode(q, out, dev(pos0, torch.int32), bt, kp, vp, scratch, B, H, G, hd, window, 1.0 / math.sqrt(hd), n_split)
+    want = torch.cat([plain.attention(f64(qs[b]), f64(kk[b]), f64(vv[b]), torch.tensor([pos0[b]]),
+                                      torch.arange(pos0[b] + 1), window).reshape(1, -1) for b in range(B)])
+    assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_and_respects_the_windows_edge(kernel_sets, dtype):
+    """Random keys would hide a key read from the wrong place: one key among 900 gets a score far
+    above the rest, so the output must be that key's value; with a window, the key at distance
+    window-1 is seen and the key at distance window is not."""
+    ks = kernel_sets[dtype]
+    H = G = 2
+    hd, n = 32, 900
+    scale = 1.0 / math.sqrt(hd)
+    for far, window, seen in [(3, None, True), (517, None, True), (n - 1 - 199, 200, True), (n - 1 - 200, 200, False)]:
+        k = rand(n, G, hd, seed=60, scale=0.1)
+        v = rand(n, G, hd, seed=61)
+        q = rand(1, H, hd, seed=62, scale=0.1)
+        k[far] = q[0] * 400.0                                            # score of `far` towers over the others
+        rnd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.bfloat16().float())
+        q, k, v = rnd(q), rnd(k), rnd(v)
+        kp, vp, bt = paged([k], [v], [n], dtype=dtype, seed=far)
+        out = torch.empty(1, H * hd, dtype=dtype, device="cuda")
+        qd = dev(q.reshape(1, -1), dtype)
+        ks.attn_paged(qd, out, dev([0, 1], torch.int32), dev([n - 1], torch.int32), bt, kp, vp, 1, 1, H, G, hd, window, scale)
+        want = plain.attention(f64(q), f64(k), f64(v), torch.tensor([n - 1]), torch.arange(n), window).reshape(1, -1)
+        assert rel_err(out.cpu().float(), want) < TOL[dtype]
+        hit = rel_err(out.cpu().float(), f64(v[far]).reshape(1, -1)) < 1e-2
+        assert hit == seen
+        if dtype == torch.bfloat16:
+            for n_split in (1, 5):
+                scratch = torch.empty(H * n_split * (hd + 2), dtype=torch.float32, device="cuda")
+                ks.decode.attn_decode(qd, out, dev([n - 1], torch.int32), bt, kp, vp, scratch, 1, H, G, hd, window, scale, n_split)
+                assert rel_err(out.cpu().float(), want) < TOL[dtype]
+                assert (rel_err(out.cpu().float(), f64(v[far]).reshape(1, -1)) < 1e-2) == seen
+
+
+# --------------------------------------------------------------------------- sampling
+def params_for(options, seeds, draws):
+    from scriptling_llm_lib_b200.sampling.sampler import pack_params
+    return dev(pack_params(options, seeds, draws))
+
+
+@pytest.mark.parametrize("V", [5, 384, 1003, 49152])
+def test_sampling_kernel_follows_the_plain_samplers(V):
+    from scriptling_llm_lib_b200.csrc.bindings import SamplingKernels
+    from scriptling_llm_lib_b200.sampling.sampler import SamplingOptions
+    sk = SamplingKernels()
+    n = 12
+    logits = rand(n, V, seed=70, scale=2.5)
+    logits[0, 3] = logits[0].max() + 1.0
+    if V > 4:
+        logits[0, 1] = logits[0, 3]                                     # equal maxima: the first wins
+        logits[1, :] = 0.25                                             # all equal but one: ties everywhere
+        logits[1, 0] = 0.5
+    lg = dev(logits)
+    seeds = [1000 + 7 * i for i in range(n)]
+    draws = [i % 5 for i in range(n)]
+    for opts in [SamplingOptions("greedy"), SamplingOptions("temperature", 0.8), SamplingOptions("temperature", 2.5),
+                 SamplingOptions("top_k", 0.9, top_k=7), SamplingOptions("top_k", 1.0, top_k=1),
+                 SamplingOptions("top_k", 1.3, top_k=10 ** 6), SamplingOptions("top_p", 1.0, top_p=0.5),
+                 SamplingOptions("top_p", 0.7, top_p=0.9), SamplingOptions("top_p", 1.0, top_p=1.0),
+                 SamplingOptions("temperature", 0.0)]:
+        out = torch.empty(n, dtype=torch.int32, device="cuda")
+        sk.sample_rows(lg, params_for(opts, seeds, draws), out)
+        got = out.cpu().tolist()
+        for i in range(n):
+            u = plain.uniform_for(seeds[i], draws[i])
+            strategy = "greedy" if opts.is_greedy else opts.strategy
+            want = plain.sample(logits[i].numpy(), strategy, opts.temperature or 1.0, opts.top_k, opts.top_p, u)
+            assert got[i] == want, f"{opts} row {i}: kernel {got[i]}, plain {want}"
+    # a strided view of a wider buffer (the padded logits of a replayed step)
+    wide = torch.zeros(n, V + 13, device="cuda")
+    wide[:, :V] = lg
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    sk.sample_rows(wide[:, :V], params_for(SamplingOptions("greedy"), seeds, draws), out)
+    assert out.cpu().tolist() == [plain.argmax_first(logits[i].numpy()) for i in range(n)]
+
+
+def test_temperature_sampling_has_the_right_distribution():
+    from scriptling_llm_lib_b200.csrc.bindings import SamplingKernels
+    from scriptling_llm_lib_b200.sampling.sampler import SamplingOptions
+    sk = SamplingKernels()
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5]])
+    n = 4000
+    lg = dev(logits.repeat(n, 1))
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    sk.sample_rows(lg, params_for(SamplingOptions("temperature", 0.7), [5] * n, list(range(n))), out)
+    freq = np.bincount(out.cpu().numpy(), minlength=5) / n
+    assert np.abs(freq - plain.softmax_t(logits[0].numpy(), 0.7)).max() < 0.03
+
+
+def test_repeat_penalty_kernel():
+    from scriptling_llm_lib_b200.csrc.bindings import SamplingKernels
+    sk = SamplingKernels()
+    logits = rand(3, 50, seed=80)
+    lg = dev(logits.clone())
+    recent = [[4, 9, 4, 49, 60, -1, 9], list(range(30)), [7]]
+    last_n = 6
+    win = np.full((3, last_n), -1, dtype=np.int32)
+    counts = np.zeros(3, dtype=np.int32)
+    for i, r in enumerate(recent):
+        tail = r[-last_n:]
+        win[i, :len(tail)], counts[i] = tail, len(tail)
+    pen = dev([1.3, 2.0, 0.0])
+    sk.repeat_penalty(lg, dev(win), dev(counts), pen, last_n)
+    for i, p in enumerate([1.3, 2.0]):
+        want = plain.apply_repeat_penalty(logits[i].numpy(), recent[i], p, last_n)
+        assert rel_err(lg[i].cpu(), want) < 1e-6
+    assert torch.equal(lg[2].cpu(), logits[2])                           # penalty 0: off
