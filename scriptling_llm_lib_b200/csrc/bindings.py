@@ -152,12 +152,50 @@ class KernelSet:
 
     # ------------------------------------------------------------------ fast bfloat16 kernels
     @property
+    def tensor_core(self) -> "TensorCoreGemm":
+        if self.dtype != torch.bfloat16:
+            raise KernelError("the tensor-core GEMM is bfloat16 only")
+        if getattr(self, "_tc", None) is None:
+            self._tc = TensorCoreGemm()
+        return self._tc
+
+    @property
     def decode(self) -> "DecodeKernels":
         if self.dtype != torch.bfloat16:
             raise KernelError("the decode kernels are bfloat16 only")
         if getattr(self, "_decode", None) is None:
             self._decode = DecodeKernels()
         return self._decode
+
+
+class TensorCoreGemm:
+    """bfloat16 GEMM on tcgen05 tensor cores with TMA-fed shared memory (the prompt step's products)."""
+
+    def __init__(self):
+        self.lib = load_library("gemm_tcgen05")
+        self.lib.sllm_gemm_tc_bf16.restype = c_int
+
+    @staticmethod
+    def takes(a, w) -> bool:
+        return (a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
+                and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def gemm(self, a, w, out, err_flag, swiglu=False):
+        """out[M,N] = a @ w^T in bfloat16 or float32; swiglu: out[M,N/2] = silu(gate)*up for w's rows
+        tiled 8 gate / 8 up. `err_flag` (int32 on the device) is set if a wait in the kernel timed out."""
+        M, K = a.shape
+        N = w.shape[0]
+        want = (M, N // 2) if swiglu else (M, N)
+        if tuple(out.shape) != want or w.shape[1] != K or out.stride(1) != 1:
+            raise KernelError(f"gemm_tc shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"gemm_tc dtypes: a {a.dtype}, w {w.dtype}, out {out.dtype}")
+        if not (a.is_cuda and w.is_cuda and out.is_cuda):
+            raise KernelError("gemm_tc runs on a CUDA device only")
+        _check(self.lib.sllm_gemm_tc_bf16(
+            c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
+            c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
+            c_int(1 if swiglu else 0), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
 
 
 class DecodeKernels:

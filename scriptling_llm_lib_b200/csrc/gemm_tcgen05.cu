@@ -1,0 +1,315 @@
+// bfloat16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T, float accumulation.
+//
+// One block computes a 128 x BN tile. Warp 0 feeds shared memory with TMA (cp.async.bulk.tensor,
+// 128-byte swizzle, no multicast), warp 1 issues tcgen05.mma from one thread with the accumulator
+// in tensor memory, warps 2-5 read the accumulator back with tcgen05.ld and write the result
+// (as bfloat16, as float, or through the SiLU gate when gate and up columns alternate in groups of 8).
+// Stages are handed over with mbarriers: TMA completes `full[s]`, the MMA's commit arrives on
+// `empty[s]`, the last commit on `tmem_full`. Rows and columns past M, N, K are zero-filled by TMA
+// and masked at the store, so every size with K % 8 == 0 is taken.
+//
+// Replaces the reference's dense matmul (float32_ops.go:462-482) for the prompt step's
+// projections (model_f32.go:391-396, :469-470, :479-493, :519-524).
+//
+// Every wait has a time limit; when one runs out the kernel raises *err, waits (again bounded) for
+// its own copies in flight, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_WAIT_NS 2000000000ull   // 2 s
+
+#define TC_EPI_STORE 0
+#define TC_EPI_SWIGLU 1
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Waits for the barrier's phase `parity`; gives up after TC_WAIT_NS or when another thread of the
+// block has given up (`*abort`), and says so by returning false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+  if (mbar_try(bar, parity)) return true;
+  uint64_t t0 = global_ns();
+  for (uint32_t it = 1;; it++) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort) return false;
+      if (global_ns() - t0 > TC_WAIT_NS) { *abort = 1; return false; }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes (64 bfloat16), 128-byte swizzle:
+// 8-row groups 1024 bytes apart (stride byte offset), leading byte offset 16 bytes, descriptor
+// version 1, layout type 2 (SWIZZLE_128B). A step of 16 in K moves the start address by 32 bytes.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// kind::f16 instruction descriptor: float accumulator, bfloat16 A and B, both K-major, shape M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ C,
+               int M, int N, int K, int ldc, int out_f32, int* __restrict__ err) {
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);     // full[STAGES], empty[STAGES], tmem_full
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  volatile int* abort = (volatile int*)(tmem_slot + 1);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tmem_full = empty0 + 8 * STAGES;
+
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+  int nkb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(tmem_full, 1);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < nkb; kb++) {
+        int s = kb % STAGES;
+        uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort)) break;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        uint32_t a_dst = smem_base + s * STAGE_BYTES;
+        tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+        tma_load_2d(a_dst + A_BYTES, &map_b, kb * TC_BK, n0, full0 + 8 * s);
+        issued = kb + 1;
+      }
+      if (*abort) {
+        // copies already issued still land in this block's shared memory: wait for them (bounded)
+        volatile int never = 0;
+        for (int kb = max(0, issued - STAGES); kb < issued; kb++) mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1, &never);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; kb++) {
+        int s = kb % STAGES;
+        uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(full0 + 8 * s, ph, abort);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t a_addr = smem_base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; k++)
+          umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      if (ok) umma_commit(tmem_full);
+    }
+  } else {
+    int q = warp & 3;                          // the quarter of tensor memory this warp may read
+    bool ok = mbar_wait(tmem_full, 0, abort);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    int row = m0 + q * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;               // uniform over the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row >= M) continue;
+        if (EPI == TC_EPI_STORE) {
+          int col = n0 + c0;
+          if (out_f32) {
+            float* dst = (float*)C + (size_t)row * ldc + col;
+            if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *(float4*)(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __uint_as_float(r[j]);
+            }
+          } else {
+            bf16* dst = (bf16*)C + (size_t)row * ldc + col;
+            if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+                *(uint4*)(dst + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          }
+        } else {
+          // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 outputs at column (n0 + c0) / 2
+          int col = (n0 + c0) >> 1, n_out = N >> 1;
+          bf16* dst = (bf16*)C + (size_t)row * ldc + col;
+          float h[16];
+#pragma unroll
+          for (int t = 0; t < 2; t++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              float g = __uint_as_float(r[16 * t + j]), u = __uint_as_float(r[16 * t + 8 + j]);
+              h[8 * t + j] = g * (1.0f / (1.0f + __expf(-g))) * u;
+            }
+          if (col + 16 <= n_out && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              uint4 v;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(h[j], h[j + 1]), p1 = __floats2bfloat162_rn(h[j + 2], h[j + 3]);
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(h[j + 4], h[j + 5]), p3 = __floats2bfloat162_rn(h[j + 6], h[j + 7]);
+              v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+              *(uint4*)(dst + j) = v;
+            }
+          } else {
+            for (int j = 0; j < 16 && col + j < n_out; j++) dst[j] = __float2bfloat16_rn(h[j]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort) atomicExch(err, 2);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// rows x cols bfloat16, row stride ld elements; box = box_rows x 64 columns, 128-byte swizzle, zero fill
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return SLLM_ERR_ARG - 1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : SLLM_ERR_ARG - 2;
+}
+
+template <int BN, int STAGES, int EPI>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int out_f32,
+                     int* err, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    raised = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+  gemm_tc_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err);
+  SLLM_RETURN_LAST();
+}
+
+// C[M,N] = A[M,K] B[N,K]^T. epilogue 0: C bfloat16 (or float when out_f32), row stride ldc;
+// epilogue 1: C[M,N/2] = silu(gate) * up for B's rows in tiles of 16 (8 gate rows, 8 up rows).
+// *err is set to 2 if a wait inside the kernel ran out of time.
+SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                  int out_f32, int epilogue, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return SLLM_ERR_ARG;
+  if (epilogue == TC_EPI_SWIGLU && ((N & 15) || out_f32)) return SLLM_ERR_ARG;
+  CUtensorMap ma, mb;
+  int big = N > 128;
+  int rc = make_map(&ma, A, M, K, lda, TC_BM);
+  if (rc) return rc;
+  rc = make_map(&mb, B, N, K, ldb, big ? 256 : 128);
+  if (rc) return rc;
+  if (epilogue == TC_EPI_SWIGLU)
+    return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream)
+               : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);
+  return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream)
+             : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
+}

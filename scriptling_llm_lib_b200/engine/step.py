@@ -213,6 +213,9 @@ class Engine:
         else:
             ctx = self._context(entries, ids, lens, pos0, want_rows)
             logits = self._forward(ctx, want=bool(want_rows))
+            if T > B and int(self.err_flag) != 0:       # a prompt step is long enough to afford the read
+                raise StepError("a kernel reported an error during the step (a wait on the device ran out of time, or a "
+                                "token id was out of range)")
         self.cache.advance(growth)
         return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
 

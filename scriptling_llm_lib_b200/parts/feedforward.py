@@ -34,8 +34,11 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         h = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
         w = self.gate_up.weight
-        if self.tiled and x.dtype == torch.bfloat16 and w.dtype == x.dtype and ctx.kernels.decode.takes(x, w):
+        fast = self.tiled and x.dtype == torch.bfloat16 and w.dtype == x.dtype
+        if fast and ctx.kernels.decode.takes(x, w):
             ctx.kernels.decode.gemm_small_m(x, w, h, swiglu=True)
+        elif fast and ctx.kernels.tensor_core.takes(x, w):
+            ctx.kernels.tensor_core.gemm(x, w, h, ctx.err_flag, swiglu=True)
         else:
             gu = self.gate_up.forward(x, ctx)
             ctx.kernels.swiglu(gu, h, tiled=self.tiled)

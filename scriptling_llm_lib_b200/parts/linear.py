@@ -45,7 +45,10 @@ class Linear:
                 ctx.kernels.decode.gemm_small_m(x, w, out)
                 return out
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
-            ctx.kernels.gemm_nt(x, w, out)
+            if x.dtype == torch.bfloat16 and ctx.kernels.tensor_core.takes(x, w):
+                ctx.kernels.tensor_core.gemm(x, w, out, ctx.err_flag)
+            else:
+                ctx.kernels.gemm_nt(x, w, out)
             return out
         if w.dtype == torch.float32 and x.dtype == torch.bfloat16:
             # a matrix kept in 32-bit inside a bfloat16 model: widen the rows, multiply in 32-bit
