@@ -31,6 +31,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "sampling": ("lib_sampling.cu", ("common.cuh",)),
     "decode_bf16": ("decode_bf16.cu", ("common.cuh",)),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh",)),
+    "attn_prefill_bf16": ("attn_prefill_bf16.cu", ("common.cuh",)),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

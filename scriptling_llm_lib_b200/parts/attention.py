@@ -65,6 +65,10 @@ class Attention(Mixer):
                                   device=x.device)
             ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
                                            self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
+        elif x.dtype == torch.bfloat16 and self.head_dim in ctx.kernels.prefill_attention.HEAD_DIMS:
+            ctx.kernels.prefill_attention.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
+                                               ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
+                                               self.window, self.scale)
         else:
             ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
                                    ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
