@@ -57,7 +57,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
@@ -194,6 +194,8 @@ def main():
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
+                    help="run one part only (a small case to profile); the JSON line then holds that part alone")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -219,7 +221,7 @@ def main():
     clocks = ClockSampler()
     try:
         write_model(model_dir, cfg_raw, seed=0)
-        biggest = 64 if not args.no_points else args.batch
+        biggest = 64 if not (args.no_points or args.only != "all") else args.batch
         eng, sampler = llm.load(model_dir, "bfloat16", "cuda:0", max_tokens=biggest * args.context, max_seqs=biggest)
         l2 = torch.zeros(128 * 1024 * 1024, dtype=torch.float32, device="cuda:0")
         rng = np.random.default_rng(1)
@@ -227,7 +229,7 @@ def main():
 
         # ---- prefill of 2,048 tokens, L2 flushed between runs
         times = []
-        for i in range(3 + 5):
+        for i in range((3 + 5) if args.only != "decode" else 0):
             flush_l2(torch, l2)
             s = eng.open()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -240,11 +242,14 @@ def main():
             s.close()
             if i >= 3:
                 times.append(e0.elapsed_time(e1))
-        pre_ms = statistics.median(times)
+        pre_ms = statistics.median(times) if times else float("nan")
         pre_flops = prefill_flops(cfg_raw, args.layers, PREFILL_TOKENS)
         prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                    "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
+        if args.only == "prefill":
+            print(json.dumps({"only": "prefill", "layers_run": args.layers, "prefill": prefill}))
+            return 0
         # ---- the decode step at the headline batch, clocks sampled meanwhile
         clocks.start()
         time.sleep(0.5)
@@ -258,6 +263,10 @@ def main():
                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
 
         points = {}
+        if args.only == "decode":
+            print(json.dumps({"only": "decode", "layers_run": args.layers, "batch": args.batch, "ms_per_step": round(ms, 4),
+                              "value": round(value, 1), "roofline": roofline}))
+            return 0
         if not args.no_points:
             for b in (1, 64):
                 k = max(8, args.steps // 4) if b == 64 else args.steps
