@@ -29,7 +29,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "f32": ("lib_f32.cu", ("common.cuh", "generic_kernels.cuh", "generic_launchers.inc")),
     "bf16": ("lib_bf16.cu", ("common.cuh", "generic_kernels.cuh", "generic_launchers.inc")),
     "sampling": ("lib_sampling.cu", ("common.cuh",)),
-    "decode_bf16": ("decode_bf16.cu", ("common.cuh",)),
+    "decode_bf16": ("decode_bf16.cu", ("common.cuh", "attn_decode_noalloc.h")),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh",)),
     "attn_prefill_bf16": ("attn_prefill_bf16.cu", ("common.cuh",)),
 }

@@ -356,3 +356,57 @@ SLLM_EXPORT int sllm_attn_decode_bf16(const void* q, int q_ld, void* out, const 
     default: return SLLM_ERR_ARG;   // other head widths go through the generic kernel
   }
 }
+
+// ------------------------------------------------------------------ decode attention without any allocation
+// Declared in attn_decode_noalloc.h. The split-key attention above needs scratch for its partial
+// results, which its caller allocates. Some callers cannot allocate device memory at all: code
+// running inside a region where the allocator must not be entered (another library's callback, a
+// real-time loop that forbids cudaMalloc's implicit synchronisation, a host program that has handed
+// all device memory to its own arena). For them the scratch lives in this file, in a fixed array
+// that every GPU loading the library holds until the process exits.
+#include "attn_decode_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[SLLM_NOALLOC_SCRATCH_FLOATS];
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not an address a kernel may
+// use; the device address is asked for once per device, with that device current.
+#define SLLM_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[SLLM_NOALLOC_MAX_DEVICES];
+
+SLLM_EXPORT const char* sllm_attn_decode_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "success";
+    case SLLM_NOALLOC_ERR_TOO_LARGE:
+      return "attn_decode_noalloc: B * H * n_split * (head_dim + 2) floats exceed the built-in scratch "
+             "(SLLM_NOALLOC_SCRATCH_FLOATS); use fewer splits or the entry point that takes caller scratch";
+    case SLLM_NOALLOC_ERR_DEVICE: return "attn_decode_noalloc: the current device's ordinal is beyond the table of 64 devices";
+    case SLLM_ERR_ARG: return "attn_decode_noalloc: bad arguments (head counts, alignment of q, or n_split < 1)";
+    default: return code > 0 ? "attn_decode_noalloc: CUDA error (see cudaError_t)" : "attn_decode_noalloc: unsupported head width";
+  }
+}
+
+SLLM_EXPORT long long sllm_attn_decode_noalloc_capacity_floats(void) { return (long long)SLLM_NOALLOC_SCRATCH_FLOATS; }
+
+SLLM_EXPORT int sllm_attn_decode_bf16_noalloc(const void* q, int q_ld, void* out, const int* seq_pos0,
+                                              const int* block_table, int max_pages, const void* kpages,
+                                              const void* vpages, int B, int H, int G, int hd, int window, float scale,
+                                              int n_split, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (G < 1 || H % G != 0 || n_split < 1 || hd < 1) return SLLM_ERR_ARG;
+  long long need = (long long)B * H * n_split * (hd + 2);
+  if (need > (long long)SLLM_NOALLOC_SCRATCH_FLOATS) return SLLM_NOALLOC_ERR_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= SLLM_NOALLOC_MAX_DEVICES) return SLLM_NOALLOC_ERR_DEVICE;
+  if (g_noalloc_ptr[dev] == nullptr) {           // first call on this device: set-up (do it before any stream capture)
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  // Nothing in the scratch has to start at zero: every block of the split kernel writes all of its
+  // (sequence, head, split) entries, empty splits included, before the merge kernel reads them.
+  return sllm_attn_decode_bf16(q, q_ld, out, seq_pos0, block_table, max_pages, kpages, vpages, g_noalloc_ptr[dev], B, H,
+                               G, hd, window, scale, n_split, stream);
+}
