@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define SLLM_PAGE 64  // tokens per cache page; the Python side asserts the same number
 
@@ -48,4 +49,57 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   float t = (lane < nw) ? red[lane] : 0.f;
   t = warp_sum(t);
   return t;
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched through sllm_launch may be scheduled while the kernel before it in the stream
+// is still draining: its blocks start, do whatever does not depend on earlier kernels (fetch
+// weights), and call pdl_wait() before they touch anything an earlier kernel wrote. Every kernel
+// launched this way calls pdl_launch_dependents() first and pdl_wait() before its first dependent
+// access, so completion stays transitive along the stream. Launched the ordinary way, both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Loads of data that an earlier kernel of the stream wrote. Under programmatic dependent launch
+// this kernel's lifetime overlaps the writer's, so the read-only (non-coherent, `ld.global.nc` /
+// __ldg) path must not be used for them, and the compiler must not move them above pdl_wait():
+// ordinary coherent loads, as volatile asm with a memory clobber. `ld_dep16_stream` does not
+// allocate in L1 (data read once).
+__device__ __forceinline__ uint4 ld_dep16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_dep16_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_dep(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bf16 ld_dep(const bf16* p) {
+  unsigned short v;
+  asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p) : "memory");
+  return __ushort_as_bfloat16(v);
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t sllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  static const bool off = getenv("SLLM_NO_PDL") != nullptr;   // launch the ordinary, fully serialised way
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

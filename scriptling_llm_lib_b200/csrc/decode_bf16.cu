@@ -21,7 +21,6 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
-__device__ __forceinline__ uint4 ld_cached16(const void* p) { return __ldg((const uint4*)p); }
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -57,8 +56,12 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
   // gridDim.y blocks share a tile's K range (their partial sums are kept apart in y); within a
   // block the warps take chunks of 64 k in turn, UN chunks in flight per warp
   int stride = gridDim.y * WARPS;
-  for (int c = blockIdx.y * WARPS + warp; c < nchunks; c += stride * UN) {
-    uint4 a[UN][4];
+  pdl_launch_dependents();
+  // Software pipeline: the weights of the next UN chunks are in flight while the current ones are
+  // multiplied. The first fetch is issued before pdl_wait(): weights do not depend on earlier
+  // kernels, the activations do.
+  uint4 cur[UN][4], nxt[UN][4];
+  auto fetch = [&](uint4 (&a)[UN][4], int c) {
 #pragma unroll
     for (int u = 0; u < UN; u++) {
       int k0 = ((c + u * stride) << 6) + 8 * t, k1 = k0 + 32;
@@ -68,6 +71,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
       a[u][2] = ok1 ? ld_stream16(w0 + k1) : zero;
       a[u][3] = ok1 ? ld_stream16(w1 + k1) : zero;
     }
+  };
+  auto multiply = [&](uint4 (&a)[UN][4], int c) {
 #pragma unroll
     for (int u = 0; u < UN; u++) {
       int k0 = ((c + u * stride) << 6) + 8 * t, k1 = k0 + 32;
@@ -77,8 +82,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
       for (int i = 0; i < NT; i++) {
         int tok = i * 8 + g;
         const bf16* xr = x + (size_t)tok * ldx;
-        b0[i] = (tok < M && ok0) ? ld_cached16(xr + k0) : zero;
-        b1[i] = (tok < M && ok1) ? ld_cached16(xr + k1) : zero;
+        b0[i] = (tok < M && ok0) ? ld_dep16(xr + k0) : zero;
+        b1[i] = (tok < M && ok1) ? ld_dep16(xr + k1) : zero;
       }
 #pragma unroll
       for (int i = 0; i < NT; i++) {
@@ -88,6 +93,20 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
         mma_16816(acc[i], a[u][2].z, a[u][3].z, a[u][2].w, a[u][3].w, b1[i].z, b1[i].w);
       }
     }
+  };
+  // two register buffers used in turn (a copy between them would wait for the loads in flight)
+  const int step = stride * UN;
+  int c = blockIdx.y * WARPS + warp;
+  fetch(cur, c);
+  pdl_wait();
+  while (c < nchunks) {
+    fetch(nxt, c + step);
+    multiply(cur, c);
+    c += step;
+    if (c >= nchunks) break;
+    fetch(cur, c + step);
+    multiply(nxt, c);
+    c += step;
   }
 #pragma unroll
   for (int i = 0; i < NT; i++)
@@ -128,14 +147,9 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
 template <int NT, int EPI>
 static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
                           int out_f32, int ksplit, cudaStream_t stream) {
-  constexpr int UN = NT <= 2 ? 4 : 2;
+  constexpr int UN = NT <= 2 ? 2 : 1;
   dim3 grid((N + 15) / 16, ksplit);
-  int chunks_per_block = ((K + 63) / 64 + ksplit - 1) / ksplit;
-  if (grid.x * grid.y >= 1184 || chunks_per_block <= 16)
-    gemm_small_m_kernel<NT, 4, EPI, UN><<<grid, 128, 0, stream>>>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
-  else
-    gemm_small_m_kernel<NT, 8, EPI, UN><<<grid, 256, 0, stream>>>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
-  SLLM_RETURN_LAST();
+  return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
 }
 
 // epilogue 0: y[M,N] in bfloat16 (or float when out_f32); epilogue 1: y[M,N/2] = silu(gate)*up with
@@ -183,6 +197,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
   constexpr int KPW = 32 / LPK;      // keys a warp reads per load
   __shared__ float sm_acc[AD_WARPS][NREP][HD];
   __shared__ float sm_ml[AD_WARPS][NREP][2];
+  pdl_launch_dependents();
+  pdl_wait();
   int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int slot = lane / LPK, dl = (lane % LPK) * 8;
@@ -200,7 +216,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
 #pragma unroll
     for (int r = 0; r < NREP; r++) {
       int h = g * nrep + r0 + r;
-      uint4 raw = ld_cached16(p.q + (size_t)b * p.q_ld + (size_t)h * HD + dl);
+      uint4 raw = ld_dep16(p.q + (size_t)b * p.q_ld + (size_t)h * HD + dl);
       const bf16* e = (const bf16*)&raw;
 #pragma unroll
       for (int j = 0; j < 8; j++) { q[r][j] = __bfloat162float(e[j]) * (p.scale * AD_LOG2E); acc[r][j] = 0.f; }
@@ -217,8 +233,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
         int kk = ok[u] ? key : k_lo;
         int page = bt[kk / SLLM_PAGE];
         size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * HD + dl;
-        kr[u] = ld_stream16(p.kpages + off);
-        vr[u] = ld_stream16(p.vpages + off);
+        kr[u] = ld_dep16_stream(p.kpages + off);
+        vr[u] = ld_dep16_stream(p.vpages + off);
       }
       float s[AD_UN][NREP];
 #pragma unroll
@@ -306,17 +322,20 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
 // out[b, h*HD + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, int H, int HD,
                                          int n_split) {
+  pdl_launch_dependents();
+  pdl_wait();
   int h = blockIdx.x, b = blockIdx.y;
   const float* src = part + ((size_t)b * H + h) * n_split * (HD + 2);
   float mn = -INFINITY;
-  for (int s = 0; s < n_split; s++) mn = fmaxf(mn, src[(size_t)s * (HD + 2) + HD]);
+  for (int s = 0; s < n_split; s++) mn = fmaxf(mn, ld_dep(src + (size_t)s * (HD + 2) + HD));
   for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
     float a = 0.f, ls = 0.f;
     for (int s = 0; s < n_split; s++) {
       const float* ps = src + (size_t)s * (HD + 2);
-      float c = (mn == -INFINITY || ps[HD] == -INFINITY) ? 0.f : exp2f(ps[HD] - mn);
-      a += ps[dd] * c;
-      ls += ps[HD + 1] * c;
+      float ms = ld_dep(ps + HD);
+      float c = (mn == -INFINITY || ms == -INFINITY) ? 0.f : exp2f(ms - mn);
+      a += ld_dep(ps + dd) * c;
+      ls += ld_dep(ps + HD + 1) * c;
     }
     out[((size_t)b * H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
   }
@@ -326,13 +345,13 @@ template <int HD>
 static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStream_t stream) {
   dim3 grid(a.n_split, a.G, B);
   int nrep = a.H / a.G;
-  if (nrep % 4 == 0) attn_decode_split_kernel<HD, 4><<<grid, AD_WARPS * 32, 0, stream>>>(a);
-  else if (nrep % 2 == 0) attn_decode_split_kernel<HD, 2><<<grid, AD_WARPS * 32, 0, stream>>>(a);
-  else attn_decode_split_kernel<HD, 1><<<grid, AD_WARPS * 32, 0, stream>>>(a);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+  else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+  else e = sllm_launch(attn_decode_split_kernel<HD, 1>, grid, dim3(AD_WARPS * 32), 0, stream, a);
   if (e != cudaSuccess) return (int)e;
-  attn_decode_merge_kernel<<<dim3(a.H, B), HD < 32 ? 32 : HD, 0, stream>>>(a.part, out, a.H, HD, a.n_split);
-  SLLM_RETURN_LAST();
+  return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD < 32 ? 32 : HD), 0, stream,
+                          (const float*)a.part, out, a.H, HD, a.n_split);
 }
 
 // Bytes of scratch `part` must have: B * H * n_split * (hd + 2) floats.

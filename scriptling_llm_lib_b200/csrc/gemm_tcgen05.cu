@@ -1,11 +1,12 @@
 // bfloat16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T, float accumulation.
 //
-// One block computes a 128 x BN tile. Warp 0 feeds shared memory with TMA (cp.async.bulk.tensor,
-// 128-byte swizzle, no multicast), warp 1 issues tcgen05.mma from one thread with the accumulator
-// in tensor memory, warps 2-5 read the accumulator back with tcgen05.ld and write the result
-// (as bfloat16, as float, or through the SiLU gate when gate and up columns alternate in groups of 8).
-// Stages are handed over with mbarriers: TMA completes `full[s]`, the MMA's commit arrives on
-// `empty[s]`, the last commit on `tmem_full`. Rows and columns past M, N, K are zero-filled by TMA
+// One block per SM walks over 128 x BN output tiles. Warp 0 feeds shared memory with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast), warp 1 issues tcgen05.mma from one thread
+// with the accumulator in tensor memory, warps 2-5 read the accumulator back with tcgen05.ld and
+// write the result (as bfloat16, as float, or through the SiLU gate when gate and up columns
+// alternate in groups of 8). Two accumulators take turns, so one tile's epilogue overlaps the next
+// tile's products. Hand-over is by mbarriers: TMA completes `full[s]`, the MMA's commit arrives on
+// `empty[s]`, a tile's last commit on `acc_full[a]`, the epilogue warps on `acc_empty[a]`. Rows and columns past M, N, K are zero-filled by TMA
 // and masked at the store, so every size with K % 8 == 0 is taken.
 //
 // Replaces the reference's dense matmul (float32_ops.go:462-482) for the prompt step's
@@ -100,6 +101,70 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                : "r"(taddr) : "memory");
 }
 
+// Writes 32 consecutive accumulator columns of one row. EPI_STORE: as they are; EPI_SWIGLU: the 32
+// columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2).
+template <int EPI>
+__device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, int ldc, int out_f32, const uint32_t (&r)[32]) {
+  if (EPI == TC_EPI_STORE) {
+    if (out_f32) {
+      float* dst = (float*)C + (size_t)row * ldc + col;
+      if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *(float4*)(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) if (col + j < N) dst[j] = __uint_as_float(r[j]);
+      }
+    } else {
+      bf16* dst = (bf16*)C + (size_t)row * ldc + col;
+      if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 v;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+          v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+          *(uint4*)(dst + j) = v;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) if (col + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+    }
+  } else {
+    int ocol = col >> 1, n_out = N >> 1;
+    bf16* dst = (bf16*)C + (size_t)row * ldc + ocol;
+    float h[16];
+#pragma unroll
+    for (int t = 0; t < 2; t++)
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float g = __uint_as_float(r[16 * t + j]), u = __uint_as_float(r[16 * t + 8 + j]);
+        h[8 * t + j] = g * (1.0f / (1.0f + __expf(-g))) * u;
+      }
+    if (ocol + 16 <= n_out && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 8) {
+        uint4 v;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(h[j], h[j + 1]), p1 = __floats2bfloat162_rn(h[j + 2], h[j + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(h[j + 4], h[j + 5]), p3 = __floats2bfloat162_rn(h[j + 6], h[j + 7]);
+        v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+        *(uint4*)(dst + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j++) if (ocol + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
+    }
+  }
+}
+
+// Persistent: each block walks over output tiles (tile = blockIdx.x, += gridDim.x; consecutive
+// tiles share a weight tile so it is read from HBM once and found in L2 by the others). The
+// shared-memory ring runs on across tiles, and two accumulators in tensor memory take turns, so
+// the epilogue of one tile overlaps the products of the next.
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ C,
@@ -107,25 +172,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);     // full[STAGES], empty[STAGES], tmem_full
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, tmem_full = empty0 + 8 * STAGES;
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, acc_full0 = empty0 + 8 * STAGES, acc_empty0 = acc_full0 + 16;
 
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
-  int nkb = (K + TC_BK - 1) / TC_BK;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN, n_tiles = tiles_m * tiles_n;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(tmem_full, 1);
+    for (int a = 0; a < 2; a++) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 4); }
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -135,114 +200,79 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < nkb; kb++) {
-        int s = kb % STAGES;
-        uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort)) break;
-        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-        uint32_t a_dst = smem_base + s * STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
-        tma_load_2d(a_dst + A_BYTES, &map_b, kb * TC_BK, n0, full0 + 8 * s);
-        issued = kb + 1;
+      int it = 0;                       // k-blocks issued so far, over all tiles of this block
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < nkb; kb++, it++) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, abort);
+          if (!ok) break;
+          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          uint32_t a_dst = smem_base + s * STAGE_BYTES;
+          tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+          tma_load_2d(a_dst + A_BYTES, &map_b, kb * TC_BK, n0, full0 + 8 * s);
+        }
       }
       if (*abort) {
         // copies already issued still land in this block's shared memory: wait for them (bounded)
         volatile int never = 0;
-        for (int kb = max(0, issued - STAGES); kb < issued; kb++) mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1, &never);
+        for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1, &never);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+      int it = 0, i = 0;
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; kb++) {
-        int s = kb % STAGES;
-        uint32_t ph = (kb / STAGES) & 1;
-        ok = mbar_wait(full0 + 8 * s, ph, abort);
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, i++) {
+        int a = i & 1;
+        ok = mbar_wait(acc_empty0 + 8 * a, ((i >> 1) & 1) ^ 1, abort);     // the epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t a_addr = smem_base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+        uint32_t acc = tmem_base + (uint32_t)(a * BN);
+        for (int kb = 0; kb < nkb; kb++, it++) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, abort);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          uint32_t a_addr = smem_base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; k++)
-          umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
-        umma_commit(empty0 + 8 * s);
+          for (int k = 0; k < TC_BK / 16; k++)
+            umma_bf16(acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);
+        }
+        if (ok) umma_commit(acc_full0 + 8 * a);
       }
-      if (ok) umma_commit(tmem_full);
     }
   } else {
     int q = warp & 3;                          // the quarter of tensor memory this warp may read
-    bool ok = mbar_wait(tmem_full, 0, abort);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    int row = m0 + q * 32 + lane;
-    if (ok) {
+    int i = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+      int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+      int a = i & 1;
+      if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      int row = m0 + q * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= N) break;               // uniform over the warp
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row >= M) continue;
-        if (EPI == TC_EPI_STORE) {
-          int col = n0 + c0;
-          if (out_f32) {
-            float* dst = (float*)C + (size_t)row * ldc + col;
-            if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *(float4*)(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
-              for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __uint_as_float(r[j]);
-            }
-          } else {
-            bf16* dst = (bf16*)C + (size_t)row * ldc + col;
-            if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
-                *(uint4*)(dst + j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-            }
-          }
-        } else {
-          // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 outputs at column (n0 + c0) / 2
-          int col = (n0 + c0) >> 1, n_out = N >> 1;
-          bf16* dst = (bf16*)C + (size_t)row * ldc + col;
-          float h[16];
-#pragma unroll
-          for (int t = 0; t < 2; t++)
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-              float g = __uint_as_float(r[16 * t + j]), u = __uint_as_float(r[16 * t + 8 + j]);
-              h[8 * t + j] = g * (1.0f / (1.0f + __expf(-g))) * u;
-            }
-          if (col + 16 <= n_out && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 8) {
-              uint4 v;
-              __nv_bfloat162 p0 = __floats2bfloat162_rn(h[j], h[j + 1]), p1 = __floats2bfloat162_rn(h[j + 2], h[j + 3]);
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(h[j + 4], h[j + 5]), p3 = __floats2bfloat162_rn(h[j + 6], h[j + 7]);
-              v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
-              *(uint4*)(dst + j) = v;
-            }
-          } else {
-            for (int j = 0; j < 16 && col + j < n_out; j++) dst[j] = __float2bfloat16_rn(h[j]);
-          }
-        }
+        if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * a) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
   if (threadIdx.x == 0 && *abort) atomicExch(err, 2);
 }
@@ -288,7 +318,14 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int 
     if (e != cudaSuccess) return (int)e;
     raised = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 1;
+  }
+  int n_tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
+  dim3 grid(n_tiles < sms ? n_tiles : sms);
   gemm_tc_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err);
   SLLM_RETURN_LAST();
 }

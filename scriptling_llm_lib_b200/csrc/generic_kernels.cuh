@@ -17,6 +17,8 @@
 template <typename W>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const W* __restrict__ table,
                                   float* __restrict__ out, int d, int vocab, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x;
   int id = ids[t];
   bool ok = id >= 0 && id < vocab;
@@ -39,6 +41,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
                                    int w_f32, A* __restrict__ y, int d, float eps) {
   extern __shared__ float sm_row[];
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   int r = blockIdx.x;
   size_t in = rows ? (size_t)rows[r] : (size_t)r;
   float* xr = x + in * d;
@@ -47,10 +51,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
   float ss = 0.f;
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = xr[j];
-    if (dr) v += to_f32(dr[j]);
+    if (dr) v += to_f32(ld_dep(dr + j));
     if (pr) {
       float a = 0.f;
-      for (int p = 0; p < n_parts; p++) a += pr[(size_t)p * part_stride + j];
+      for (int p = 0; p < n_parts; p++) a += ld_dep(pr + (size_t)p * part_stride + j);
       v += a;
     }
     sm_row[j] = v;
@@ -168,6 +172,8 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, int ld, const int* __r
                                      const int* __restrict__ tok_seq, const int* __restrict__ block_table,
                                      int max_pages, const float2* __restrict__ cs, A* __restrict__ kpages,
                                      A* __restrict__ vpages, int H, int n_kv, int hd, int rot, int interleaved) {
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x;
   int pos = tok_pos[t];
   int half = rot >> 1;

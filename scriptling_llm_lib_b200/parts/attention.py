@@ -14,6 +14,7 @@ import math
 import torch
 
 from ..cache.needs import CacheNeed
+from ..csrc.bindings import DecodeKernels, PrefillAttention
 from .base import MIXERS, POSITION_ENCODINGS, Mixer, PartSpec
 from .linear import Linear
 
@@ -59,13 +60,13 @@ class Attention(Mixer):
             qkv = self.q_only.forward(x, ctx)
             self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
         attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        if ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in ctx.kernels.decode.HEAD_DIMS:
+        if ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS:
             n_split = ctx.decode_splits(self.n_kv_heads)
             scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                   device=x.device)
             ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
                                            self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
-        elif x.dtype == torch.bfloat16 and self.head_dim in ctx.kernels.prefill_attention.HEAD_DIMS:
+        elif x.dtype == torch.bfloat16 and self.head_dim in PrefillAttention.HEAD_DIMS:
             ctx.kernels.prefill_attention.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
                                                ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
                                                self.window, self.scale)
