@@ -87,6 +87,59 @@ __device__ __forceinline__ bf16 ld_dep(const bf16* p) {
   return __ushort_as_bfloat16(v);
 }
 
+// four / eight consecutive elements as floats
+__device__ __forceinline__ float4 ld_dep4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_dep4(const bf16* p) {
+  uint32_t a, b;
+  asm volatile("ld.global.v2.u32 {%0,%1}, [%2];" : "=r"(a), "=r"(b) : "l"(p) : "memory");
+  __nv_bfloat162 lo = *(__nv_bfloat162*)&a, hi = *(__nv_bfloat162*)&b;
+  return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+__device__ __forceinline__ float4 ld4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  uint2 r = *(const uint2*)p;
+  __nv_bfloat162 lo = *(__nv_bfloat162*)&r.x, hi = *(__nv_bfloat162*)&r.y;
+  return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 r;
+  r.x = *(uint32_t*)&lo;
+  r.y = *(uint32_t*)&hi;
+  *(uint2*)p = r;
+}
+struct F8 { float f[8]; };
+__device__ __forceinline__ F8 ld8(const float* p) {
+  F8 r;
+  float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  r.f[0] = a.x; r.f[1] = a.y; r.f[2] = a.z; r.f[3] = a.w; r.f[4] = b.x; r.f[5] = b.y; r.f[6] = b.z; r.f[7] = b.w;
+  return r;
+}
+__device__ __forceinline__ F8 ld8(const bf16* p) {
+  F8 r;
+  uint4 v = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+  for (int i = 0; i < 4; i++) { r.f[2 * i] = __low2float(h[i]); r.f[2 * i + 1] = __high2float(h[i]); }
+  return r;
+}
+__device__ __forceinline__ void st8(float* p, const F8& r) {
+  *(float4*)p = make_float4(r.f[0], r.f[1], r.f[2], r.f[3]);
+  *(float4*)(p + 4) = make_float4(r.f[4], r.f[5], r.f[6], r.f[7]);
+}
+__device__ __forceinline__ void st8(bf16* p, const F8& r) {
+  uint4 v;
+  __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+  for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(r.f[2 * i], r.f[2 * i + 1]);
+  *(uint4*)p = v;
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t sllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                       Args... args) {

@@ -49,6 +49,34 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
   const A* dr = (delta && n_parts == 0) ? (const A*)delta + in * d : nullptr;
   const float* pr = (delta && n_parts > 0) ? (const float*)delta + in * d : nullptr;
   float ss = 0.f;
+  A* yr = y + (size_t)r * d;
+  bool update = (rows == nullptr) && (delta != nullptr);
+  if ((d & 3) == 0) {
+    // four elements per thread and step: 16-byte accesses to the float rows
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+      float4 v = *(const float4*)(xr + j);
+      if (dr) { float4 a = ld_dep4(dr + j); v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
+      if (pr) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < n_parts; p++) {
+          float4 b = ld_dep4(pr + (size_t)p * part_stride + j);
+          a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+      }
+      *(float4*)(sm_row + j) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+      float4 v = *(const float4*)(sm_row + j);
+      if (update) *(float4*)(xr + j) = v;
+      float4 wv = w_f32 ? ld4((const float*)w + j) : ld4((const bf16*)w + j);
+      st4(yr + j, make_float4((v.x * inv) * wv.x, (v.y * inv) * wv.y, (v.z * inv) * wv.z, (v.w * inv) * wv.w));
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = xr[j];
     if (dr) v += to_f32(ld_dep(dr + j));
@@ -62,8 +90,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
   }
   ss = block_sum(ss, red);
   float inv = 1.0f / sqrtf(ss / (float)d + eps);
-  A* yr = y + (size_t)r * d;
-  bool update = (rows == nullptr) && (delta != nullptr);
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = sm_row[j];
     if (update) xr[j] = v;
@@ -211,6 +237,79 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, int ld, const int* __r
   for (int idx = threadIdx.x; idx < n_kv * hd; idx += blockDim.x) {
     int g = idx / hd, j = idx % hd;
     vpages[cache_base + (size_t)g * SLLM_PAGE * hd + j] = row[(size_t)(H + n_kv + g) * hd + j];
+  }
+}
+
+// The same with 16-byte accesses, eight elements per thread and step. Needs head width and row
+// stride in multiples of 8 and a rotary width in multiples of 16 (half pairing) or 8 (interleaved).
+template <typename A>
+__global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, int ld, const int* __restrict__ tok_pos,
+                                         const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                         int max_pages, const float2* __restrict__ cs, A* __restrict__ kpages,
+                                         A* __restrict__ vpages, int H, int n_kv, int hd, int rot, int interleaved) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int t = blockIdx.x;
+  int pos = tok_pos[t];
+  int half = rot >> 1;
+  A* row = qkv + (size_t)t * ld;
+  size_t cache_base = 0;
+  if (n_kv > 0) {
+    int page = block_table[(size_t)tok_seq[t] * max_pages + pos / SLLM_PAGE];
+    cache_base = ((size_t)page * n_kv * SLLM_PAGE + (pos % SLLM_PAGE)) * hd;
+  }
+  const float2* csr = cs + (size_t)pos * half;
+  if (interleaved) {
+    int vecs = rot >> 3;                       // 8 elements = 4 adjacent pairs
+    for (int idx = threadIdx.x; idx < (H + n_kv) * vecs; idx += blockDim.x) {
+      int head = idx / vecs, v = idx % vecs;
+      A* h = row + (size_t)head * hd + v * 8;
+      F8 x = ld8(h), y;
+      const float4* c4 = (const float4*)(csr + v * 4);   // (cos, sin) of 4 pairs
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        float4 c = c4[i];
+        y.f[4 * i] = x.f[4 * i] * c.x - x.f[4 * i + 1] * c.y;
+        y.f[4 * i + 1] = x.f[4 * i] * c.y + x.f[4 * i + 1] * c.x;
+        y.f[4 * i + 2] = x.f[4 * i + 2] * c.z - x.f[4 * i + 3] * c.w;
+        y.f[4 * i + 3] = x.f[4 * i + 2] * c.w + x.f[4 * i + 3] * c.z;
+      }
+      if (head < H) st8(h, y);
+      else st8(kpages + cache_base + (size_t)(head - H) * SLLM_PAGE * hd + v * 8, y);
+    }
+  } else {
+    int vecs = half >> 3;                      // 8 first-half elements and their 8 partners
+    for (int idx = threadIdx.x; idx < (H + n_kv) * vecs; idx += blockDim.x) {
+      int head = idx / vecs, v = idx % vecs;
+      A* h = row + (size_t)head * hd + v * 8;
+      F8 x0 = ld8(h), x1 = ld8(h + half), y0, y1;
+      const float4* c4 = (const float4*)(csr + v * 8);
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        float4 c = c4[i];
+        y0.f[2 * i] = x0.f[2 * i] * c.x - x1.f[2 * i] * c.y;
+        y1.f[2 * i] = x0.f[2 * i] * c.y + x1.f[2 * i] * c.x;
+        y0.f[2 * i + 1] = x0.f[2 * i + 1] * c.z - x1.f[2 * i + 1] * c.w;
+        y1.f[2 * i + 1] = x0.f[2 * i + 1] * c.w + x1.f[2 * i + 1] * c.z;
+      }
+      if (head < H) { st8(h, y0); st8(h + half, y1); }
+      else {
+        A* dst = kpages + cache_base + (size_t)(head - H) * SLLM_PAGE * hd + v * 8;
+        st8(dst, y0);
+        st8(dst + half, y1);
+      }
+    }
+  }
+  if (n_kv == 0) return;
+  int tail = (hd - rot) >> 3;
+  for (int idx = threadIdx.x; idx < n_kv * tail; idx += blockDim.x) {
+    int g = idx / tail, j = rot + (idx % tail) * 8;
+    st8(kpages + cache_base + (size_t)g * SLLM_PAGE * hd + j, ld8(row + (size_t)(H + g) * hd + j));
+  }
+  int vv = hd >> 3;
+  for (int idx = threadIdx.x; idx < n_kv * vv; idx += blockDim.x) {
+    int g = idx / vv, j = (idx % vv) * 8;
+    st8(vpages + cache_base + (size_t)g * SLLM_PAGE * hd + j, ld8(row + (size_t)(H + n_kv + g) * hd + j));
   }
 }
 

@@ -179,7 +179,8 @@ def paged(k, v, lengths, n_extra=3, seed=0, dtype=torch.float32):
 # --------------------------------------------------------------------------- rotary + cache write
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, G, hd, rot, pairing", [(4, 2, 16, 16, "interleaved"), (3, 1, 32, 16, "half"),
-                                                    (6, 3, 48, 48, "half"), (2, 2, 80, 40, "interleaved")])
+                                                    (6, 3, 48, 48, "half"), (2, 2, 80, 40, "interleaved"),
+                                                    (2, 1, 16, 8, "half"), (5, 5, 32, 12, "interleaved")])
 def test_rope_kv_write(kernel_sets, dtype, H, G, hd, rot, pairing):
     from scriptling_llm_lib_b200.parts.rotary import RotaryEncoding
     ks = kernel_sets[dtype]
