@@ -48,6 +48,11 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *(uint32_t*)&v;
@@ -145,40 +150,45 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_kernel(FaArgs p) {
         mma16816(s[2 * np + 1], qf[ks], b2, b3);
       }
     }
-    // ---- mask, online softmax
+    // ---- mask, online softmax. The maximum is kept on the raw scores; the scale (times log2 e)
+    // enters the exponent through one fused multiply-add: p = 2^(s*sc - m*sc).
     bool need_mask = (t * FA_BK + FA_BK - 1 > q_lo + qrow) || (p.window > 0 && t * FA_BK <= q_hi - p.window + 0);
     float mx[2] = {-INFINITY, -INFINITY};
+    if (need_mask) {
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+      for (int i = 0; i < 8; i++)
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        float v = s[i][e] * sc;
-        if (need_mask) {
+        for (int e = 0; e < 4; e++) {
           int key = t * FA_BK + i * 8 + tig * 2 + (e & 1);
           int qp = (e >> 1) ? qpos_b : qpos_a;
           bool seen = key <= qp && (p.window == 0 || key > qp - p.window);
-          if (!seen) v = -INFINITY;
+          if (!seen) s[i][e] = -INFINITY;
         }
-        s[i][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-      }
-    float corr[2];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      mx[0] = fmaxf(mx[0], fmaxf(s[i][0], s[i][1]));
+      mx[1] = fmaxf(mx[1], fmaxf(s[i][2], s[i][3]));
+    }
+    float corr[2], msc[2];
 #pragma unroll
     for (int r = 0; r < 2; r++) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       float m_new = fmaxf(m[r], mx[r]);
-      corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(m[r] - m_new);
+      float m_fin = (m_new == -INFINITY) ? 0.f : m_new;        // nothing seen yet: every s is -inf, p = 0
+      corr[r] = ex2_approx((m[r] - m_fin) * sc);               // m[r] = -inf gives 0
+      msc[r] = m_fin * sc;
       m[r] = m_new;
     }
     float rs[2] = {0.f, 0.f};
     uint32_t pf[4][4];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      float e0 = m[0] == -INFINITY ? 0.f : exp2f(s[i][0] - m[0]);
-      float e1 = m[0] == -INFINITY ? 0.f : exp2f(s[i][1] - m[0]);
-      float e2 = m[1] == -INFINITY ? 0.f : exp2f(s[i][2] - m[1]);
-      float e3 = m[1] == -INFINITY ? 0.f : exp2f(s[i][3] - m[1]);
+      float e0 = ex2_approx(fmaf(s[i][0], sc, -msc[0]));
+      float e1 = ex2_approx(fmaf(s[i][1], sc, -msc[0]));
+      float e2 = ex2_approx(fmaf(s[i][2], sc, -msc[1]));
+      float e3 = ex2_approx(fmaf(s[i][3], sc, -msc[1]));
       rs[0] += e0 + e1;
       rs[1] += e2 + e3;
       pf[i >> 1][(i & 1) * 2] = pack_bf16(e0, e1);
