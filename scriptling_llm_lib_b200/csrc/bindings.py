@@ -231,7 +231,7 @@ class DecodeKernels:
 
     def __init__(self):
         self.lib = load_library("decode_bf16")
-        for n in ("sllm_gemm_small_m_bf16", "sllm_attn_decode_bf16"):
+        for n in ("sllm_gemm_small_m_bf16", "sllm_attn_decode_bf16", "sllm_attn_decode_merged_bf16"):
             getattr(self.lib, n).restype = c_int
         self.lib.sllm_attn_decode_scratch_bytes.restype = c_longlong
 
@@ -240,6 +240,12 @@ class DecodeKernels:
         K = a.shape[1]
         return (a.shape[0] <= DecodeKernels.MAX_M and K % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
                 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+    @staticmethod
+    def prefers(a, w) -> bool:
+        """True when this kernel is the faster one for the shape: always up to 16 rows; beyond that
+        only while the output is too narrow to give the 128 x 256 tensor-core tiles enough blocks."""
+        return DecodeKernels.takes(a, w) and (a.shape[0] <= 16 or w.shape[0] < 12288)
 
     def gemm_small_m(self, a, w, out, swiglu=False):
         """out[M,N] = a @ w^T (bfloat16 or float32 out); swiglu: out[M,N/2] = silu(gate)*up for w rows
@@ -266,16 +272,24 @@ class DecodeKernels:
         return max(1, min(8, (4 * sm_count) // tiles, k // 512))
 
     def attn_decode(self, q, out, seq_pos0, block_table, kpages, vpages, scratch, n_seqs, n_heads, n_kv, head_dim,
-                    window, scale, n_split):
+                    window, scale, n_split, tickets=None):
+        """`tickets` (int32 [>= n_seqs * n_kv], zero before its first use, left zero): the last split
+        to finish merges the partial results in the same kernel; without it a second kernel merges."""
         need = self.lib.sllm_attn_decode_scratch_bytes(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_split))
         if scratch.numel() * scratch.element_size() < need:
             raise KernelError(f"attn_decode scratch holds {scratch.numel() * scratch.element_size()} bytes, needs {need}")
-        _check(self.lib.sllm_attn_decode_bf16(
-            _ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), _ptr(out, torch.bfloat16, "out"),
-            _ptr(seq_pos0, torch.int32, "seq_pos0"), _ptr(block_table, torch.int32, "block_table"),
-            c_int(block_table.shape[1]), _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"),
-            _ptr(scratch, torch.float32, "scratch"), c_int(n_seqs), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-            c_int(window or 0), c_float(scale), c_int(n_split), _stream()), "attn_decode")
+        head = (_ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), _ptr(out, torch.bfloat16, "out"),
+                _ptr(seq_pos0, torch.int32, "seq_pos0"), _ptr(block_table, torch.int32, "block_table"),
+                c_int(block_table.shape[1]), _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"),
+                _ptr(scratch, torch.float32, "scratch"))
+        tail = (c_int(n_seqs), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(window or 0), c_float(scale),
+                c_int(n_split), _stream())
+        if tickets is None:
+            _check(self.lib.sllm_attn_decode_bf16(*head, *tail), "attn_decode")
+        else:
+            if tickets.numel() < n_seqs * n_kv:
+                raise KernelError(f"attn_decode tickets hold {tickets.numel()} ints, needs {n_seqs * n_kv}")
+            _check(self.lib.sllm_attn_decode_merged_bf16(*head, _ptr(tickets, torch.int32, "tickets"), *tail), "attn_decode")
 
 
 class CastKernels:

@@ -189,6 +189,8 @@ struct AttnDecodeArgs {
   float* part;          // [B][H][n_split][HD + 2]: unnormalised sum, running max (log2 units), running sum
   int H, G, window, n_split;
   float scale;
+  bf16* out;            // [B, H*HD]; written by this kernel only when `tickets` is given
+  int* tickets;         // [B*G] zero before the first launch, or null: a separate kernel merges the splits
 };
 
 template <int HD, int NREP>
@@ -317,6 +319,36 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
     }
     __syncthreads();
   }
+  if (p.tickets == nullptr) return;
+  // The block that finishes last among the splits of this (sequence, key/value head) merges them:
+  // every block publishes its partial results, then takes a ticket; nobody waits for anybody.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = p.tickets + (size_t)b * p.G + g;
+    int t = atomicAdd(tk, 1);
+    s_last = (t == p.n_split - 1);
+    if (s_last) *tk = 0;                       // all splits have drawn: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int v = threadIdx.x; v < nrep * HD; v += AD_WARPS * 32) {
+    int h = g * nrep + v / HD, dd = v % HD;
+    const float* src = p.part + ((size_t)b * p.H + h) * p.n_split * (HD + 2);
+    float mn = -INFINITY;
+    for (int s2 = 0; s2 < p.n_split; s2++) mn = fmaxf(mn, __ldcg(src + (size_t)s2 * (HD + 2) + HD));
+    float a = 0.f, ls = 0.f;
+    for (int s2 = 0; s2 < p.n_split; s2++) {
+      const float* ps = src + (size_t)s2 * (HD + 2);
+      float ms = __ldcg(ps + HD);
+      float c = (mn == -INFINITY || ms == -INFINITY) ? 0.f : exp2f(ms - mn);
+      a += __ldcg(ps + dd) * c;
+      ls += __ldcg(ps + HD + 1) * c;
+    }
+    p.out[((size_t)b * p.H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+  }
 }
 
 // out[b, h*HD + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M)
@@ -349,7 +381,7 @@ static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStr
   if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4>, grid, dim3(AD_WARPS * 32), 0, stream, a);
   else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2>, grid, dim3(AD_WARPS * 32), 0, stream, a);
   else e = sllm_launch(attn_decode_split_kernel<HD, 1>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess || a.tickets != nullptr) return (int)e;
   return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD < 32 ? 32 : HD), 0, stream,
                           (const float*)a.part, out, a.H, HD, a.n_split);
 }
@@ -359,13 +391,13 @@ SLLM_EXPORT long long sllm_attn_decode_scratch_bytes(int B, int H, int hd, int n
   return (long long)B * H * n_split * (hd + 2) * (long long)sizeof(float);
 }
 
-SLLM_EXPORT int sllm_attn_decode_bf16(const void* q, int q_ld, void* out, const int* seq_pos0, const int* block_table,
-                                      int max_pages, const void* kpages, const void* vpages, void* scratch, int B, int H,
-                                      int G, int hd, int window, float scale, int n_split, cudaStream_t stream) {
+static int attn_decode_dispatch(const void* q, int q_ld, void* out, const int* seq_pos0, const int* block_table,
+                                int max_pages, const void* kpages, const void* vpages, void* scratch, int* tickets, int B,
+                                int H, int G, int hd, int window, float scale, int n_split, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (G < 1 || H % G != 0 || n_split < 1 || (q_ld & 7) || ((uintptr_t)q & 15)) return SLLM_ERR_ARG;
   AttnDecodeArgs a{(const bf16*)q, q_ld, seq_pos0, block_table, max_pages, (const bf16*)kpages, (const bf16*)vpages,
-                   (float*)scratch, H, G, window, n_split, scale};
+                   (float*)scratch, H, G, window, n_split, scale, (bf16*)out, tickets};
   switch (hd) {
     case 16: return attn_decode_launch<16>(a, (bf16*)out, B, stream);
     case 32: return attn_decode_launch<32>(a, (bf16*)out, B, stream);
@@ -374,6 +406,25 @@ SLLM_EXPORT int sllm_attn_decode_bf16(const void* q, int q_ld, void* out, const 
     case 256: return attn_decode_launch<256>(a, (bf16*)out, B, stream);
     default: return SLLM_ERR_ARG;   // other head widths go through the generic kernel
   }
+}
+
+// Split kernel + merge kernel; `scratch` may hold anything.
+SLLM_EXPORT int sllm_attn_decode_bf16(const void* q, int q_ld, void* out, const int* seq_pos0, const int* block_table,
+                                      int max_pages, const void* kpages, const void* vpages, void* scratch, int B, int H,
+                                      int G, int hd, int window, float scale, int n_split, cudaStream_t stream) {
+  return attn_decode_dispatch(q, q_ld, out, seq_pos0, block_table, max_pages, kpages, vpages, scratch, nullptr, B, H, G, hd,
+                              window, scale, n_split, stream);
+}
+
+// One kernel: the last split to finish merges. `tickets` holds B*G ints that are zero before the
+// first launch (the kernel leaves them zero); launches that share it must not overlap.
+SLLM_EXPORT int sllm_attn_decode_merged_bf16(const void* q, int q_ld, void* out, const int* seq_pos0,
+                                             const int* block_table, int max_pages, const void* kpages,
+                                             const void* vpages, void* scratch, int* tickets, int B, int H, int G, int hd,
+                                             int window, float scale, int n_split, cudaStream_t stream) {
+  if (tickets == nullptr) return SLLM_ERR_ARG;
+  return attn_decode_dispatch(q, q_ld, out, seq_pos0, block_table, max_pages, kpages, vpages, scratch, tickets, B, H, G, hd,
+                              window, scale, n_split, stream);
 }
 
 // ------------------------------------------------------------------ decode attention without any allocation

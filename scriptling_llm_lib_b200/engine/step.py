@@ -110,6 +110,7 @@ class Engine:
         self.decode_graphs = DecodeGraphs(self)
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._tickets = None
         self.cache = None
         self.resize_cache(max_tokens, max_seqs)
 
@@ -161,6 +162,13 @@ class Engine:
     # ------------------------------------------------------------------ sequences
     def open(self) -> Sequence:
         return Sequence(self, self.cache.open())
+
+    def tickets(self, n: int) -> torch.Tensor:
+        """Zeroed int32 counters that kernels of one stream draw tickets from and leave zero (which
+        of several blocks finishes last). One buffer for the engine: its kernels run one after another."""
+        if self._tickets is None or self._tickets.numel() < n:
+            self._tickets = torch.zeros(max(4096, 2 * n), dtype=torch.int32, device=self.device)
+        return self._tickets
 
     def new_event(self):
         return torch.cuda.Event(enable_timing=True)

@@ -65,7 +65,8 @@ class Attention(Mixer):
             scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                   device=x.device)
             ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
-                                           self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
+                                           self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split,
+                                           tickets=ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads))
         elif x.dtype == torch.bfloat16 and self.head_dim in PrefillAttention.HEAD_DIMS:
             ctx.kernels.prefill_attention.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
                                                ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,

@@ -38,7 +38,7 @@ class Linear:
         w = self.weight
         out_dtype = out_dtype or x.dtype
         if w.dtype == x.dtype:
-            if x.dtype == torch.bfloat16 and ctx.kernels.decode.takes(x, w):
+            if x.dtype == torch.bfloat16 and ctx.kernels.decode.prefers(x, w):
                 split = ctx.kernels.decode.split_for(w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
                 shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
                 out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)

@@ -64,6 +64,24 @@ class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self.kernels = SamplingKernels()
+        self._greedy_params = torch.zeros((0, SamplingKernels.PARAM_WORDS), dtype=torch.int32, device=self.device)
+        self._host = torch.zeros((64, SamplingKernels.PARAM_WORDS), dtype=torch.int32).pin_memory()
+        self._copied = torch.cuda.Event()
+
+    def _params(self, options, seeds, draws) -> torch.Tensor:
+        n = len(seeds)
+        if options.is_greedy:                       # strategy word 0 in every row; nothing else is read
+            if self._greedy_params.shape[0] < n:
+                self._greedy_params = torch.zeros((max(64, 2 * n), SamplingKernels.PARAM_WORDS), dtype=torch.int32,
+                                                  device=self.device)
+            return self._greedy_params[:n]
+        if self._host.shape[0] < n:
+            self._host = torch.zeros((2 * n, SamplingKernels.PARAM_WORDS), dtype=torch.int32).pin_memory()
+        self._copied.synchronize()                  # the last copy out of the pinned rows is done
+        self._host[:n] = torch.from_numpy(pack_params(options, seeds, draws))
+        dev = self._host[:n].to(self.device, non_blocking=True)
+        self._copied.record()
+        return dev
 
     def sample(self, logits: torch.Tensor, options: SamplingOptions, seeds: list[int], draws: list[int],
                recent: list[list[int]] | None = None) -> torch.Tensor:
@@ -82,7 +100,7 @@ class Sampler:
             self.kernels.repeat_penalty(
                 logits, torch.from_numpy(win).to(self.device), torch.from_numpy(counts).to(self.device),
                 torch.full((n,), float(options.repeat_penalty), dtype=torch.float32, device=self.device), last_n)
-        params = torch.from_numpy(pack_params(options, seeds, draws)).to(self.device)
+        params = self._params(options, seeds, draws)
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         self.kernels.sample_rows(logits, params, out)
         return out

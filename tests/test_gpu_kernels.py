@@ -287,6 +287,15 @@ def test_attn_decode(kernel_sets, H, G, hd, window, n_split):
     want = torch.cat([plain.attention(f64(qs[b]), f64(kk[b]), f64(vv[b]), torch.tensor([pos0[b]]),
                                       torch.arange(pos0[b] + 1), window).reshape(1, -1) for b in range(B)])
     assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+    # one kernel: the last split to finish merges; twice, the tickets must come back to zero
+    tickets = torch.zeros(B * G, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        out.fill_(float("nan"))
+        scratch.fill_(float("nan"))
+        dk.attn_decode(q, out, dev(pos0, torch.int32), bt, kp, vp, scratch, B, H, G, hd, window, 1.0 / math.sqrt(hd), n_split,
+                       tickets=tickets)
+        assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+        assert int(tickets.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
