@@ -39,9 +39,22 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 template <int NT, int WARPS, int EPI, int UN>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ y, int M, int N, int K,
-                    int ldx, int ldw, int ldy, int out_f32) {
+                    int ldx, int ldw, int ldy, int out_f32, const void* next_w, unsigned long long next_bytes) {
   __shared__ float red[WARPS][NT][4][32];
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  if (next_w != nullptr && threadIdx.x == 0) {
+    // ask L2 for this block's share of the weights the next product will stream
+    unsigned long long blocks = (unsigned long long)gridDim.x * gridDim.y, id = blockIdx.y * (unsigned long long)gridDim.x + blockIdx.x;
+    unsigned long long per = ((next_bytes + blocks - 1) / blocks + 127ull) & ~127ull;
+    unsigned long long off = id * per;
+    while (off < next_bytes && per > 0) {
+      unsigned long long n = min(min(per, next_bytes - off), 8192ull) & ~15ull;
+      if (n == 0) break;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)next_w + off), "r"((unsigned)n) : "memory");
+      off += n;
+      per -= n;
+    }
+  }
   int n0 = blockIdx.x * 16;
   const bf16* w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
   const bf16* w1 = W + (size_t)min(n0 + g + 8, N - 1) * ldw;
@@ -146,26 +159,32 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
 
 template <int NT, int EPI>
 static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
-                          int out_f32, int ksplit, cudaStream_t stream) {
+                          int out_f32, int ksplit, const void* next_w, unsigned long long next_bytes, cudaStream_t stream) {
   constexpr int UN = NT <= 2 ? 2 : 1;
   dim3 grid((N + 15) / 16, ksplit);
-  return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
+  return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32,
+                          next_w, next_bytes);
 }
 
 // epilogue 0: y[M,N] in bfloat16 (or float when out_f32); epilogue 1: y[M,N/2] = silu(gate)*up with
 // the rows of W interleaved 8 gate rows, 8 up rows. ksplit > 1 (float output only): K is split over
 // ksplit blocks and y receives their partial sums as y[ksplit][M][ldy]; the reader adds them.
+// next_w / next_bytes (optional): weights of the product that will run next; each block asks L2 to
+// fetch a share of them, so that product finds its weights on the chip.
 SLLM_EXPORT int sllm_gemm_small_m_bf16(const void* x, const void* W, void* y, int M, int N, int K, int ldx, int ldw,
-                                       int ldy, int out_f32, int epilogue, int ksplit, cudaStream_t stream) {
+                                       int ldy, int out_f32, int epilogue, int ksplit, const void* next_w,
+                                       long long next_bytes, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return SLLM_ERR_ARG;
   if (epilogue == SM_EPI_SWIGLU && ((N & 15) || out_f32 || ksplit != 1)) return SLLM_ERR_ARG;
   if (ksplit < 1 || ksplit > 64 || (ksplit > 1 && !out_f32)) return SLLM_ERR_ARG;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
+  unsigned long long nb = (next_w != nullptr && next_bytes > 0 && ((uintptr_t)next_w & 15) == 0) ? (unsigned long long)next_bytes : 0ull;
+  if (nb == 0) next_w = nullptr;
 #define SM_CASE(NT)                                                                                                     \
-  return epilogue == SM_EPI_SWIGLU ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, stream) \
-                                   : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, stream)
+  return epilogue == SM_EPI_SWIGLU ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, next_w, nb, stream) \
+                                   : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, next_w, nb, stream)
   if (M <= 8) { SM_CASE(1); }
   if (M <= 16) { SM_CASE(2); }
   if (M <= 32) { SM_CASE(4); }

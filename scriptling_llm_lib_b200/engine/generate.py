@@ -17,6 +17,8 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Sequence as Seq
 
+import torch
+
 from ..cache.needs import PAGE
 from ..sampling.sampler import SamplingOptions
 
@@ -96,6 +98,11 @@ class BatchState:
                 ended.append(i)
         return ended
 
+    def ends_by_count(self, i: int, fed: int) -> bool:
+        """Whether sequence i ends with its next accepted token whatever that token is."""
+        s = self.seqs[i]
+        return len(s.out) + 1 >= self.max_tokens or s.held + fed + 1 > self.max_positions
+
     def cancel(self) -> list[int]:
         ended = self.live()
         for i in ended:
@@ -130,12 +137,24 @@ class Generator:
                 logits = eng.step([StepEntry(seqs[i], state.seqs[i].prompt) for i in live])
                 fed = [len(state.seqs[i].prompt) for i in live]
                 step_no = 0
+                # When the engine replays its decode step, the next step is launched with the sampled ids
+                # still on the device, before the host reads them: only a stop token can then end a
+                # sequence one step "late", and its extra row is dropped.
+                pipelined = bool(getattr(eng, "use_graphs", False)) and hasattr(eng, "decode_step_device") \
+                    and not options.penalises
                 while True:
                     recent = [state.seqs[i].prompt + state.seqs[i].out for i in live] if options.penalises else None
-                    toks = self.sampler.sample(logits, options, [seeds[i] for i in live],
-                                               [len(state.seqs[i].out) for i in live], recent).tolist()
+                    toks_dev = self.sampler.sample(logits, options, [seeds[i] for i in live],
+                                                   [len(state.seqs[i].out) for i in live], recent)
                     if step_no == 0:
                         t_ev[1].record()
+                    ahead = None
+                    if pipelined:
+                        cont = [j for j, i in enumerate(live) if not state.ends_by_count(i, fed[j])]
+                        if cont:
+                            rows = toks_dev if len(cont) == len(live) else toks_dev[torch.as_tensor(cont, device=toks_dev.device)]
+                            ahead = ([live[j] for j in cont], eng.decode_step_device([seqs[live[j]] for j in cont], rows))
+                    toks = toks_dev.tolist()
                     for i in state.accept(live, fed, toks):
                         seqs.pop(i).close()
                     if on_step is not None and on_step(step_no, {batch[i]: t for i, t in zip(live, toks)}):
@@ -144,7 +163,11 @@ class Generator:
                     live = state.live()
                     if not live:
                         break
-                    logits = eng.step([StepEntry(seqs[i], [state.seqs[i].out[-1]]) for i in live])
+                    if ahead is not None:
+                        keep = [j for j, i in enumerate(ahead[0]) if state.seqs[i].reason is None]
+                        logits = ahead[1] if len(keep) == len(ahead[0]) else ahead[1][torch.as_tensor(keep, device=ahead[1].device)]
+                    else:
+                        logits = eng.step([StepEntry(seqs[i], [state.seqs[i].out[-1]]) for i in live])
                     fed = [1] * len(live)
                     step_no += 1
                 t_ev[2].record()

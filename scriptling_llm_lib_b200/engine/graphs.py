@@ -93,14 +93,25 @@ class DecodeGraph:
             off += B * W
 
     def run(self, ids, pos0, slots, tables) -> torch.Tensor:
+        """`ids`: token ids on the host (a sequence of ints), or an int32 device tensor (the sampler's
+        output fed straight back, so that the host need not have seen the tokens yet)."""
         self.copied.synchronize()
-        self._fill_host(ids, pos0, slots, tables)
-        self.dev.copy_(self.host, non_blocking=True)
+        on_device = isinstance(ids, torch.Tensor)
+        n = ids.shape[0] if on_device else len(ids)
+        self._fill_host([0] * n if on_device else ids, pos0, slots, tables)
+        if on_device:
+            B = self.batch
+            self.dev[B:].copy_(self.host[B:], non_blocking=True)        # everything but the ids
+            self.dev[:n].copy_(ids)
+            if n < B:
+                self.dev[n:B].zero_()
+        else:
+            self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         self.graph.replay()
         from ..csrc import bindings
         bindings.LAUNCHES[0] += self.kernels_per_replay
-        return self.logits[:len(ids)]
+        return self.logits[:n]
 
 
 class DecodeGraphs:
@@ -117,7 +128,7 @@ class DecodeGraphs:
         need = max(1, max(t.shape[1] for t in tables)) if tables else 1
         cap = -(-self.engine.max_positions // PAGE)
         width = min(max(8, _next_pow2(need)), max(cap, need))
-        batch = _next_pow2(len(ids))
+        batch = _next_pow2(ids.shape[0] if isinstance(ids, torch.Tensor) else len(ids))
         key = (batch, width)
         g = self.graphs.get(key)
         if g is None:

@@ -227,6 +227,29 @@ class Engine:
         self.cache.advance(growth)
         return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
 
+    def decode_step_device(self, sequences: list[Sequence], ids: torch.Tensor) -> torch.Tensor:
+        """One token for each of `sequences`, the ids taken from an int32 device tensor (what the
+        sampler just wrote), logits of every row back. Lets a caller launch the next step before it
+        has read the last step's tokens. Only for engines that replay their decode step."""
+        if not self.use_graphs:
+            raise StepError("this engine does not replay its decode step; feed token ids from the host")
+        if ids.dtype != torch.int32 or ids.device != self.device or ids.shape[0] != len(sequences):
+            raise StepError("ids must be an int32 tensor on the engine's device, one per sequence")
+        seen = set()
+        for s in sequences:
+            if s.closed or s.engine is not self or s.slot in seen:
+                raise StepError("a sequence is closed, foreign, or named twice")
+            seen.add(s.slot)
+            if s.length + 1 > self.max_positions:
+                raise StepError(f"sequence would reach {s.length + 1} tokens; the engine holds at most {self.max_positions}")
+        growth = [(s.slot, 1) for s in sequences]
+        self.cache.reserve(growth)
+        slots = [s.slot for s in sequences]
+        tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
+        logits = self.decode_graphs.run(ids.contiguous(), [s.length for s in sequences], slots, tables)
+        self.cache.advance(growth)
+        return logits
+
     def _forward(self, ctx: StepContext, want: bool):
         """The model on the rows of `ctx`: embedding, the scheduled blocks, and for the wanted rows the
         final norm and the output head."""

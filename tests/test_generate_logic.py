@@ -126,6 +126,37 @@ def test_generator_batches_stops_and_reuses_slots():
         assert alone[0].tokens == r.tokens
 
 
+class PipelinedEngine(ScriptedEngine):
+    """An engine that can take the sampled ids from the device: the loop then launches a step before
+    it has read the last tokens."""
+    use_graphs = True
+
+    def __init__(self, n_slots):
+        super().__init__(n_slots)
+        self.device_steps = 0
+
+    def decode_step_device(self, sequences, ids):
+        self.device_steps += 1
+        from scriptling_llm_lib_b200.engine.step import StepEntry
+        return self.step([StepEntry(s, [int(t)]) for s, t in zip(sequences, ids.tolist())])
+
+
+def test_generator_pipelined_steps_give_the_same_tokens():
+    prompts = [[1, 2], [3], [6, 6, 6, 5], [2, 2], [1], [4, 4, 4], [5]]
+    for max_tokens in (1, 2, 6):
+        eng = PipelinedEngine(n_slots=3)
+        res = Generator(eng, ScriptedSampler()).generate(prompts, max_tokens=max_tokens, options=SamplingOptions())
+        for p, r in zip(prompts, res):
+            assert r.tokens == expected(p, max_tokens)
+            assert r.finish_reason == ("stop" if r.tokens[-1] == 0 else "length")
+        assert eng.opened == len(prompts) and eng.closed == len(prompts) and sorted(eng.free) == [0, 1, 2]
+        assert (eng.device_steps > 0) == (max_tokens > 1)
+    # with the repeat penalty the host needs the tokens first: no step is launched ahead
+    eng = PipelinedEngine(n_slots=3)
+    Generator(eng, ScriptedSampler()).generate(prompts, 4, SamplingOptions("temperature", repeat_penalty=1.2))
+    assert eng.device_steps == 0
+
+
 def test_generator_no_stop_ids_and_cancel():
     eng = ScriptedEngine(3)
     res = Generator(eng, ScriptedSampler()).generate([[1, 2], [5, 2]], 5, SamplingOptions(), stop_ids=())
