@@ -188,12 +188,15 @@ class TensorCoreGemm:
         return (a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
                 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def gemm(self, a, w, out, err_flag, swiglu=False):
+    def gemm(self, a, w, out, err_flag, swiglu=False, accumulate=False):
         """out[M,N] = a @ w^T in bfloat16 or float32; swiglu: out[M,N/2] = silu(gate)*up for w's rows
-        tiled 8 gate / 8 up. `err_flag` (int32 on the device) is set if a wait in the kernel timed out."""
+        tiled 8 gate / 8 up; accumulate: out (float32) += a @ w^T. `err_flag` (int32 on the device) is
+        set if a wait in the kernel timed out."""
         M, K = a.shape
         N = w.shape[0]
         want = (M, N // 2) if swiglu else (M, N)
+        if accumulate and (swiglu or out.dtype != torch.float32):
+            raise KernelError("gemm_tc accumulates into a float32 matrix only")
         if tuple(out.shape) != want or w.shape[1] != K or out.stride(1) != 1:
             raise KernelError(f"gemm_tc shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
@@ -203,7 +206,7 @@ class TensorCoreGemm:
         _check(self.lib.sllm_gemm_tc_bf16(
             c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
             c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
-            c_int(1 if swiglu else 0), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
+            c_int(2 if accumulate else (1 if swiglu else 0)), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
 
 
 class PrefillAttention:
@@ -231,7 +234,8 @@ class DecodeKernels:
 
     def __init__(self):
         self.lib = load_library("decode_bf16")
-        for n in ("sllm_gemm_small_m_bf16", "sllm_attn_decode_bf16", "sllm_attn_decode_merged_bf16"):
+        for n in ("sllm_gemm_small_m_bf16", "sllm_attn_decode_bf16", "sllm_attn_decode_merged_bf16",
+                  "sllm_attn_decode_rope_bf16"):
             getattr(self.lib, n).restype = c_int
         self.lib.sllm_attn_decode_scratch_bytes.restype = c_longlong
 
@@ -266,6 +270,25 @@ class DecodeKernels:
             c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
             c_int(1 if swiglu else 0), c_int(ksplit), c_void_p(next_w.data_ptr() if next_w is not None else 0),
             c_longlong(next_w.numel() * next_w.element_size() if next_w is not None else 0), _stream()), "gemm_small_m")
+
+    def attn_decode_rope(self, qkv, out, seq_pos0, block_table, kpages, vpages, scratch, tickets, cos_sin, rot,
+                         interleaved, write_kv, n_seqs, n_heads, n_kv, head_dim, window, scale, n_split):
+        """Rotary positions, cache write and attention of a decode step in one kernel: `qkv` holds the
+        unrotated [q | k | v] rows of the step (only q when write_kv is false)."""
+        need = self.lib.sllm_attn_decode_scratch_bytes(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_split))
+        if scratch.numel() * scratch.element_size() < need or tickets.numel() < n_seqs * n_kv:
+            raise KernelError("attn_decode_rope: scratch or tickets too small")
+        width = (n_heads + 2 * n_kv) * head_dim if write_kv else n_heads * head_dim
+        if qkv.shape[1] < width:
+            raise KernelError(f"attn_decode_rope: rows of {qkv.shape[1]} columns, need {width}")
+        _check(self.lib.sllm_attn_decode_rope_bf16(
+            _ptr(qkv, torch.bfloat16, "qkv"), c_int(qkv.shape[1]), _ptr(out, torch.bfloat16, "out"),
+            _ptr(seq_pos0, torch.int32, "seq_pos0"), _ptr(block_table, torch.int32, "block_table"),
+            c_int(block_table.shape[1]), _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"),
+            _ptr(scratch, torch.float32, "scratch"), _ptr(tickets, torch.int32, "tickets"),
+            _ptr(cos_sin, torch.float32, "cos_sin"), c_int(rot), c_int(1 if interleaved else 0), c_int(1 if write_kv else 0),
+            c_int(n_seqs), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(window or 0), c_float(scale), c_int(n_split),
+            _stream()), "attn_decode_rope")
 
     def split_for(self, n_out: int, k: int, sm_count: int) -> int:
         """Over how many blocks to split K so that a product with few output rows still fills the GPU."""

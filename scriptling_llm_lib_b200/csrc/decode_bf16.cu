@@ -160,8 +160,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
 template <int NT, int EPI>
 static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
                           int out_f32, int ksplit, const void* next_w, unsigned long long next_bytes, cudaStream_t stream) {
-  constexpr int UN = NT <= 2 ? 2 : 1;
   dim3 grid((N + 15) / 16, ksplit);
+  constexpr int UN = NT <= 2 ? 2 : 1;
   return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32,
                           next_w, next_bytes);
 }
@@ -210,9 +210,51 @@ struct AttnDecodeArgs {
   float scale;
   bf16* out;            // [B, H*HD]; written by this kernel only when `tickets` is given
   int* tickets;         // [B*G] zero before the first launch, or null: a separate kernel merges the splits
+  // raw mode (cs != null): `q` is the step's unrotated [q heads | k heads | v heads] rows; the kernel
+  // rotates the queries itself and, when write_kv is set, rotates the new key, stores it and the new
+  // value at position seq_pos0[b] of the cache and uses them -- no separate rotary kernel
+  const float2* cs;     // [positions][rot/2] (cos, sin)
+  int rot, interleaved, write_kv;
 };
 
-template <int HD, int NREP>
+// Eight consecutive dims [d0, d0+8) of a head's raw row, rotated for the position whose table row
+// is `csr`, rounded to bfloat16 as the rotary kernel would store them.
+__device__ __forceinline__ void rope8_raw(const bf16* head, int d0, int rot, int interleaved, const float2* csr, float (&out)[8]) {
+  uint4 raw = ld_dep16(head + d0);
+  const bf16* e = (const bf16*)&raw;
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) x[j] = __bfloat162float(e[j]);
+  if (d0 >= rot) {
+#pragma unroll
+    for (int j = 0; j < 8; j++) out[j] = x[j];
+    return;
+  }
+  int half = rot >> 1;
+  if (interleaved) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float2 c = csr[(d0 >> 1) + j];
+      out[2 * j] = x[2 * j] * c.x - x[2 * j + 1] * c.y;
+      out[2 * j + 1] = x[2 * j] * c.y + x[2 * j + 1] * c.x;
+    }
+  } else {
+    bool first = d0 < half;
+    uint4 praw = ld_dep16(head + (first ? d0 + half : d0 - half));
+    const bf16* pe = (const bf16*)&praw;
+    const float2* c0 = csr + (first ? d0 : d0 - half);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      float y = __bfloat162float(pe[j]);
+      float2 c = c0[j];
+      out[j] = first ? x[j] * c.x - y * c.y : y * c.y + x[j] * c.x;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) out[j] = __bfloat162float(__float2bfloat16_rn(out[j]));
+}
+
+template <int HD, int NREP, bool RAW>
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDecodeArgs p) {
   constexpr int LPK = HD / 8;        // lanes that share one key (8 dims = 16 bytes each)
   constexpr int KPW = 32 / LPK;      // keys a warp reads per load
@@ -231,26 +273,37 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
   int k_lo = max(k_begin, p0 * SLLM_PAGE), k_hi = min(pos + 1, p1 * SLLM_PAGE);
   const int* bt = p.block_table + (size_t)b * p.max_pages;
   int nrep = p.H / p.G;
+  // raw mode: the key at the query's own position is not in the cache yet; the block whose range
+  // holds it takes it from the step's raw row after the cached keys
+  const bool has_new = RAW && p.write_kv && pos >= k_lo && pos < k_hi;
+  const int k_end = has_new ? pos : k_hi;
 
   for (int r0 = 0; r0 < nrep; r0 += NREP) {
     float q[NREP][8], acc[NREP][8], m[NREP], l[NREP];
 #pragma unroll
     for (int r = 0; r < NREP; r++) {
       int h = g * nrep + r0 + r;
-      uint4 raw = ld_dep16(p.q + (size_t)b * p.q_ld + (size_t)h * HD + dl);
-      const bf16* e = (const bf16*)&raw;
+      if (RAW) {
+        float qr[8];
+        rope8_raw(p.q + (size_t)b * p.q_ld + (size_t)h * HD, dl, p.rot, p.interleaved, p.cs + (size_t)pos * (p.rot >> 1), qr);
 #pragma unroll
-      for (int j = 0; j < 8; j++) { q[r][j] = __bfloat162float(e[j]) * (p.scale * AD_LOG2E); acc[r][j] = 0.f; }
+        for (int j = 0; j < 8; j++) { q[r][j] = qr[j] * (p.scale * AD_LOG2E); acc[r][j] = 0.f; }
+      } else {
+        uint4 raw = ld_dep16(p.q + (size_t)b * p.q_ld + (size_t)h * HD + dl);
+        const bf16* e = (const bf16*)&raw;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { q[r][j] = __bfloat162float(e[j]) * (p.scale * AD_LOG2E); acc[r][j] = 0.f; }
+      }
       m[r] = -INFINITY;
       l[r] = 0.f;
     }
-    for (int kb = k_lo + warp * KPW * AD_UN; kb < k_hi; kb += AD_WARPS * KPW * AD_UN) {
+    for (int kb = k_lo + warp * KPW * AD_UN; kb < k_end; kb += AD_WARPS * KPW * AD_UN) {
       uint4 kr[AD_UN], vr[AD_UN];
       bool ok[AD_UN];
 #pragma unroll
       for (int u = 0; u < AD_UN; u++) {
         int key = kb + u * KPW + slot;
-        ok[u] = key < k_hi;
+        ok[u] = key < k_end;
         int kk = ok[u] ? key : k_lo;
         int page = bt[kk / SLLM_PAGE];
         size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * HD + dl;
@@ -294,6 +347,45 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
           for (int j = 0; j < 8; j++) acc[r][j] = fmaf(pr, __bfloat162float(ve[j]), acc[r][j]);
         }
         l[r] = lsum;
+      }
+    }
+    if (has_new) {
+      // this step's own key and value: rotate, round, store at their place in the cache, use
+      bool mine = warp == 0 && slot == 0;
+      float kn[8], vn[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) kn[j] = vn[j] = 0.f;
+      if (mine) {
+        const bf16* rowp = p.q + (size_t)b * p.q_ld;
+        rope8_raw(rowp + (size_t)(p.H + g) * HD, dl, p.rot, p.interleaved, p.cs + (size_t)pos * (p.rot >> 1), kn);
+        uint4 vraw = ld_dep16(rowp + (size_t)(p.H + p.G + g) * HD + dl);
+        const bf16* ve = (const bf16*)&vraw;
+#pragma unroll
+        for (int j = 0; j < 8; j++) vn[j] = __bfloat162float(ve[j]);
+        if (r0 == 0) {
+          size_t off = (((size_t)bt[pos / SLLM_PAGE] * p.G + g) * SLLM_PAGE + (pos % SLLM_PAGE)) * HD + dl;
+          uint4 kraw;
+          __nv_bfloat162* kp2 = (__nv_bfloat162*)&kraw;
+#pragma unroll
+          for (int j = 0; j < 4; j++) kp2[j] = __floats2bfloat162_rn(kn[2 * j], kn[2 * j + 1]);
+          *(uint4*)(const_cast<bf16*>(p.kpages) + off) = kraw;
+          *(uint4*)(const_cast<bf16*>(p.vpages) + off) = vraw;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < NREP; r++) {
+        float d = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) d = fmaf(q[r][j], kn[j], d);
+#pragma unroll
+        for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (!mine) continue;
+        float m_new = fmaxf(m[r], d);
+        float corr = exp2f(m[r] - m_new), pr = exp2f(d - m_new);
+        m[r] = m_new;
+        l[r] = l[r] * corr + pr;
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[r][j] = fmaf(pr, vn[j], acc[r][j] * corr);
       }
     }
     // merge the key slots of the warp, then the warps
@@ -397,9 +489,15 @@ static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStr
   dim3 grid(a.n_split, a.G, B);
   int nrep = a.H / a.G;
   cudaError_t e;
-  if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-  else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-  else e = sllm_launch(attn_decode_split_kernel<HD, 1>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+  if (a.cs != nullptr) {
+    if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else e = sllm_launch(attn_decode_split_kernel<HD, 1, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+  } else {
+    if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else e = sllm_launch(attn_decode_split_kernel<HD, 1, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+  }
   if (e != cudaSuccess || a.tickets != nullptr) return (int)e;
   return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD < 32 ? 32 : HD), 0, stream,
                           (const float*)a.part, out, a.H, HD, a.n_split);
@@ -412,11 +510,14 @@ SLLM_EXPORT long long sllm_attn_decode_scratch_bytes(int B, int H, int hd, int n
 
 static int attn_decode_dispatch(const void* q, int q_ld, void* out, const int* seq_pos0, const int* block_table,
                                 int max_pages, const void* kpages, const void* vpages, void* scratch, int* tickets, int B,
-                                int H, int G, int hd, int window, float scale, int n_split, cudaStream_t stream) {
+                                int H, int G, int hd, int window, float scale, int n_split, cudaStream_t stream,
+                                const void* cos_sin = nullptr, int rot = 0, int interleaved = 0, int write_kv = 0) {
   if (B <= 0) return 0;
   if (G < 1 || H % G != 0 || n_split < 1 || (q_ld & 7) || ((uintptr_t)q & 15)) return SLLM_ERR_ARG;
+  if (cos_sin != nullptr && (rot < 2 || rot > hd || (rot % (interleaved ? 8 : 16)) != 0 || tickets == nullptr)) return SLLM_ERR_ARG;
   AttnDecodeArgs a{(const bf16*)q, q_ld, seq_pos0, block_table, max_pages, (const bf16*)kpages, (const bf16*)vpages,
-                   (float*)scratch, H, G, window, n_split, scale, (bf16*)out, tickets};
+                   (float*)scratch, H, G, window, n_split, scale, (bf16*)out, tickets, (const float2*)cos_sin, rot, interleaved,
+                   write_kv};
   switch (hd) {
     case 16: return attn_decode_launch<16>(a, (bf16*)out, B, stream);
     case 32: return attn_decode_launch<32>(a, (bf16*)out, B, stream);
@@ -444,6 +545,19 @@ SLLM_EXPORT int sllm_attn_decode_merged_bf16(const void* q, int q_ld, void* out,
   if (tickets == nullptr) return SLLM_ERR_ARG;
   return attn_decode_dispatch(q, q_ld, out, seq_pos0, block_table, max_pages, kpages, vpages, scratch, tickets, B, H, G, hd,
                               window, scale, n_split, stream);
+}
+
+// Rotary positions, cache write and attention of a decode step in one kernel: `qkv` holds the
+// step's unrotated rows [q heads | k heads | v heads]; the queries are rotated on the fly, and with
+// write_kv the new key (rotated) and value are stored at position seq_pos0[b] by the block whose key
+// range holds that position. Rotary width in multiples of 16 (half pairing) or 8 (interleaved).
+SLLM_EXPORT int sllm_attn_decode_rope_bf16(const void* qkv, int ld, void* out, const int* seq_pos0, const int* block_table,
+                                           int max_pages, void* kpages, void* vpages, void* scratch, int* tickets,
+                                           const void* cos_sin, int rot, int interleaved, int write_kv, int B, int H, int G,
+                                           int hd, int window, float scale, int n_split, cudaStream_t stream) {
+  if (tickets == nullptr || cos_sin == nullptr) return SLLM_ERR_ARG;
+  return attn_decode_dispatch(qkv, ld, out, seq_pos0, block_table, max_pages, kpages, vpages, scratch, tickets, B, H, G, hd,
+                              window, scale, n_split, stream, cos_sin, rot, interleaved, write_kv);
 }
 
 // ------------------------------------------------------------------ decode attention without any allocation

@@ -24,6 +24,7 @@
 
 #define TC_EPI_STORE 0
 #define TC_EPI_SWIGLU 1
+#define TC_EPI_RESIDUAL 2   // C is the float residual stream: C += A B^T
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -105,7 +106,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2).
 template <int EPI>
 __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, int ldc, int out_f32, const uint32_t (&r)[32]) {
-  if (EPI == TC_EPI_STORE) {
+  if (EPI == TC_EPI_RESIDUAL) {
+    float* dst = (float*)C + (size_t)row * ldc + col;
+    if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 v = *(float4*)(dst + j);
+        v.x += __uint_as_float(r[j]); v.y += __uint_as_float(r[j + 1]); v.z += __uint_as_float(r[j + 2]); v.w += __uint_as_float(r[j + 3]);
+        *(float4*)(dst + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++) if (col + j < N) dst[j] += __uint_as_float(r[j]);
+    }
+  } else if (EPI == TC_EPI_STORE) {
     if (out_f32) {
       float* dst = (float*)C + (size_t)row * ldc + col;
       if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
@@ -331,7 +345,8 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int 
 }
 
 // C[M,N] = A[M,K] B[N,K]^T. epilogue 0: C bfloat16 (or float when out_f32), row stride ldc;
-// epilogue 1: C[M,N/2] = silu(gate) * up for B's rows in tiles of 16 (8 gate rows, 8 up rows).
+// epilogue 1: C[M,N/2] = silu(gate) * up for B's rows in tiles of 16 (8 gate rows, 8 up rows);
+// epilogue 2: C is a float matrix and the product is added to it (the residual sum).
 // *err is set to 2 if a wait inside the kernel ran out of time.
 SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                                   int out_f32, int epilogue, int* err, cudaStream_t stream) {
@@ -344,6 +359,9 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
   if (rc) return rc;
   rc = make_map(&mb, B, N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
+  if (epilogue == TC_EPI_RESIDUAL)
+    return big ? tc_launch<256, 4, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream)
+               : tc_launch<128, 6, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream);
   if (epilogue == TC_EPI_SWIGLU)
     return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream)
                : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);

@@ -53,20 +53,28 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, unit, writes):
         kpages, vpages, block_table = ctx.unit_kv(unit)
-        if writes:
-            qkv = self.qkv.forward(x, ctx)
-            self.position.apply(qkv, ctx, self.n_heads, self.n_kv_heads, kpages, vpages, block_table)
-        else:
-            qkv = self.q_only.forward(x, ctx)
-            self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
+        fast_decode = ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
+        fusion = getattr(self.position, "decode_fusion", lambda: None)() if fast_decode else None
+        qkv = (self.qkv if writes else self.q_only).forward(x, ctx)
+        if fusion is None:
+            if writes:
+                self.position.apply(qkv, ctx, self.n_heads, self.n_kv_heads, kpages, vpages, block_table)
+            else:
+                self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
         attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
-        if ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS:
+        if fast_decode:
             n_split = ctx.decode_splits(self.n_kv_heads)
             scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                   device=x.device)
-            ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
-                                           self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split,
-                                           tickets=ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads))
+            tickets = ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads)
+            if fusion is not None:      # rotation and cache write happen inside the attention kernel
+                ctx.kernels.decode.attn_decode_rope(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, tickets,
+                                                    fusion[0], fusion[1], fusion[2], writes, ctx.n_seqs, self.n_heads,
+                                                    self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
+            else:
+                ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
+                                               self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale,
+                                               n_split, tickets=tickets)
         elif x.dtype == torch.bfloat16 and self.head_dim in PrefillAttention.HEAD_DIMS:
             ctx.kernels.prefill_attention.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
                                                ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,

@@ -58,6 +58,14 @@ class RotaryEncoding(PositionEncoding):
     def max_positions(self) -> int:
         return 0 if self.cos_sin is None else self.cos_sin.shape[0]
 
+    def decode_fusion(self):
+        """(table, rotary width, interleaved) when the decode attention kernel can rotate by itself
+        (its 16-byte vectors must not straddle the rotary width or its half), else None."""
+        interleaved = self.pairing == "interleaved"
+        if self.cos_sin is None or self.rotary_dim % (8 if interleaved else 16):
+            return None
+        return self.cos_sin, self.rotary_dim, interleaved
+
     def apply(self, qkv, ctx, n_heads: int, n_kv: int, kpages, vpages, block_table) -> None:
         """Rotate the q heads of `qkv` in place; rotate its k heads and store them with the v heads at
         each token's place in the cache (n_kv == 0: queries only)."""

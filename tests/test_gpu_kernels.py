@@ -126,6 +126,34 @@ def test_gemm_small_m(kernel_sets, M, N, K):
         assert rel_err(h.cpu().float(), plain.swiglu(want[:, :F], want[:, F:])) < TOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("M, N, K", [(128, 128, 64), (100, 200, 72), (130, 264, 520), (2048, 2048, 2048), (65, 1003 * 8, 136),
+                                     (300, 96, 8192)])
+def test_gemm_tensor_core(kernel_sets, M, N, K):
+    """The tcgen05 GEMM: bfloat16 and float outputs, the SiLU-gate epilogue, accumulation into a float matrix."""
+    tc = kernel_sets[torch.bfloat16].tensor_core
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a, w = dev(rand(M, K, seed=14), torch.bfloat16), dev(rand(N, K, seed=15, scale=0.05), torch.bfloat16)
+    assert tc.takes(a, w)
+    want = plain.linear(f64(a), f64(w))
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    tc.gemm(a, w, out, err)
+    assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    tc.gemm(a, w, out32, err)
+    assert rel_err(out32.cpu(), want) < 3e-5              # tensor-core accumulation over long K
+    base = dev(rand(M, N, seed=16))
+    acc = base.clone()
+    tc.gemm(a, w, acc, err, accumulate=True)
+    assert rel_err(acc.cpu(), f64(base) + want) < 3e-5
+    if N % 16 == 0:
+        F = N // 2
+        tiled = w.view(2, F // 8, 8, K).permute(1, 0, 2, 3).reshape(N, K).contiguous()
+        h = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+        tc.gemm(a, tiled, h, err, swiglu=True)
+        assert rel_err(h.cpu().float(), plain.swiglu(want[:, :F], want[:, F:])) < TOL[torch.bfloat16]
+    assert int(err) == 0
+
+
 def test_gemm_small_m_refuses_what_it_cannot_take(kernel_sets):
     from scriptling_llm_lib_b200.csrc.bindings import KernelError
     dk = kernel_sets[torch.bfloat16].decode
@@ -296,6 +324,55 @@ def test_attn_decode(kernel_sets, H, G, hd, window, n_split):
                        tickets=tickets)
         assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
         assert int(tickets.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("H, G, hd, rot, pairing, window", [(4, 2, 16, 16, "half", None), (3, 1, 32, 16, "interleaved", None),
+                                                            (32, 32, 64, 64, "half", None), (8, 2, 128, 64, "half", 300),
+                                                            (4, 4, 64, 8, "interleaved", 65)])
+@pytest.mark.parametrize("n_split", [1, 5])
+def test_attn_decode_with_rotation_and_cache_write_fused(kernel_sets, H, G, hd, rot, pairing, window, n_split):
+    """One kernel does what rope_kv_write + attn_decode do: rotate q, rotate and store the new key,
+    store the new value, attend. Checked against the plain functions, and the cache afterwards."""
+    from scriptling_llm_lib_b200.parts.rotary import RotaryEncoding
+    dk = kernel_sets[torch.bfloat16].decode
+    enc = RotaryEncoding(hd, rot, 54321.0, None, pairing)
+    enc.prepare(1024, "cuda")
+    assert enc.decode_fusion() is not None
+    pos0 = [0, 63, 64, 700, 257]
+    B = len(pos0)
+    rnd = lambda t: t.bfloat16().float()
+    old_k = [rnd(rand(p, G, hd, seed=90 + b)) for b, p in enumerate(pos0)]           # cached (already rotated) keys
+    old_v = [rnd(rand(p, G, hd, seed=95 + b)) for b, p in enumerate(pos0)]
+    raw = rnd(rand(B, (H + 2 * G) * hd, seed=99, scale=1.5))                         # this step's unrotated q | k | v
+    inv = plain.rope_inv_freq(rot, 54321.0)
+    q_rot, k_new, v_new = [], [], []
+    for b, p in enumerate(pos0):
+        pos = torch.tensor([p])
+        q_rot.append(rnd(plain.apply_rope(f64(raw[b:b + 1, :H * hd]).view(1, H, hd), pos, inv, pairing).float()))
+        k_new.append(rnd(plain.apply_rope(f64(raw[b:b + 1, H * hd:(H + G) * hd]).view(1, G, hd), pos, inv, pairing).float()))
+        v_new.append(raw[b:b + 1, (H + G) * hd:].view(1, G, hd))
+    want = torch.cat([plain.attention(f64(q_rot[b]), f64(torch.cat([old_k[b], k_new[b]])), f64(torch.cat([old_v[b], v_new[b]])),
+                                      torch.tensor([pos0[b]]), torch.arange(pos0[b] + 1), window).reshape(1, -1) for b in range(B)])
+    # pages sized for pos0 + 1 keys; the new key's place holds NaN until the kernel writes it
+    nan_row = torch.full((1, G, hd), float("nan"))
+    kp, vp, bt = paged([torch.cat([old_k[b], nan_row]) for b in range(B)], [torch.cat([old_v[b], nan_row]) for b in range(B)],
+                       [p + 1 for p in pos0], dtype=torch.bfloat16)
+    out = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.full((B * H * n_split * (hd + 2),), float("nan"), dtype=torch.float32, device="cuda")
+    tickets = torch.zeros(B * G, dtype=torch.int32, device="cuda")
+    dk.attn_decode_rope(dev(raw, torch.bfloat16), out, dev(pos0, torch.int32), bt, kp, vp, scratch, tickets, enc.cos_sin, rot,
+                        pairing == "interleaved", True, B, H, G, hd, window, 1.0 / math.sqrt(hd), n_split)
+    assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+    assert int(tickets.abs().sum()) == 0
+    for b, p in enumerate(pos0):
+        pg = int(bt[b, p // PAGE])
+        assert rel_err(f64(kp[pg, :, p % PAGE]), f64(k_new[b][0])) < TOL[torch.bfloat16]
+        assert torch.equal(f64(vp[pg, :, p % PAGE]), f64(v_new[b][0]))
+    # a layer that reads another layer's cache: queries only, the key at the query's position is read, not written
+    out2 = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dk.attn_decode_rope(dev(raw[:, :H * hd], torch.bfloat16), out2, dev(pos0, torch.int32), bt, kp, vp, scratch, tickets,
+                        enc.cos_sin, rot, pairing == "interleaved", False, B, H, G, hd, window, 1.0 / math.sqrt(hd), n_split)
+    assert rel_err(out2.cpu().float(), want) < TOL[torch.bfloat16]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
