@@ -103,10 +103,6 @@ class KernelSet:
                                        c_int(1 if weight.dtype == torch.float32 else 0), _ptr(y, self.dtype, "y"),
                                        c_int(n), c_int(d), c_float(eps), _stream()), "add_rmsnorm")
 
-    def residual_add(self, x, delta):
-        _check(self._fn("residual_add")(_ptr(x, torch.float32, "x"), _ptr(delta, self.dtype, "delta"),
-                                        c_longlong(delta.numel()), _stream()), "residual_add")
-
     # ------------------------------------------------------------------ matrix products
     def gemm_nt(self, a, w, out):
         """out[M,N] = a[M,K] @ w[N,K]^T; `out` is of this set's dtype or float32."""
@@ -251,7 +247,7 @@ class DecodeKernels:
         only while the output is too narrow to give the 128 x 256 tensor-core tiles enough blocks."""
         return DecodeKernels.takes(a, w) and (a.shape[0] <= 16 or w.shape[0] < 12288)
 
-    def gemm_small_m(self, a, w, out, swiglu=False, next_w=None):
+    def gemm_small_m(self, a, w, out, swiglu=False):
         """out[M,N] = a @ w^T (bfloat16 or float32 out); swiglu: out[M,N/2] = silu(gate)*up for w rows
         tiled 8 gate / 8 up; out float32 [P,M,N]: K split P ways, out receives the partial sums."""
         M, K = a.shape
@@ -268,8 +264,7 @@ class DecodeKernels:
             _ptr(a, torch.bfloat16, "a") if a.is_contiguous() else c_void_p(a.data_ptr()),
             _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
             c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
-            c_int(1 if swiglu else 0), c_int(ksplit), c_void_p(next_w.data_ptr() if next_w is not None else 0),
-            c_longlong(next_w.numel() * next_w.element_size() if next_w is not None else 0), _stream()), "gemm_small_m")
+            c_int(1 if swiglu else 0), c_int(ksplit), _stream()), "gemm_small_m")
 
     def attn_decode_rope(self, qkv, out, seq_pos0, block_table, kpages, vpages, scratch, tickets, cos_sin, rot,
                          interleaved, write_kv, n_seqs, n_heads, n_kv, head_dim, window, scale, n_split):

@@ -2,17 +2,24 @@
 // bytes it must read once -- the weights, and the cached keys and values of the live sequences.
 //
 //   gemm_small_m: y[M,N] = x[M,K] W[N,K]^T for a few rows M. Each weight element is loaded from
-//     HBM exactly once (16-byte loads straight into tensor-core fragments, no shared memory); the
-//     weights are the 16-row operand of mma.sync.m16n8k16 and the tokens its 8 columns, float
-//     accumulation. The warps of a block split K and add their partial sums in a fixed order.
-//     Replaces the reference's row matmul for one token (float32_ops.go:779-794) and its dense
-//     matmul for a few (float32_ops.go:462-482). An epilogue can apply the SiLU gate
-//     (model_f32.go:484-490) when gate and up rows are interleaved 8 and 8.
+//     HBM exactly once (16-byte loads straight into tensor-core fragments, no shared memory, two
+//     register buffers used in turn so the next chunks are in flight while the current ones are
+//     multiplied); the weights are the 16-row operand of mma.sync.m16n8k16 and the tokens its 8
+//     columns, float accumulation. The warps of a block split K and add their partial sums in a
+//     fixed order; several blocks may split K further and leave float partial sums for the reader
+//     (the next norm) to add. Replaces the reference's row matmul for one token
+//     (float32_ops.go:779-794) and its dense matmul for a few (float32_ops.go:462-482). An epilogue
+//     can apply the SiLU gate (model_f32.go:484-490) when gate and up rows are interleaved 8 and 8.
 //   attn_decode: grouped-query attention of one query per sequence over the paged cache, keys
 //     split over blocks (each block streams a contiguous run of pages once and serves all query
-//     heads of its key/value head), online softmax in float, partial results merged by a second
-//     small kernel. Same mathematics as fusedAttentionHeadF32 with one query row
+//     heads of its key/value head), online softmax in float. The last block of a (sequence, head
+//     group) to finish merges the splits. In raw mode the kernel also does the rotary step
+//     (float32_ops.go:174-188) for the queries and the new key and appends key and value to the
+//     cache (model_f32.go:445-448). Same mathematics as fusedAttentionHeadF32 with one query row
 //     (float32_ops.go:190-235).
+//
+// All kernels here are launched with programmatic stream serialisation (see common.cuh): they may
+// start while the previous kernel drains, and wait before touching what it wrote.
 #include "common.cuh"
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
@@ -39,22 +46,9 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 template <int NT, int WARPS, int EPI, int UN>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ y, int M, int N, int K,
-                    int ldx, int ldw, int ldy, int out_f32, const void* next_w, unsigned long long next_bytes) {
+                    int ldx, int ldw, int ldy, int out_f32) {
   __shared__ float red[WARPS][NT][4][32];
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  if (next_w != nullptr && threadIdx.x == 0) {
-    // ask L2 for this block's share of the weights the next product will stream
-    unsigned long long blocks = (unsigned long long)gridDim.x * gridDim.y, id = blockIdx.y * (unsigned long long)gridDim.x + blockIdx.x;
-    unsigned long long per = ((next_bytes + blocks - 1) / blocks + 127ull) & ~127ull;
-    unsigned long long off = id * per;
-    while (off < next_bytes && per > 0) {
-      unsigned long long n = min(min(per, next_bytes - off), 8192ull) & ~15ull;
-      if (n == 0) break;
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)next_w + off), "r"((unsigned)n) : "memory");
-      off += n;
-      per -= n;
-    }
-  }
   int n0 = blockIdx.x * 16;
   const bf16* w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
   const bf16* w1 = W + (size_t)min(n0 + g + 8, N - 1) * ldw;
@@ -159,32 +153,26 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
 
 template <int NT, int EPI>
 static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
-                          int out_f32, int ksplit, const void* next_w, unsigned long long next_bytes, cudaStream_t stream) {
+                          int out_f32, int ksplit, cudaStream_t stream) {
   dim3 grid((N + 15) / 16, ksplit);
   constexpr int UN = NT <= 2 ? 2 : 1;
-  return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32,
-                          next_w, next_bytes);
+  return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
 }
 
 // epilogue 0: y[M,N] in bfloat16 (or float when out_f32); epilogue 1: y[M,N/2] = silu(gate)*up with
 // the rows of W interleaved 8 gate rows, 8 up rows. ksplit > 1 (float output only): K is split over
 // ksplit blocks and y receives their partial sums as y[ksplit][M][ldy]; the reader adds them.
-// next_w / next_bytes (optional): weights of the product that will run next; each block asks L2 to
-// fetch a share of them, so that product finds its weights on the chip.
 SLLM_EXPORT int sllm_gemm_small_m_bf16(const void* x, const void* W, void* y, int M, int N, int K, int ldx, int ldw,
-                                       int ldy, int out_f32, int epilogue, int ksplit, const void* next_w,
-                                       long long next_bytes, cudaStream_t stream) {
+                                       int ldy, int out_f32, int epilogue, int ksplit, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return SLLM_ERR_ARG;
   if (epilogue == SM_EPI_SWIGLU && ((N & 15) || out_f32 || ksplit != 1)) return SLLM_ERR_ARG;
   if (ksplit < 1 || ksplit > 64 || (ksplit > 1 && !out_f32)) return SLLM_ERR_ARG;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-  unsigned long long nb = (next_w != nullptr && next_bytes > 0 && ((uintptr_t)next_w & 15) == 0) ? (unsigned long long)next_bytes : 0ull;
-  if (nb == 0) next_w = nullptr;
 #define SM_CASE(NT)                                                                                                     \
-  return epilogue == SM_EPI_SWIGLU ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, next_w, nb, stream) \
-                                   : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, next_w, nb, stream)
+  return epilogue == SM_EPI_SWIGLU ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, stream) \
+                                   : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, stream)
   if (M <= 8) { SM_CASE(1); }
   if (M <= 16) { SM_CASE(2); }
   if (M <= 32) { SM_CASE(4); }

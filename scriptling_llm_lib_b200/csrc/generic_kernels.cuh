@@ -97,13 +97,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
   }
 }
 
-// x[row] += delta[row] only (a block arrangement that ends without a norm needs it).
-template <typename A>
-__global__ void residual_add_kernel(float* __restrict__ x, const A* __restrict__ delta, size_t n) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) x[i] += to_f32(delta[i]);
-}
-
 // ------------------------------------------------------------------ C = A * B^T, tiled, FP32 FMA
 // A [M,K] (row stride lda), B [N,K] (row stride ldb: weights are [out, in]), C [M,N].
 // Each output is one ascending-k chain of fused multiply-adds in float.
