@@ -22,6 +22,7 @@ VERSION = "0.1.0"
 
 _models: dict[tuple[str, str, str], tuple[Engine, Sampler]] = {}
 _models_lock = threading.Lock()
+_run_locks: dict[int, threading.Lock] = {}      # one generation at a time per engine (its cache and graphs are shared)
 
 
 def load(model_dir, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096, max_seqs: int | None = None):
@@ -38,6 +39,7 @@ def unload(model_dir=None) -> None:
     """Drop one cached model, or all of them."""
     with _models_lock:
         for key in [k for k in _models if model_dir is None or k[0] == os.path.realpath(str(model_dir))]:
+            _run_locks.pop(id(_models[key][0]), None)
             del _models[key]
 
 
@@ -75,8 +77,11 @@ def generate(model_dir, prompt_ids, max_tokens: int = 100, strategy: str = "gree
     options = SamplingOptions(strategy, float(temperature), int(top_k), float(top_p), float(repeat_penalty),
                               int(repeat_last_n))
     eng, sampler = load(model_dir, dtype, device)
-    _fit_cache(eng, prompts, max_tokens, max_batch)
-    results = Generator(eng, sampler).generate(prompts, max_tokens, options, stop_ids, seed, max_batch, on_step)
+    with _models_lock:
+        run_lock = _run_locks.setdefault(id(eng), threading.Lock())
+    with run_lock:      # concurrent callers of one model take turns (the reference gives each a clone; here they share a cache)
+        _fit_cache(eng, prompts, max_tokens, max_batch)
+        results = Generator(eng, sampler).generate(prompts, max_tokens, options, stop_ids, seed, max_batch, on_step)
     ids = [r.tokens for r in results]
     if not stats:
         return ids[0] if single else ids
