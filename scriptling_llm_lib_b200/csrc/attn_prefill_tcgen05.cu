@@ -1,0 +1,312 @@
+// Causal grouped-query attention of a prompt step over the paged cache on tcgen05 tensor cores
+// (bfloat16, head width 64).
+//
+// One block: 128 consecutive queries of one sequence and one query head. Warp 0 fetches the query
+// tile and, page by page, the keys and values of the sequence with TMA (128-byte swizzle, no
+// multicast) -- the pages are found through the block table, this step's own keys were written
+// to the cache before. Warp 1 issues the products from one thread: S = Q K^T (128 x 64, float, in
+// tensor memory, two buffers) and O += P V (128 x 64). Warps 2-5 are the softmax:
+// thread = query row = tensor-memory lane, so a row's maximum and sum need no shuffles. They read a
+// row of S, keep a reference maximum and the running sum (base 2, scale folded into one FFMA) and
+// write the probabilities as bfloat16 into shared memory in the swizzled operand layout. O stays in
+// tensor memory and is accumulated by the tensor core itself; the softmax threads rescale it (read,
+// multiply, write back) only when a row's maximum has grown by more than 2^8 since its reference
+// was set -- probabilities then stay below 2^8, and the final division by the row sum makes the
+// result the same as with an exact running maximum (float32_ops.go:190-235; key j is seen by the
+// query at position p when j <= p, and with a window only when j > p - window). The hand-over
+// between the three roles is by mbarriers; every wait is bounded (2 s), after which the kernel
+// raises *err, drains its own TMA copies, frees its tensor memory and returns.
+#include "tcgen05.cuh"
+
+#define FT_BQ 128
+#define FT_BK 64           // = SLLM_PAGE
+#define FT_HD 64
+#define FT_STAGES 3
+#define FT_THREADS 192       // warp 0: TMA, warp 1: MMA, warps 2-5: softmax (thread = query row)
+#define FT_LOG2E 1.4426950408889634f
+
+struct FtArgs {
+  bf16* out;            // [T, H*64]
+  const int* seq_start; // [B+1]
+  const int* seq_pos0;  // [B]
+  const int* block_table;
+  int max_pages;
+  int H, G, window;
+  float scale;
+  int* err;
+};
+
+__device__ __forceinline__ float ft_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(FT_THREADS, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, FtArgs p) {
+  constexpr uint32_t Q_BYTES = FT_BQ * FT_HD * 2, KV_BYTES = FT_BK * FT_HD * 2, P_BYTES = FT_BQ * FT_BK * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // [Q][P][K stages][V stages][barriers]
+  const uint32_t sQ = smem_u32(smem), sP = sQ + Q_BYTES, sK = sP + P_BYTES, sV = sK + FT_STAGES * KV_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + P_BYTES + 2 * FT_STAGES * KV_BYTES);
+  // q_full, kv_full[ST], kv_empty[ST], s_full[2], s_empty[2], p_full, p_empty, o_full
+  const uint32_t b_qfull = smem_u32(bars), b_kvfull = b_qfull + 8, b_kvempty = b_kvfull + 8 * FT_STAGES,
+                 b_sfull = b_kvempty + 8 * FT_STAGES, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16, b_pempty = b_pfull + 8,
+                 b_ofull = b_pempty + 8;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 1 + 1 + 1);
+  volatile int* abort = (volatile int*)(tmem_slot + 1);
+
+  int b = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;     // long tiles first
+  int row0 = p.seq_start[b], S = p.seq_start[b + 1] - row0;
+  int r0 = qt * FT_BQ;
+  if (r0 >= S) return;
+  int nq = min(FT_BQ, S - r0);
+  int pos0 = p.seq_pos0[b];
+  int g = h / (p.H / p.G);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* bt = p.block_table + (size_t)b * p.max_pages;
+  int q_lo = pos0 + r0, q_hi = pos0 + r0 + nq - 1;
+  int k_first = p.window > 0 ? max(0, q_lo - p.window + 1) : 0;
+  int t_lo = k_first / FT_BK, t_hi = q_hi / FT_BK, n_tiles = t_hi - t_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_qfull, 1);
+    for (int s = 0; s < FT_STAGES; s++) { mbar_init(b_kvfull + 8 * s, 1); mbar_init(b_kvempty + 8 * s, 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(b_sfull + 8 * a, 1); mbar_init(b_sempty + 8 * a, 4); }
+    mbar_init(b_pfull, 4);
+    mbar_init(b_pempty, 1);
+    mbar_init(b_ofull, 1);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;          // columns: S0 0-63, S1 64-127, O 128-191
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(b_qfull, Q_BYTES);
+      tma_load_2d(sQ, &map_q, h * FT_HD, row0 + r0, b_qfull);
+      int issued = 0;
+      for (int j = 0; j < n_tiles; j++) {
+        int s = j % FT_STAGES;
+        if (!mbar_wait(b_kvempty + 8 * s, ((j / FT_STAGES) & 1) ^ 1, abort)) break;
+        int page = bt[t_lo + j];
+        int krow = (page * p.G + g) * FT_BK;
+        mbar_expect_tx(b_kvfull + 8 * s, 2 * KV_BYTES);
+        tma_load_2d(sK + s * KV_BYTES, &map_k, 0, krow, b_kvfull + 8 * s);
+        tma_load_2d(sV + s * KV_BYTES, &map_v, 0, krow, b_kvfull + 8 * s);
+        issued = j + 1;
+      }
+      if (*abort) {
+        volatile int never = 0;
+        mbar_wait(b_qfull, 0, &never);
+        for (int j = max(0, issued - FT_STAGES); j < issued; j++) mbar_wait(b_kvfull + 8 * (j % FT_STAGES), (j / FT_STAGES) & 1, &never);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(FT_BQ, FT_BK);          // S = Q K^T: both K-major
+      constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(FT_BQ, FT_HD);      // O = P V: V is MN-major (dims contiguous)
+      bool ok = mbar_wait(b_qfull, 0, abort);
+      auto issue_s = [&](int j) -> bool {
+        int s = j % FT_STAGES, a = j & 1;
+        if (!mbar_wait(b_kvfull + 8 * s, (j / FT_STAGES) & 1, abort)) return false;
+        if (!mbar_wait(b_sempty + 8 * a, ((j >> 1) & 1) ^ 1, abort)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < FT_HD / 16; k++)
+          umma_bf16(tmem_base + a * 64, umma_desc_sw128(sQ + k * 32), umma_desc_sw128(sK + s * KV_BYTES + k * 32), idesc_s, k ? 1u : 0u);
+        umma_commit(b_sfull + 8 * a);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; j++) {
+        if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
+        int s = j % FT_STAGES;
+        ok = mbar_wait(b_pfull, j & 1, abort);        // P of tile j is written, and O has been rescaled if it had to be
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < FT_BK / 16; k++)
+          umma_bf16(tmem_base + 128, umma_desc_sw128(sP + k * 32), umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, 0),
+                    idesc_o, (j | k) ? 1u : 0u);
+        umma_commit(b_ofull);
+        umma_commit(b_kvempty + 8 * s);
+        umma_commit(b_pempty);
+      }
+    }
+  } else {
+    const int q = warp & 3;                        // tensor-memory quarter of this warp
+    const int r = q * 32 + lane;                   // query row of this thread in the tile
+    const int qpos = pos0 + r0 + r;
+    const float sc = p.scale * FT_LOG2E;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+    float m_ref = -INFINITY, l = 0.f;              // reference maximum (raw score units) and sum relative to it
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; j++) {
+      int a = j & 1, t = t_lo + j;
+      ok = mbar_wait(b_sfull + 8 * a, (j >> 1) & 1, abort);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t s0[32], s1[32];
+      tmem_ld32(t_lane + a * 64, s0);
+      tmem_ld32(t_lane + a * 64 + 32, s1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_sempty + 8 * a);
+      // ---- mask, row maximum (raw scores; four independent chains)
+      bool need_mask = (t * FT_BK + FT_BK - 1 > qpos) || (p.window > 0 && t * FT_BK <= qpos - p.window);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          int k0 = t * FT_BK + i, k1 = k0 + 32;
+          if (!(k0 <= qpos && (p.window == 0 || k0 > qpos - p.window))) s0[i] = 0xff800000u;   // -inf
+          if (!(k1 <= qpos && (p.window == 0 || k1 > qpos - p.window))) s1[i] = 0xff800000u;
+        }
+      }
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        mxa = fmaxf(mxa, __uint_as_float(s0[i]));
+        mxb = fmaxf(mxb, __uint_as_float(s0[i + 1]));
+        mxc = fmaxf(mxc, __uint_as_float(s1[i]));
+        mxd = fmaxf(mxd, __uint_as_float(s1[i + 1]));
+      }
+      float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+      // ---- move the reference maximum only when the row's maximum has outgrown it by 2^8
+      bool grow = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > 8.0f);
+      if (__any_sync(0xffffffffu, grow)) {
+        float factor = grow ? ((m_ref == -INFINITY) ? 0.f : ft_ex2((m_ref - mx) * sc)) : 1.f;
+        if (j >= 1) {
+          // O holds the products of tiles 0..j-1: they must be complete before it is rewritten
+          ok = mbar_wait(b_ofull, (j - 1) & 1, abort);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          uint32_t v[32];
+#pragma unroll 1
+          for (int c0 = 0; c0 < FT_HD; c0 += 32) {
+            tmem_ld32(t_lane + 128 + c0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tmem_st32(t_lane + 128 + c0, v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+        l *= factor;
+        if (grow) m_ref = mx;
+      }
+      float msc = (m_ref == -INFINITY) ? 0.f : m_ref * sc;
+      float rsa = 0.f, rsb = 0.f;
+      uint32_t pk[32];                              // 64 probabilities as bfloat16 pairs: keys 2i, 2i+1
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        float e0 = ft_ex2(fmaf(__uint_as_float(s0[2 * i]), sc, -msc)), e1 = ft_ex2(fmaf(__uint_as_float(s0[2 * i + 1]), sc, -msc));
+        float e2 = ft_ex2(fmaf(__uint_as_float(s1[2 * i]), sc, -msc)), e3 = ft_ex2(fmaf(__uint_as_float(s1[2 * i + 1]), sc, -msc));
+        rsa += e0 + e1;
+        rsb += e2 + e3;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(e0, e1), hi = __floats2bfloat162_rn(e2, e3);
+        pk[i] = *(uint32_t*)&lo;
+        pk[16 + i] = *(uint32_t*)&hi;
+      }
+      l += rsa + rsb;
+      // ---- P into shared memory (the MMA must have finished reading the previous P)
+      ok = mbar_wait(b_pempty, (j & 1) ^ 1, abort);
+      if (!ok) break;
+      if (t == t_hi) {
+        // keys of the last page beyond the last query's position hold whatever the page held before:
+        // their probabilities are zero, but 0 * NaN is NaN, so their value rows are cleared
+        int s = j % FT_STAGES, n_valid = q_hi + 1 - t * FT_BK;
+        ok = mbar_wait(b_kvfull + 8 * s, (j / FT_STAGES) & 1, abort);
+        if (!ok) break;
+        for (int e = (warp - 2) * 32 + lane; e < (FT_BK - n_valid) * 8; e += 128) {
+          int row = n_valid + e / 8, c = e % 8;
+          *(uint4*)(smem + Q_BYTES + P_BYTES + FT_STAGES * KV_BYTES + s * KV_BYTES + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      {
+        uint8_t* prow = smem + Q_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+          *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_pfull);
+    }
+    if (ok) ok = mbar_wait(b_ofull, (n_tiles - 1) & 1, abort);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + (size_t)(row0 + r0 + r) * ((size_t)p.H * FT_HD) + (size_t)h * FT_HD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < FT_HD; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + 128 + c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (r < nq) {
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            uint4 w;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(v[8 * c]) * inv, __uint_as_float(v[8 * c + 1]) * inv);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2]) * inv, __uint_as_float(v[8 * c + 3]) * inv);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 4]) * inv, __uint_as_float(v[8 * c + 5]) * inv);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 6]) * inv, __uint_as_float(v[8 * c + 7]) * inv);
+            w.x = *(uint32_t*)&p0; w.y = *(uint32_t*)&p1; w.z = *(uint32_t*)&p2; w.w = *(uint32_t*)&p3;
+            *(uint4*)(dst + c0 + 8 * c) = w;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+  if (threadIdx.x == 0 && *abort) atomicExch(p.err, 2);
+}
+
+// q: [T, q_ld] rotated queries (head h at columns h*64); out: [T, H*64]; kpages/vpages:
+// [n_pages][G][64][64] with n_pages the number of pages the storage holds.
+SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* out, const int* seq_start, const int* seq_pos0,
+                                          const int* block_table, int max_pages, const void* kpages, const void* vpages,
+                                          long long n_pages, int B, int max_new, int H, int G, int hd, int window, float scale,
+                                          int* err, cudaStream_t stream) {
+  if (B <= 0 || max_new <= 0) return 0;
+  if (hd != FT_HD || G < 1 || H % G != 0 || (q_ld & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+      ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15))
+    return SLLM_ERR_ARG;
+  long long kv_rows = n_pages * G * FT_BK;
+  if (kv_rows <= 0 || kv_rows > 0x7fffffffLL) return SLLM_ERR_ARG;
+  CUtensorMap mq, mk, mv;
+  int rc = tc_make_map(&mq, q, T, q_ld, q_ld, FT_BQ);
+  if (rc) return rc;
+  rc = tc_make_map(&mk, kpages, (int)kv_rows, FT_HD, FT_HD, FT_BK);
+  if (rc) return rc;
+  rc = tc_make_map(&mv, vpages, (int)kv_rows, FT_HD, FT_HD, FT_BK);
+  if (rc) return rc;
+  constexpr size_t smem = FT_BQ * FT_HD * 2 + FT_BQ * FT_BK * 2 + 2 * FT_STAGES * FT_BK * FT_HD * 2 + 1024 + 256;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    raised = true;
+  }
+  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err};
+  dim3 grid((max_new + FT_BQ - 1) / FT_BQ, H, B);
+  attn_prefill_tc_kernel<<<grid, FT_THREADS, smem, stream>>>(mq, mk, mv, a);
+  SLLM_RETURN_LAST();
+}

@@ -30,8 +30,9 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "bf16": ("lib_bf16.cu", ("common.cuh", "generic_kernels.cuh", "generic_launchers.inc")),
     "sampling": ("lib_sampling.cu", ("common.cuh",)),
     "decode_bf16": ("decode_bf16.cu", ("common.cuh", "attn_decode_noalloc.h")),
-    "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh",)),
+    "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
     "attn_prefill_bf16": ("attn_prefill_bf16.cu", ("common.cuh",)),
+    "attn_prefill_tcgen05": ("attn_prefill_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -14,93 +14,15 @@
 //
 // Every wait has a time limit; when one runs out the kernel raises *err, waits (again bounded) for
 // its own copies in flight, frees its tensor memory and returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
-#define TC_WAIT_NS 2000000000ull   // 2 s
 
 #define TC_EPI_STORE 0
 #define TC_EPI_SWIGLU 1
 #define TC_EPI_RESIDUAL 2   // C is the float residual stream: C += A B^T
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Waits for the barrier's phase `parity`; gives up after TC_WAIT_NS or when another thread of the
-// block has given up (`*abort`), and says so by returning false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
-  if (mbar_try(bar, parity)) return true;
-  uint64_t t0 = global_ns();
-  for (uint32_t it = 1;; it++) {
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 255u) == 0) {
-      if (*abort) return false;
-      if (global_ns() - t0 > TC_WAIT_NS) { *abort = 1; return false; }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-
-// K-major operand tile in shared memory, rows of 128 bytes (64 bfloat16), 128-byte swizzle:
-// 8-row groups 1024 bytes apart (stride byte offset), leading byte offset 16 bytes, descriptor
-// version 1, layout type 2 (SWIZZLE_128B). A step of 16 in K moves the start address by 32 bytes.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// kind::f16 instruction descriptor: float accumulator, bfloat16 A and B, both K-major, shape M x N.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr) : "memory");
-}
 
 // Writes 32 consecutive accumulator columns of one row. EPI_STORE: as they are; EPI_SWIGLU: the 32
 // columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2).
@@ -292,36 +214,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// rows x cols bfloat16, row stride ld elements; box = box_rows x 64 columns, 128-byte swizzle, zero fill
-static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return SLLM_ERR_ARG - 1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : SLLM_ERR_ARG - 2;
-}
-
 template <int BN, int STAGES, int EPI>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int out_f32,
                      int* err, cudaStream_t stream) {
@@ -355,9 +247,9 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
   if (epilogue == TC_EPI_SWIGLU && ((N & 15) || out_f32)) return SLLM_ERR_ARG;
   CUtensorMap ma, mb;
   int big = N > 128;
-  int rc = make_map(&ma, A, M, K, lda, TC_BM);
+  int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
   if (rc) return rc;
-  rc = make_map(&mb, B, N, K, ldb, big ? 256 : 128);
+  rc = tc_make_map(&mb, B, N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
   if (epilogue == TC_EPI_RESIDUAL)
     return big ? tc_launch<256, 4, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream)
