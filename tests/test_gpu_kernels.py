@@ -297,15 +297,16 @@ def test_attn_prefill_tensor_core(kernel_sets, H, G, hd, window):
     assert rel_err(out.cpu().float(), want) < 1.2e-2          # probabilities are rounded to bfloat16 before P V
 
 
+@pytest.mark.parametrize("lens, pos0", [([37, 1, 130, 64, 200, 128], [0, 250, 70, 64, 0, 300]), ([37], [0]), ([1], [700]),
+                                        ([2, 3], [63, 64])])
 @pytest.mark.parametrize("H, G, window", [(4, 2, None), (3, 1, None), (6, 3, 24), (8, 2, 100), (5, 5, 1), (2, 2, 64)])
-def test_attn_prefill_tcgen05(kernel_sets, H, G, window):
+def test_attn_prefill_tcgen05(kernel_sets, H, G, window, lens, pos0):
     """The tcgen05 attention (S and P V in tensor memory, TMA-fed pages): prompts that start at a
     non-empty cache, a one-token prompt, tiles of exactly 64 and 128 queries, windows; unused cache
     memory is NaN, which the kernel must never let through."""
     fa = kernel_sets[torch.bfloat16].prefill_attention_tc
     hd = 64
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    lens, pos0 = [37, 1, 130, 64, 200, 128], [0, 250, 70, 64, 0, 300]
     qs, kk, vv = attention_case(H, G, hd, lens, pos0, 30)
     rnd = lambda t: t.bfloat16().float()
     qs, kk, vv = [rnd(t) for t in qs], [rnd(t) for t in kk], [rnd(t) for t in vv]
