@@ -30,6 +30,16 @@ SHAPE = {
     "vocab_size": 49152, "rope_theta": 130000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
     "max_position_embeddings": 8192, "hidden_act": "silu",
 }
+# further sizes of the family (BASELINE.json configs[3], configs[4]); the default run uses SHAPE
+OTHER_SHAPES = {
+    "llama3.2-1b": dict(SHAPE, num_hidden_layers=16, num_key_value_heads=8, vocab_size=128256, rope_theta=500000.0,
+                        rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                      "original_max_position_embeddings": 8192}),
+    "llama3.1-8b": dict(SHAPE, num_hidden_layers=32, hidden_size=4096, num_key_value_heads=8, head_dim=128,
+                        intermediate_size=14336, vocab_size=128256, rope_theta=500000.0, tie_word_embeddings=False,
+                        rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                      "original_max_position_embeddings": 8192}),
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -188,7 +198,9 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"],
+    ap.add_argument("--shape", default="smollm2-1.7b", choices=["smollm2-1.7b"] + sorted(OTHER_SHAPES),
+                    help="layer sizes to run (default: the SmolLM2-1.7B shape of the headline metric)")
+    ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers of the same sizes (named in config as layers_run / layers_full)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
@@ -197,6 +209,9 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
     args = ap.parse_args()
+    shape = SHAPE if args.shape == "smollm2-1.7b" else OTHER_SHAPES[args.shape]
+    if args.layers is None:
+        args.layers = shape["num_hidden_layers"]
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go package (go.mod) with CPU-only code; "
@@ -214,7 +229,7 @@ def main():
     from scriptling_llm_lib_b200.engine.step import StepEntry
 
     pk = peaks()
-    cfg_raw = dict(SHAPE, num_hidden_layers=args.layers)
+    cfg_raw = dict(shape, num_hidden_layers=args.layers)
     nums = model_numbers(cfg_raw, args.layers)
     tmp = tempfile.mkdtemp(prefix="sllm_bench_")
     model_dir = os.path.join(tmp, "model")
@@ -304,16 +319,16 @@ def main():
             pass
 
     line = {
-        "metric": "decode tokens/s (SmolLM2-1.7B shape, random weights, batch 8, context 4096)",
+        "metric": f"decode tokens/s ({args.shape} shape, random weights, batch {args.batch}, context {args.context})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, random-init weights N(0,0.02)",
         "impl": "ours",
-        "config": {"model": "SmolLM2-1.7B shape", "layers_run": args.layers, "layers_full": SHAPE["num_hidden_layers"],
-                   "hidden": SHAPE["hidden_size"], "heads": SHAPE["num_attention_heads"],
-                   "kv_heads": SHAPE["num_key_value_heads"], "head_dim": SHAPE["head_dim"],
-                   "intermediate": SHAPE["intermediate_size"], "vocab": SHAPE["vocab_size"],
-                   "rope_theta": SHAPE["rope_theta"], "rms_eps": SHAPE["rms_norm_eps"], "tied": True,
+        "config": {"model": f"{args.shape} shape", "layers_run": args.layers, "layers_full": shape["num_hidden_layers"],
+                   "hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
+                   "kv_heads": shape["num_key_value_heads"], "head_dim": shape["head_dim"],
+                   "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+                   "rope_theta": shape["rope_theta"], "rms_eps": shape["rms_norm_eps"], "tied": shape["tie_word_embeddings"],
                    "global_batch": args.batch, "seq_len": args.context, "prompt_len": args.context - args.steps - args.warmup,
                    "parallelism": "1gpu", "l2": "step inputs (weights+cache) exceed L2; prefill flushes L2",
                    "sampling": "greedy"},
