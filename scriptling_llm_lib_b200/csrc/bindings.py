@@ -274,6 +274,21 @@ class DecodeKernels:
         only while the output is too narrow to give the 128 x 256 tensor-core tiles enough blocks."""
         return DecodeKernels.takes(a, w) and (a.shape[0] <= 16 or w.shape[0] < 12288)
 
+    MAX_SPLITS = 64      # beyond this the merging block falls back to a slow loop
+
+    @staticmethod
+    def attention_splits(n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, pages: int, sm_count: int) -> int:
+        """Over how many blocks a decode step splits each sequence's keys: enough blocks to fill the
+        GPU, never more than the longest sequence has pages. The grouped-query kernel (two or more
+        query heads per key/value head at widths 64 and 128) has fatter blocks: it wants about four
+        per SM and at least four pages each; the one-head kernel about six per SM."""
+        pairs = max(1, n_seqs * n_kv_heads)
+        if n_heads >= 2 * n_kv_heads and head_dim in (64, 128):
+            want, cap = -(-4 * sm_count // pairs), max(1, pages // 4)
+        else:
+            want, cap = -(-6 * sm_count // pairs), pages
+        return max(1, min(want, cap, DecodeKernels.MAX_SPLITS))
+
     def gemm_small_m(self, a, w, out, swiglu=False):
         """out[M,N] = a @ w^T (bfloat16 or float32 out); swiglu: out[M,N/2] = silu(gate)*up for w rows
         tiled 8 gate / 8 up; out float32 [P,M,N]: K split P ways, out receives the partial sums."""

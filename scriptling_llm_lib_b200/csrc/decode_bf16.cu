@@ -184,6 +184,7 @@ SLLM_EXPORT int sllm_gemm_small_m_bf16(const void* x, const void* W, void* y, in
 #define AD_WARPS 4
 #define AD_UN 4   // keys each lane group has in flight
 #define AD_LOG2E 1.4426950408889634f
+#define AD_MAX_SPLIT 64   // splits the merging block weighs with one warp pass; more are merged the slow way
 
 struct AttnDecodeArgs {
   const bf16* q;        // [B, q_ld] rotated queries of this step, head h at columns h*HD
@@ -240,6 +241,82 @@ __device__ __forceinline__ void rope8_raw(const bf16* head, int d0, int rot, int
   }
 #pragma unroll
   for (int j = 0; j < 8; j++) out[j] = __bfloat162float(__float2bfloat16_rn(out[j]));
+}
+
+// The block that finishes last among the splits of a (sequence, key/value head) merges them: every
+// block publishes its partial results, then takes a ticket; nobody waits for anybody.
+__device__ __forceinline__ void ad_ticket_merge(const AttnDecodeArgs& p, int b, int g, int nrep, int HD) {
+  if (p.tickets == nullptr || p.n_split == 1) return;     // one split: its block wrote the output itself
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = p.tickets + (size_t)b * p.G + g;
+    int t = atomicAdd(tk, 1);
+    s_last = (t == p.n_split - 1);
+    if (s_last) *tk = 0;                       // all splits have drawn: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (p.n_split > 8 && p.n_split <= AD_MAX_SPLIT) {
+    // many splits, eight heads at a time: a warp per head weighs the splits (lanes over splits), then every
+    // thread adds one output element over the splits with loads that do not depend on each other
+    __shared__ float sm_c[8][AD_MAX_SPLIT];
+    __shared__ float sm_l[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int h0 = 0; h0 < nrep; h0 += 8) {
+      const int nh = min(8, nrep - h0);
+      for (int r = warp; r < nh; r += AD_WARPS) {
+        const float* src = p.part + ((size_t)b * p.H + g * nrep + h0 + r) * p.n_split * (HD + 2) + HD;
+        float ms[AD_MAX_SPLIT / 32], ls[AD_MAX_SPLIT / 32], mn = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < AD_MAX_SPLIT / 32; i++) {
+          int s2 = lane + 32 * i;
+          ms[i] = s2 < p.n_split ? __ldcg(src + (size_t)s2 * (HD + 2)) : -INFINITY;
+          ls[i] = s2 < p.n_split ? __ldcg(src + (size_t)s2 * (HD + 2) + 1) : 0.f;
+          mn = fmaxf(mn, ms[i]);
+        }
+        mn = warp_max(mn);
+        float lsum = 0.f;
+#pragma unroll
+        for (int i = 0; i < AD_MAX_SPLIT / 32; i++) {
+          float c = (mn == -INFINITY || ms[i] == -INFINITY) ? 0.f : exp2f(ms[i] - mn);
+          sm_c[r][lane + 32 * i] = c;
+          lsum += ls[i] * c;
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) sm_l[r] = lsum;
+      }
+      __syncthreads();
+      for (int v = threadIdx.x; v < nh * HD; v += AD_WARPS * 32) {
+        int r = v / HD, dd = v % HD, h = g * nrep + h0 + r;
+        const float* src = p.part + ((size_t)b * p.H + h) * p.n_split * (HD + 2) + dd;
+        float a = 0.f;
+#pragma unroll 8
+        for (int s2 = 0; s2 < p.n_split; s2++) a += __ldcg(src + (size_t)s2 * (HD + 2)) * sm_c[r][s2];
+        float ls = sm_l[r];
+        p.out[((size_t)b * p.H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+      }
+      __syncthreads();
+    }
+    return;
+  }
+  for (int v = threadIdx.x; v < nrep * HD; v += AD_WARPS * 32) {
+    int h = g * nrep + v / HD, dd = v % HD;
+    const float* src = p.part + ((size_t)b * p.H + h) * p.n_split * (HD + 2);
+    float mn = -INFINITY;
+    for (int s2 = 0; s2 < p.n_split; s2++) mn = fmaxf(mn, __ldcg(src + (size_t)s2 * (HD + 2) + HD));
+    float a = 0.f, ls = 0.f;
+    for (int s2 = 0; s2 < p.n_split; s2++) {
+      const float* ps = src + (size_t)s2 * (HD + 2);
+      float ms = __ldcg(ps + HD);
+      float c = (mn == -INFINITY || ms == -INFINITY) ? 0.f : exp2f(ms - mn);
+      a += __ldcg(ps + dd) * c;
+      ls += __ldcg(ps + HD + 1) * c;
+    }
+    p.out[((size_t)b * p.H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+  }
 }
 
 template <int HD, int NREP, bool RAW>
@@ -450,6 +527,245 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
   }
 }
 
+// Grouped-query variant on the tensor cores (mma.sync.m16n8k16), for 2 or more query heads per
+// key/value head: the heads of the group are the 16 rows of the MMA, a tile of 16 keys its
+// columns. Lane (n = lane/4, t = lane%4) loads keys and values straight from the pages into
+// fragments with 16-byte loads, no shared memory:
+//   scores: B operand = K; the lane loads dims [(4j+t)*8, +8) of key n; those 8 dims fill the k-slots
+//     (2t, 2t+1, 2t+8, 2t+9) of two MMAs and the query fragments use the same assignment.
+//   output: A operand = the probabilities, whose layout is the one the score MMAs left them in;
+//     B operand = V, which the MMA wants as pairs of keys for one dim: the lane loads dims
+//     [n*8, +8) of keys 2t, 2t+1, 2t+8, 2t+9 and pairs them up with byte permutes. Column n of
+//     output tile jt is dim n*8 + jt.
+// UP: rows 8..15 carry heads too (more than 8 heads per group). The maximum is kept per row over
+// the four lanes that share it, and the running output is rescaled only when some row's grew.
+template <int HD, bool UP, bool RAW>
+__global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDecodeArgs p) {
+  constexpr int ROWS = UP ? 16 : 8;
+  constexpr int CH = HD / 8;       // 16-byte chunks of a head row
+  constexpr int NJ = HD / 32;      // pairs of k-steps of the score product
+  constexpr int NC = HD / 64;      // 64-dim column blocks of the output
+  __shared__ __align__(16) bf16 sm_q[ROWS][HD];
+  __shared__ float sm_acc[AD_WARPS][ROWS][HD + 1];
+  __shared__ float sm_ml[AD_WARPS][ROWS][2];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = lane >> 2, t = lane & 3;
+  const int pos = p.seq_pos0[b];
+  const int k_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int pb = k_begin / SLLM_PAGE, pe = pos / SLLM_PAGE;
+  const int pps = (pe - pb + 1 + p.n_split - 1) / p.n_split;
+  const int p0 = pb + split * pps, p1 = min(pe + 1, p0 + pps);
+  const int k_lo = max(k_begin, p0 * SLLM_PAGE), k_hi = min(pos + 1, p1 * SLLM_PAGE);
+  const int* bt = p.block_table + (size_t)b * p.max_pages;
+  const int nrep = p.H / p.G;
+  const bf16* rowp = p.q + (size_t)b * p.q_ld;
+  const float2* csr = RAW ? p.cs + (size_t)pos * (p.rot >> 1) : nullptr;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  const float sc = p.scale * AD_LOG2E;
+
+  // raw mode: the block whose range holds the query's own position rotates the new key and appends
+  // key and value to the cache; after the barrier below they are cached keys like the others
+  if (RAW && p.write_kv && pos >= k_lo && pos < k_hi && threadIdx.x < CH) {
+    int dl = threadIdx.x * 8;
+    float kn[8];
+    rope8_raw(rowp + (size_t)(p.H + g) * HD, dl, p.rot, p.interleaved, csr, kn);
+    uint4 vraw = ld_dep16(rowp + (size_t)(p.H + p.G + g) * HD + dl);
+    uint4 kraw;
+    __nv_bfloat162* kp2 = (__nv_bfloat162*)&kraw;
+#pragma unroll
+    for (int j = 0; j < 4; j++) kp2[j] = __floats2bfloat162_rn(kn[2 * j], kn[2 * j + 1]);
+    size_t off = (((size_t)bt[pos / SLLM_PAGE] * p.G + g) * SLLM_PAGE + (pos % SLLM_PAGE)) * HD + dl;
+    *(uint4*)(const_cast<bf16*>(p.kpages) + off) = kraw;
+    *(uint4*)(const_cast<bf16*>(p.vpages) + off) = vraw;
+  }
+
+  for (int r0 = 0; r0 < nrep; r0 += ROWS) {
+    for (int i = threadIdx.x; i < ROWS * CH; i += AD_WARPS * 32) {
+      int r = i / CH, dl = (i % CH) * 8;
+      uint4 val = zero;
+      if (r0 + r < nrep) {
+        const bf16* head = rowp + (size_t)(g * nrep + r0 + r) * HD;
+        if (RAW) {
+          float qr[8];
+          rope8_raw(head, dl, p.rot, p.interleaved, csr, qr);
+          __nv_bfloat162* q2 = (__nv_bfloat162*)&val;
+#pragma unroll
+          for (int j = 0; j < 4; j++) q2[j] = __floats2bfloat162_rn(qr[2 * j], qr[2 * j + 1]);
+        } else {
+          val = ld_dep16(head + dl);
+        }
+      }
+      *(uint4*)&sm_q[r][dl] = val;
+    }
+    __syncthreads();
+    uint32_t qa[2 * NJ][4];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+      uint4 lo = *(const uint4*)&sm_q[n][(j * 4 + t) * 8];
+      uint4 hi = UP ? *(const uint4*)&sm_q[UP ? n + 8 : n][(j * 4 + t) * 8] : zero;
+      qa[2 * j][0] = lo.x; qa[2 * j][1] = hi.x; qa[2 * j][2] = lo.y; qa[2 * j][3] = hi.y;
+      qa[2 * j + 1][0] = lo.z; qa[2 * j + 1][1] = hi.z; qa[2 * j + 1][2] = lo.w; qa[2 * j + 1][3] = hi.w;
+    }
+    float o[NC * 8][4];
+#pragma unroll
+    for (int i = 0; i < NC * 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    auto fetch = [&](uint4 (&kr)[2][NJ], uint4 (&vr)[4][NC], int base) {
+      const size_t row0 = ((size_t)bt[base / SLLM_PAGE] * p.G + g) * SLLM_PAGE + (base % SLLM_PAGE);
+      const bf16* kp = p.kpages + row0 * HD;
+      const bf16* vp = p.vpages + row0 * HD;
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        int key = base + u * 8 + n;
+        bool ok = key >= k_lo && key < k_hi;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) kr[u][j] = ok ? ld_dep16_stream(kp + (size_t)(u * 8 + n) * HD + (j * 4 + t) * 8) : zero;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        int kk = 2 * t + (i & 1) + (i >> 1) * 8;
+        bool ok = base + kk >= k_lo && base + kk < k_hi;
+#pragma unroll
+        for (int c = 0; c < NC; c++) vr[i][c] = ok ? ld_dep16_stream(vp + (size_t)kk * HD + (c * 8 + n) * 8) : zero;
+      }
+    };
+    auto attend = [&](uint4 (&kr)[2][NJ], uint4 (&vr)[4][NC], int base) {
+      float s[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        s[u][0] = s[u][1] = s[u][2] = s[u][3] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+          mma_16816(s[u], qa[2 * j][0], qa[2 * j][1], qa[2 * j][2], qa[2 * j][3], kr[u][j].x, kr[u][j].y);
+          mma_16816(s[u], qa[2 * j + 1][0], qa[2 * j + 1][1], qa[2 * j + 1][2], qa[2 * j + 1][3], kr[u][j].z, kr[u][j].w);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          int key = base + u * 8 + 2 * t + (e & 1);
+          s[u][e] = (key >= k_lo && key < k_hi) ? s[u][e] * sc : -INFINITY;
+        }
+      }
+      float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      float mx1 = UP ? fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3])) : -INFINITY;
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      if (UP) {
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      }
+      if (__any_sync(0xffffffffu, mx0 > m0 || (UP && mx1 > m1))) {
+        float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        float c0 = n0 == -INFINITY ? 1.f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.f : exp2f(m1 - n1);
+        m0 = n0; m1 = n1;
+        l0 *= c0; l1 *= c1;
+#pragma unroll
+        for (int i = 0; i < NC * 8; i++) {
+          o[i][0] *= c0; o[i][1] *= c0;
+          if (UP) { o[i][2] *= c1; o[i][3] *= c1; }
+        }
+      }
+      const float u0 = m0 == -INFINITY ? 0.f : m0, u1 = m1 == -INFINITY ? 0.f : m1;
+      float pr[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        pr[u][0] = exp2f(s[u][0] - u0); pr[u][1] = exp2f(s[u][1] - u0);
+        pr[u][2] = UP ? exp2f(s[u][2] - u1) : 0.f; pr[u][3] = UP ? exp2f(s[u][3] - u1) : 0.f;
+      }
+      l0 += (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+      if (UP) l1 += (pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]);
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(pr[0][0], pr[0][1]), h1 = __floats2bfloat162_rn(pr[0][2], pr[0][3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(pr[1][0], pr[1][1]), h3 = __floats2bfloat162_rn(pr[1][2], pr[1][3]);
+      const uint32_t pa0 = *(uint32_t*)&h0, pa1 = UP ? *(uint32_t*)&h1 : 0u, pa2 = *(uint32_t*)&h2, pa3 = UP ? *(uint32_t*)&h3 : 0u;
+#pragma unroll
+      for (int c = 0; c < NC; c++) {
+        const uint32_t* va = (const uint32_t*)&vr[0][c];
+        const uint32_t* vb = (const uint32_t*)&vr[1][c];
+        const uint32_t* vc = (const uint32_t*)&vr[2][c];
+        const uint32_t* vd = (const uint32_t*)&vr[3][c];
+#pragma unroll
+        for (int jt = 0; jt < 8; jt++) {
+          const uint32_t sel = (jt & 1) ? 0x7632u : 0x5410u;
+          uint32_t b0 = __byte_perm(va[jt >> 1], vb[jt >> 1], sel), b1 = __byte_perm(vc[jt >> 1], vd[jt >> 1], sel);
+          mma_16816(o[c * 8 + jt], pa0, pa1, pa2, pa3, b0, b1);
+        }
+      }
+    };
+    // a warp takes every AD_WARPS-th tile of 16 keys; two register buffers used in turn, so the next
+    // tile's keys and values are in flight while the current tile is multiplied
+    constexpr int STEP = AD_WARPS * 16;
+    int base = (k_lo & ~15) + warp * 16;
+    if constexpr (HD >= 128) {
+      // two register buffers used in turn: the next tile is in flight while this one is multiplied.
+      // (At width 64 a tile is too small for that to pay for the registers.)
+      uint4 ka[2][NJ], va[4][NC], kb[2][NJ], vb[4][NC];
+      if (base < k_hi) fetch(ka, va, base);
+      while (base < k_hi) {
+        if (base + STEP < k_hi) fetch(kb, vb, base + STEP);
+        attend(ka, va, base);
+        base += STEP;
+        if (base >= k_hi) break;
+        if (base + STEP < k_hi) fetch(ka, va, base + STEP);
+        attend(kb, vb, base);
+        base += STEP;
+      }
+    } else {
+      uint4 ka[2][NJ], va[4][NC];
+      for (; base < k_hi; base += STEP) {
+        fetch(ka, va, base);
+        attend(ka, va, base);
+      }
+    }
+    // the four lanes of a row hold different keys' shares of the sum; then the warps are merged
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    if (UP) {
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+#pragma unroll
+      for (int jt = 0; jt < 8; jt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          int d = (c * 8 + 2 * t + e) * 8 + jt;
+          sm_acc[warp][n][d] = o[c * 8 + jt][e];
+          if (UP) sm_acc[warp][UP ? n + 8 : n][d] = o[c * 8 + jt][2 + e];
+        }
+    if (t == 0) {
+      sm_ml[warp][n][0] = m0; sm_ml[warp][n][1] = l0;
+      if (UP) { sm_ml[warp][UP ? n + 8 : n][0] = m1; sm_ml[warp][UP ? n + 8 : n][1] = l1; }
+    }
+    __syncthreads();
+    const int rows = min(ROWS, nrep - r0);
+    for (int v = threadIdx.x; v < rows * HD; v += AD_WARPS * 32) {
+      int r = v / HD, dd = v % HD;
+      float mn = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < AD_WARPS; w++) mn = fmaxf(mn, sm_ml[w][r][0]);
+      float a = 0.f, ls = 0.f;
+#pragma unroll
+      for (int w = 0; w < AD_WARPS; w++) {
+        float c = mn == -INFINITY ? 0.f : exp2f(sm_ml[w][r][0] - mn);
+        a += sm_acc[w][r][dd] * c;
+        ls += sm_ml[w][r][1] * c;
+      }
+      if (p.n_split == 1 && p.tickets != nullptr) {        // nothing to merge with: this is the result
+        p.out[((size_t)b * p.H + g * nrep + r0 + r) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
+        continue;
+      }
+      float* dst = p.part + (((size_t)b * p.H + g * nrep + r0 + r) * p.n_split + split) * (HD + 2);
+      dst[dd] = a;
+      if (dd == 0) { dst[HD] = mn; dst[HD + 1] = ls; }
+    }
+    __syncthreads();
+  }
+  ad_ticket_merge(p, b, g, nrep, HD);
+}
+
 // out[b, h*HD + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, int H, int HD,
                                          int n_split) {
@@ -477,6 +793,19 @@ static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStr
   dim3 grid(a.n_split, a.G, B);
   int nrep = a.H / a.G;
   cudaError_t e;
+  if constexpr (HD == 64 || HD == 128) {
+    static const bool scalar_only = getenv("SLLM_DECODE_SCALAR") != nullptr;   // for comparisons
+    if (nrep >= 2 && !scalar_only) {
+      bool up = nrep > 8;
+#define AD_MMA(UPV, RAWV) sllm_launch(attn_decode_mma_kernel<HD, UPV, RAWV>, grid, dim3(AD_WARPS * 32), 0, stream, a)
+      if (a.cs != nullptr) e = up ? AD_MMA(true, true) : AD_MMA(false, true);
+      else e = up ? AD_MMA(true, false) : AD_MMA(false, false);
+#undef AD_MMA
+      if (e != cudaSuccess || a.tickets != nullptr) return (int)e;
+      return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD), 0, stream, (const float*)a.part, out, a.H,
+                              HD, a.n_split);
+    }
+  }
   if (a.cs != nullptr) {
     if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
     else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);

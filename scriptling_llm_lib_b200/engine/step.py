@@ -74,11 +74,10 @@ class StepContext:
     def casts(self):
         return self.engine.casts
 
-    def decode_splits(self, n_kv_heads: int) -> int:
-        """Over how many blocks a decode step splits each sequence's keys: enough blocks to fill the
-        GPU a few times over, never more than the longest sequence has pages."""
-        want = -(-6 * self.engine.sm_count // max(1, self.n_seqs * n_kv_heads))
-        return max(1, min(self.max_pages, want))
+    def decode_splits(self, n_heads: int, n_kv_heads: int, head_dim: int) -> int:
+        """Over how many blocks a decode step splits each sequence's keys."""
+        return self.kernels.decode.attention_splits(self.n_seqs, n_heads, n_kv_heads, head_dim, self.max_pages,
+                                                    self.engine.sm_count)
 
     def unit_kv(self, unit: int):
         g = self.cache.group_of_unit[unit]

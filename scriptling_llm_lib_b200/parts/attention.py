@@ -63,7 +63,7 @@ class Attention(Mixer):
                 self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
         attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
         if fast_decode:
-            n_split = ctx.decode_splits(self.n_kv_heads)
+            n_split = ctx.decode_splits(self.n_heads, self.n_kv_heads, self.head_dim)
             scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                   device=x.device)
             tickets = ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads)

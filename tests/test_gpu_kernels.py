@@ -323,8 +323,12 @@ def test_attn_prefill_tcgen05(kernel_sets, H, G, window, lens, pos0):
 
 
 @pytest.mark.parametrize("H, G, hd, window", [(4, 2, 16, None), (3, 1, 32, None), (32, 32, 64, None), (8, 2, 128, 300),
-                                              (4, 1, 64, 65), (2, 2, 256, None)])
-@pytest.mark.parametrize("n_split", [1, 3, 16])
+                                              (4, 1, 64, 65), (2, 2, 256, None),
+                                              # two or more query heads per key/value head at widths 64 and 128: the
+                                              # tensor-core variant; 12 and 40 heads per group use its upper rows and loop
+                                              (32, 8, 64, None), (9, 3, 64, 100), (6, 3, 128, None), (24, 2, 64, 17),
+                                              (40, 1, 128, 500)])
+@pytest.mark.parametrize("n_split", [1, 3, 16, 40, 70])      # 70: more than the merging block weighs in one pass
 def test_attn_decode(kernel_sets, H, G, hd, window, n_split):
     dk = kernel_sets[torch.bfloat16].decode
     lens, pos0 = [1, 1, 1, 1, 1], [0, 63, 64, 700, 257]
@@ -353,7 +357,9 @@ def test_attn_decode(kernel_sets, H, G, hd, window, n_split):
 
 @pytest.mark.parametrize("H, G, hd, rot, pairing, window", [(4, 2, 16, 16, "half", None), (3, 1, 32, 16, "interleaved", None),
                                                             (32, 32, 64, 64, "half", None), (8, 2, 128, 64, "half", 300),
-                                                            (4, 4, 64, 8, "interleaved", 65)])
+                                                            (4, 4, 64, 8, "interleaved", 65),
+                                                            (9, 3, 64, 64, "half", 70), (12, 1, 64, 32, "interleaved", None),
+                                                            (32, 8, 128, 128, "half", None)])
 @pytest.mark.parametrize("n_split", [1, 5])
 def test_attn_decode_with_rotation_and_cache_write_fused(kernel_sets, H, G, hd, rot, pairing, window, n_split):
     """One kernel does what rope_kv_write + attn_decode do: rotate q, rotate and store the new key,
