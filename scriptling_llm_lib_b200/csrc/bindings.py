@@ -186,6 +186,7 @@ class TensorCoreGemm:
     def __init__(self):
         self.lib = load_library("gemm_tcgen05")
         self.lib.sllm_gemm_tc_bf16.restype = c_int
+        self.lib.sllm_gemm_tc_skinny_bf16.restype = c_int
 
     @staticmethod
     def takes(a, w) -> bool:
@@ -211,6 +212,50 @@ class TensorCoreGemm:
             c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
             c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
             c_int(2 if accumulate else (1 if swiglu else 0)), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
+
+
+    SKINNY_MAX_M = 128
+
+    def gemm_skinny(self, a, w, out, err_flag, swiglu=False):
+        """The same product for at most 128 rows of `a`, with the weights as the tensor cores' 128-row
+        operand and a grid over (128 weight rows, K splits). out [M,N] bfloat16 or float32, or
+        [M,N/2] with swiglu; float32 [P,M,N]: K split P ways, out receives the partial sums."""
+        M, K = a.shape
+        N = w.shape[0]
+        ksplit = out.shape[0] if out.dim() == 3 else 1
+        want = (M, N // 2) if swiglu else ((ksplit, M, N) if out.dim() == 3 else (M, N))
+        if out.dim() == 3 and out.dtype != torch.float32:
+            raise KernelError("partial sums are written in float32")
+        if tuple(out.shape) != want or w.shape[1] != K or not out.is_contiguous():
+            raise KernelError(f"gemm_skinny shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"gemm_skinny dtypes: a {a.dtype}, w {w.dtype}, out {out.dtype}")
+        if not (a.is_cuda and w.is_cuda and out.is_cuda):
+            raise KernelError("gemm_skinny runs on a CUDA device only")
+        _check(self.lib.sllm_gemm_tc_skinny_bf16(
+            c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
+            c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
+            c_int(1 if swiglu else 0), c_int(ksplit), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_skinny")
+
+    def prefers_skinny(self, a, w, kind: str) -> bool:
+        """True where the few-rows kernel is the fastest of the three products for a [M,K] x [N,K]^T
+        (measured on the layer shapes of 1-8 B models): 9..128 rows; always when the reader takes
+        partial sums ("partials": K is split to fill the GPU); with the SiLU gate ("swiglu") up to 64
+        rows; a plain product ("plain") from 33 rows on and only while its N/128 blocks fit one wave."""
+        M, N = a.shape[0], w.shape[0]
+        if not (8 < M <= self.SKINNY_MAX_M and self.takes(a, w)):
+            return False
+        if kind == "partials":
+            return True
+        if kind == "swiglu":
+            return M <= 64
+        return M > 32 and N <= 128 * 148
+
+    @staticmethod
+    def skinny_split(n_out: int, k: int, sm_count: int) -> int:
+        """Over how many blocks to split K so that the (n_out / 128) x split grid about fills the GPU."""
+        tiles = -(-n_out // 128)
+        return max(1, min(sm_count // tiles, k // 256, 16))
 
 
 class PrefillAttention:

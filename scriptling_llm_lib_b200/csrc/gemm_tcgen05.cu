@@ -260,3 +260,183 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
   return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream)
              : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
 }
+
+// ------------------------------------------------------------------ few rows: the weights are the 128-row operand
+// C[M,N] = A[M,K] B[N,K]^T for M <= 128 rows (a decode step of 17..128 sequences): all the time
+// goes into streaming B, the weights, once. Here the roles are swapped: a block takes 128 rows of B
+// as the MMA's 128-row operand and the M rows of A, padded to BT, as its columns, so the
+// accumulator in tensor memory is C^T (lane = output column n, column = row m). The grid is
+// (N / 128, ksplit); each block streams its 128 x K/ksplit slab of B through a deep TMA ring, and
+// because weights do not depend on the kernel before, the ring is filled with them before
+// griddepcontrol.wait; only then are the activations fetched. ksplit > 1 writes float partial sums
+// C[ksplit][M][N] that the reader adds. EPI_SWIGLU as above (B's rows in tiles of 8 gate, 8 up).
+template <int BT, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, void* __restrict__ C,
+                      int M, int N, int K, int ldc, int out_f32, int* __restrict__ err) {
+  constexpr uint32_t W_BYTES = 128 * TC_BK * 2, X_BYTES = BT * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+  constexpr uint32_t TMEM_COLS = BT < 32 ? 32 : BT;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[STAGES], empty[STAGES], acc_full
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  volatile int* abort = (volatile int*)(tmem_slot + 1);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, acc_full = empty0 + 8 * STAGES;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 128;
+  const int nkb_all = (K + TC_BK - 1) / TC_BK, per = (nkb_all + gridDim.y - 1) / gridDim.y;
+  const int kb0 = blockIdx.y * per, kb1 = min(nkb_all, kb0 + per), nkb = max(0, kb1 - kb0);
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(acc_full, 1);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the first ring-full of weights goes out before the wait, their activations after it
+      const int pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; i++) {
+        mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+        tma_load_2d(smem_base + i * STAGE_BYTES, &map_w, (kb0 + i) * TC_BK, n0, full0 + 8 * i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; i++)
+        tma_load_2d(smem_base + i * STAGE_BYTES + W_BYTES, &map_x, (kb0 + i) * TC_BK, 0, full0 + 8 * i);
+      int it = pre;
+      for (; it < nkb; it++) {
+        int s = it % STAGES;
+        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, abort)) break;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(smem_base + s * STAGE_BYTES, &map_w, (kb0 + it) * TC_BK, n0, full0 + 8 * s);
+        tma_load_2d(smem_base + s * STAGE_BYTES + W_BYTES, &map_x, (kb0 + it) * TC_BK, 0, full0 + 8 * s);
+      }
+      if (*abort) {
+        // copies already issued still land in this block's shared memory: wait for them (bounded)
+        volatile int never = 0;
+        for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1, &never);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, BT);
+      bool ok = true;
+      for (int it = 0; it < nkb; it++) {
+        int s = it % STAGES;
+        ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t w_addr = smem_base + s * STAGE_BYTES, x_addr = w_addr + W_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; k++)
+          umma_bf16(tmem_base, umma_desc_sw128(w_addr + k * 32), umma_desc_sw128(x_addr + k * 32), idesc, (it | k) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int q = warp & 3;                      // the quarter of tensor memory this warp may read
+    const int n = n0 + q * 32 + lane;            // this lane's output column
+    // float output: this split's own [M][N] matrix of partial sums (the only one when K is not split)
+    const bool as_partial = EPI == TC_EPI_STORE && out_f32;
+    float* pdst = (float*)C + (size_t)blockIdx.y * M * ldc + n;
+    const int pld = ldc;
+    if (nkb == 0) {
+      // a split that got no k-blocks still owes the reader its (zero) partial sums
+      pdl_wait();
+      if (as_partial && n < N)
+        for (int m = 0; m < M; m++) pdst[(size_t)m * pld] = 0.f;
+    } else if (mbar_wait(acc_full, 0, abort)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      pdl_wait();        // returns at once: the activations behind the accumulator were fetched after the producer's wait
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 32) {
+        if (c0 >= M) break;                      // uniform over the block
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (as_partial) {
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (n < N && c0 + j < M) pdst[(size_t)(c0 + j) * pld] = __uint_as_float(r[j]);
+        } else if (EPI == TC_EPI_SWIGLU) {
+          // lanes 0-7 and 16-23 hold gate rows, the lanes 8 above them the matching up rows
+          int ocol = (n >> 4) * 8 + (n & 7);
+          bool gate_lane = (lane & 8) == 0;
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            float v = __uint_as_float(r[j]);
+            float u = __shfl_xor_sync(0xffffffffu, v, 8);
+            if (gate_lane && n < N && c0 + j < M)
+              ((bf16*)C)[(size_t)(c0 + j) * ldc + ocol] = __float2bfloat16_rn(v * (1.0f / (1.0f + __expf(-v))) * u);
+          }
+        } else {
+          bf16* dst = (bf16*)C + n;
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (n < N && c0 + j < M) dst[(size_t)(c0 + j) * ldc] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort) atomicExch(err, 2);
+}
+
+template <int BT, int STAGES, int EPI>
+static int tc_skinny_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, int K, int ldc, int out_f32,
+                            int ksplit, int* err, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (128 * TC_BK * 2 + BT * TC_BK * 2) + 1024 + 256;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_skinny_kernel<BT, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    raised = true;
+  }
+  dim3 grid((N + 127) / 128, ksplit);
+  return (int)sllm_launch(gemm_tc_skinny_kernel<BT, STAGES, EPI>, grid, dim3(TC_THREADS), smem, stream, mw, mx, C, M, N, K, ldc,
+                          out_f32, err);
+}
+
+// C[M,N] = A[M,K] B[N,K]^T for M <= 128. epilogue 0: C bfloat16, or float when out_f32; with
+// ksplit > 1 (float only) C is [ksplit][M][N] partial sums. epilogue 1: C[M,N/2] = silu(gate) * up.
+SLLM_EXPORT int sllm_gemm_tc_skinny_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                         int out_f32, int epilogue, int ksplit, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 128 || K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return SLLM_ERR_ARG;
+  if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_SWIGLU) return SLLM_ERR_ARG;
+  if (epilogue == TC_EPI_SWIGLU && ((N & 15) || out_f32 || ksplit != 1)) return SLLM_ERR_ARG;
+  if (ksplit < 1 || ksplit > (K + TC_BK - 1) / TC_BK || (ksplit > 1 && !out_f32)) return SLLM_ERR_ARG;
+  int bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  CUtensorMap mw, mx;
+  int rc = tc_make_map(&mw, B, N, K, ldb, 128);
+  if (rc) return rc;
+  rc = tc_make_map(&mx, A, M, K, lda, bt);
+  if (rc) return rc;
+#define SK_CASE(BT, ST)                                                                                                     \
+  return epilogue == TC_EPI_SWIGLU ? tc_skinny_launch<BT, ST, TC_EPI_SWIGLU>(mw, mx, C, M, N, K, ldc, 0, 1, err, stream)   \
+                                   : tc_skinny_launch<BT, ST, TC_EPI_STORE>(mw, mx, C, M, N, K, ldc, out_f32, ksplit, err, stream)
+  if (bt == 16) { SK_CASE(16, 8); }
+  if (bt == 32) { SK_CASE(32, 8); }
+  if (bt == 64) { SK_CASE(64, 8); }
+  SK_CASE(128, 6);
+#undef SK_CASE
+}

@@ -154,6 +154,35 @@ def test_gemm_tensor_core(kernel_sets, M, N, K):
     assert int(err) == 0
 
 
+@pytest.mark.parametrize("M, N, K", [(1, 128, 64), (17, 200, 72), (33, 264, 520), (64, 2048, 2048), (100, 1003 * 8, 136),
+                                     (128, 96, 8192), (16, 6144, 2048)])
+def test_gemm_tensor_core_few_rows(kernel_sets, M, N, K):
+    """The weight-stationary tcgen05 GEMM for at most 128 rows: bfloat16 and float outputs, float partial
+    sums of a split K (with more splits than some sizes have k-blocks to give), the SiLU-gate epilogue."""
+    tc = kernel_sets[torch.bfloat16].tensor_core
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a, w = dev(rand(M, K, seed=24), torch.bfloat16), dev(rand(N, K, seed=25, scale=0.05), torch.bfloat16)
+    want = plain.linear(f64(a), f64(w))
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    tc.gemm_skinny(a, w, out, err)
+    assert rel_err(out.cpu().float(), want) < TOL[torch.bfloat16]
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    tc.gemm_skinny(a, w, out32, err)
+    assert rel_err(out32.cpu(), want) < 3e-5
+    nkb = -(-K // 64)
+    for split in sorted({min(2, nkb), min(4, nkb), min(7, nkb)} - {1}):
+        parts = torch.full((split, M, N), float("nan"), dtype=torch.float32, device="cuda")
+        tc.gemm_skinny(a, w, parts, err)
+        assert rel_err(parts.cpu().double().sum(0), want) < 3e-5
+    if N % 16 == 0:
+        F = N // 2
+        tiled = w.view(2, F // 8, 8, K).permute(1, 0, 2, 3).reshape(N, K).contiguous()
+        h = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+        tc.gemm_skinny(a, tiled, h, err, swiglu=True)
+        assert rel_err(h.cpu().float(), plain.swiglu(want[:, :F], want[:, F:])) < TOL[torch.bfloat16]
+    assert int(err) == 0
+
+
 def test_gemm_small_m_refuses_what_it_cannot_take(kernel_sets):
     from scriptling_llm_lib_b200.csrc.bindings import KernelError
     dk = kernel_sets[torch.bfloat16].decode
