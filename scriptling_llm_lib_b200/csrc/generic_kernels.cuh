@@ -35,7 +35,7 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const W* __restri
 // range was split over blocks); they are added in a fixed order.
 // rows == nullptr: row r of y comes from row r of x, and x is updated in place (the residual sum).
 // rows != nullptr: row r of y comes from row rows[r]; x is left alone.
-template <typename A>
+template <typename A, int U>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta, int n_parts,
                                    size_t part_stride, const int* __restrict__ rows, const void* __restrict__ w,
                                    int w_f32, A* __restrict__ y, int d, float eps) {
@@ -52,20 +52,46 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
   A* yr = y + (size_t)r * d;
   bool update = (rows == nullptr) && (delta != nullptr);
   if ((d & 3) == 0) {
-    // four elements per thread and step: 16-byte accesses to the float rows
-    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
-      float4 v = *(const float4*)(xr + j);
-      if (dr) { float4 a = ld_dep4(dr + j); v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w; }
-      if (pr) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < n_parts; p++) {
-          float4 b = ld_dep4(pr + (size_t)p * part_stride + j);
-          a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-        }
-        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    // four elements per thread and access (16 bytes of the float rows), U accesses in flight before
+    // the first is used: with many rows the blocks are small and each thread walks further
+    for (int j0 = threadIdx.x * 4; j0 < d; j0 += blockDim.x * 4 * U) {
+      float4 v[U], a[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        int j = j0 + u * blockDim.x * 4;
+        v[u] = j < d ? *(const float4*)(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      *(float4*)(sm_row + j) = v;
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      if (dr) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          int j = j0 + u * blockDim.x * 4;
+          a[u] = j < d ? ld_dep4(dr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; u++) a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      if (pr) {
+        for (int p = 0; p < n_parts; p++) {
+#pragma unroll
+          for (int u = 0; u < U; u++) {
+            int j = j0 + u * blockDim.x * 4;
+            if (j < d) {
+              float4 b = ld_dep4(pr + (size_t)p * part_stride + j);
+              a[u].x += b.x; a[u].y += b.y; a[u].z += b.z; a[u].w += b.w;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        int j = j0 + u * blockDim.x * 4;
+        if (j < d) {
+          float4 t = make_float4(v[u].x + a[u].x, v[u].y + a[u].y, v[u].z + a[u].z, v[u].w + a[u].w);
+          *(float4*)(sm_row + j) = t;
+          ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        }
+      }
     }
     ss = block_sum(ss, red);
     float inv = 1.0f / sqrtf(ss / (float)d + eps);
