@@ -306,6 +306,7 @@ class DecodeKernels:
                   "sllm_attn_decode_rope_bf16"):
             getattr(self.lib, n).restype = c_int
         self.lib.sllm_attn_decode_scratch_bytes.restype = c_longlong
+        self.lib.sllm_attn_decode_uses_mma.restype = c_int
 
     @staticmethod
     def takes(a, w) -> bool:
@@ -321,14 +322,13 @@ class DecodeKernels:
 
     MAX_SPLITS = 64      # beyond this the merging block falls back to a slow loop
 
-    @staticmethod
-    def attention_splits(n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, pages: int, sm_count: int) -> int:
+    def attention_splits(self, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, pages: int, sm_count: int) -> int:
         """Over how many blocks a decode step splits each sequence's keys: enough blocks to fill the
-        GPU, never more than the longest sequence has pages. The grouped-query kernel (two or more
-        query heads per key/value head at widths 64 and 128) has fatter blocks: it wants about four
-        per SM and at least four pages each; the one-head kernel about six per SM."""
+        GPU, never more than the longest sequence has pages. The tensor-core kernel (grouped queries,
+        or very few sequences) has fatter blocks: it wants about four per SM and at least four
+        pages each; the one-head kernel about six per SM."""
         pairs = max(1, n_seqs * n_kv_heads)
-        if n_heads >= 2 * n_kv_heads and head_dim in (64, 128):
+        if self.lib.sllm_attn_decode_uses_mma(c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim)):
             want, cap = -(-4 * sm_count // pairs), max(1, pages // 4)
         else:
             want, cap = -(-6 * sm_count // pairs), pages

@@ -172,6 +172,8 @@ class Generator:
                     step_no += 1
                 t_ev[2].record()
                 t_ev[2].synchronize()
+                if hasattr(eng, "check_errors"):
+                    eng.check_errors()
                 pre_ms, dec_ms = t_ev[0].elapsed_time(t_ev[1]), t_ev[1].elapsed_time(t_ev[2])
             finally:
                 for s in seqs.values():

@@ -220,11 +220,20 @@ class Engine:
         else:
             ctx = self._context(entries, ids, lens, pos0, want_rows)
             logits = self._forward(ctx, want=bool(want_rows))
-            if T > B and int(self.err_flag) != 0:       # a prompt step is long enough to afford the read
-                raise StepError("a kernel reported an error during the step (a wait on the device ran out of time, or a "
-                                "token id was out of range)")
+            if T > B:                                   # a prompt step is long enough to afford the read
+                self.check_errors()
         self.cache.advance(growth)
         return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
+
+    def check_errors(self) -> None:
+        """Raises if a kernel of an earlier step reported an error (a wait on the device that ran out
+        of time, a token id out of range). Reading the flag waits for the stream, so replayed decode
+        steps do not do it themselves: the generation loop asks once per batch, trace replay after
+        every step, and every prompt step asks for itself."""
+        if int(self.err_flag) != 0:
+            self.err_flag.zero_()
+            raise StepError("a kernel reported an error during a step (a wait on the device ran out of time, or a "
+                            "token id was out of range)")
 
     def decode_step_device(self, sequences: list[Sequence], ids: torch.Tensor) -> torch.Tensor:
         """One token for each of `sequences`, the ids taken from an int32 device tensor (what the

@@ -356,7 +356,9 @@ def test_attn_prefill_tcgen05(kernel_sets, H, G, window, lens, pos0):
                                               # two or more query heads per key/value head at widths 64 and 128: the
                                               # tensor-core variant; 12 and 40 heads per group use its upper rows and loop
                                               (32, 8, 64, None), (9, 3, 64, 100), (6, 3, 128, None), (24, 2, 64, 17),
-                                              (40, 1, 128, 500)])
+                                              (40, 1, 128, 500),
+                                              # one head per group, few (sequence, head) pairs: the same variant
+                                              (4, 4, 64, None), (8, 8, 128, 70)])
 @pytest.mark.parametrize("n_split", [1, 3, 16, 40, 70])      # 70: more than the merging block weighs in one pass
 def test_attn_decode(kernel_sets, H, G, hd, window, n_split):
     dk = kernel_sets[torch.bfloat16].decode
