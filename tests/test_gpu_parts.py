@@ -294,3 +294,182 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path, dtype):
         rows.append(f64(eng.step([StepEntry(s, [t], [0])])))
     s.close()
     assert rel_err(torch.cat(rows), want) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- a routed feed-forward and another position encoding
+def register_routed_toy():
+    """Two more parts defined here and registered without a change to the library: a feed-forward
+    that sends each token to the one expert (of three dense SiLU-gated ones) its router scores
+    highest, weighted by that score's sigmoid; and a position encoding that rotates by the angle
+    f_i * log(1 + position) instead of f_i * position (its own table, the library's kernels)."""
+    from scriptling_llm_lib_b200.config import ConfigError, register_architecture
+    from scriptling_llm_lib_b200.engine.layout import ModelLayout, sequential_schedule
+    from scriptling_llm_lib_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, LayerSpec, Linear, PartSpec, PositionEncoding
+    from scriptling_llm_lib_b200.parts.feedforward import SwiGLU
+
+    class TopOneExperts(FeedForward):
+        graph_safe = False                       # the routing decision is read on the host
+
+        def __init__(self, hidden, intermediate, n_experts, prefix):
+            self.hidden = hidden
+            self.router = Linear([prefix + "router"], [n_experts], hidden)
+            self.experts = [SwiGLU(hidden, intermediate, f"{prefix}e{e}.gate", f"{prefix}e{e}.up", f"{prefix}e{e}.down")
+                            for e in range(n_experts)]
+
+        def tensor_specs(self):
+            return self.router.tensor_specs() + [s for e in self.experts for s in e.tensor_specs()]
+
+        def bind(self, tensors, dtype, device):
+            self.router.bind(tensors, dtype, device)
+            for e in self.experts:
+                e.bind(tensors, dtype, device)
+
+        def forward(self, x, ctx):
+            scores = self.router.forward(x, ctx, out_dtype=torch.float32)          # router logits in 32-bit
+            choice = scores.argmax(dim=1)
+            gate = torch.sigmoid(scores.gather(1, choice[:, None]))
+            out = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+            for e, expert in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    y = expert.forward(x[rows].contiguous(), ctx)
+                    y = y.float().sum(0) if y.dim() == 3 else y.float()
+                    out[rows] = y * gate[rows]
+            return out.to(x.dtype)
+
+    class LogRotary(PositionEncoding):
+        def __init__(self, head_dim, theta):
+            self.head_dim, self.theta = head_dim, theta
+            self.cos_sin = None
+
+        def prepare(self, max_positions, device):
+            inv = 1.0 / np.power(self.theta, 2.0 * np.arange(self.head_dim // 2, dtype=np.float64) / self.head_dim)
+            ang = np.log1p(np.arange(max_positions, dtype=np.float64))[:, None] * inv[None, :]
+            self.cos_sin = torch.from_numpy(np.stack([np.cos(ang), np.sin(ang)], -1).astype(np.float32)).to(device)
+
+        def decode_fusion(self):
+            return self.cos_sin, self.head_dim, False
+
+        def apply(self, qkv, ctx, n_heads, n_kv, kpages, vpages, block_table):
+            ctx.kernels.rope_kv_write(qkv, ctx.tok_pos, ctx.tok_seq, block_table, self.cos_sin, kpages, vpages, n_heads, n_kv,
+                                      self.head_dim, self.head_dim, False)
+
+    FEED_FORWARDS.register("top_one_experts", TopOneExperts, replace=True)
+    POSITION_ENCODINGS.register("log_rotary", LogRotary, replace=True)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        hidden_size: int
+        vocab_size: int
+        intermediate_size: int
+        max_position_embeddings: int
+
+        @classmethod
+        def from_dict(cls, raw, where="config.json"):
+            try:
+                return cls(raw["hidden_size"], raw["vocab_size"], raw["intermediate_size"], raw["max_position_embeddings"])
+            except KeyError as e:
+                raise ConfigError(f"{where}: required key {e} is missing") from None
+
+        def to_json_dict(self):
+            return {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                    "intermediate_size": self.intermediate_size, "max_position_embeddings": self.max_position_embeddings}
+
+    def layout(cfg):
+        def norm(name):
+            return PartSpec("rmsnorm", dict(width=cfg.hidden_size, eps=1e-6, weight_name=name))
+        pos = PartSpec("log_rotary", dict(head_dim=32, theta=100.0))
+        attn = lambda i: PartSpec("attention", dict(hidden=cfg.hidden_size, n_heads=3, n_kv_heads=1, head_dim=32, position=pos,
+                                                    q_name=f"l{i}.q", k_name=f"l{i}.k", v_name=f"l{i}.v", o_name=f"l{i}.o"))
+        dense = PartSpec("swiglu", dict(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size,
+                                        gate_name="l0.gate", up_name="l0.up", down_name="l0.down"))
+        routed = PartSpec("top_one_experts", dict(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size, n_experts=3, prefix="l1."))
+        layers = (LayerSpec(attn(0), dense, norm("l0.n1"), norm("l0.n2")),
+                  LayerSpec(attn(1), routed, norm("l1.n1"), norm("l1.n2")))      # different feed-forwards in different layers
+        return ModelLayout(cfg.vocab_size, cfg.hidden_size, cfg.max_position_embeddings, "embed", layers,
+                           sequential_schedule(2), norm("final"), "head")
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, layout, replace=True)
+    return RoutedConfig, layout
+
+
+def routed_plain_logits(w, ids, act_round):
+    """The routed toy model in plain float64, whole sequence; `act_round` rounds where the engine's
+    activations are stored (identity in 32-bit), so that a near-tie between two experts' scores is
+    decided on the same numbers."""
+    S = len(ids)
+    pos = torch.arange(S)
+    logpos = torch.log1p(pos.to(torch.float64))
+    inv = plain.rope_inv_freq(32, 100.0)
+    x = w["embed"][torch.as_tensor(ids)]
+    margins = []
+    for i in range(2):
+        n = act_round(plain.rms_norm(x, w[f"l{i}.n1"], 1e-6))
+        q = plain.apply_rope(act_round(plain.linear(n, w[f"l{i}.q"])).view(S, 3, 32), logpos, inv, "half")
+        k = plain.apply_rope(act_round(plain.linear(n, w[f"l{i}.k"])).view(S, 1, 32), logpos, inv, "half")
+        v = act_round(plain.linear(n, w[f"l{i}.v"])).view(S, 1, 32)
+        a = act_round(plain.attention(act_round(q), act_round(k), v, pos, pos).reshape(S, 96))
+        x = x + plain.linear(a, w[f"l{i}.o"])
+        n = act_round(plain.rms_norm(x, w[f"l{i}.n2"], 1e-6))
+        if i == 0:
+            h = act_round(plain.swiglu(plain.linear(n, w["l0.gate"]), plain.linear(n, w["l0.up"])))
+            x = x + plain.linear(h, w["l0.down"])
+        else:
+            scores = plain.linear(n, w["l1.router"])
+            top2 = scores.topk(2, dim=1).values
+            margins.append((top2[:, 0] - top2[:, 1]).min())
+            choice = scores.argmax(dim=1)
+            y = torch.zeros_like(x)
+            for e in range(3):
+                rows = (choice == e).nonzero().flatten()
+                h = act_round(plain.swiglu(plain.linear(n[rows], w[f"l1.e{e}.gate"]), plain.linear(n[rows], w[f"l1.e{e}.up"])))
+                y[rows] = plain.linear(h, w[f"l1.e{e}.down"]) * torch.sigmoid(scores[rows, e])[:, None]
+            x = x + y
+    return plain.linear(plain.rms_norm(x, w["final"], 1e-6), w["head"]), min(margins)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
+    from scriptling_llm_lib_b200.engine.model import DecoderModel
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    from scriptling_llm_lib_b200.weights import write_random_model
+    RoutedConfig, layout = register_routed_toy()
+    cfg = RoutedConfig(hidden_size=48, vocab_size=101, intermediate_size=40, max_position_embeddings=256)
+    d = write_random_model(cfg, DecoderModel(layout(cfg)).tensor_specs(), 11, tmp_path / "routed")
+    from scriptling_llm_lib_b200.weights import write_safetensors
+    w = plain.read_safetensors(d / "model.safetensors")
+    w["l1.router"] = w["l1.router"] * 40.0                          # routing decisions that do not hang on rounding
+    write_safetensors(d / "model.safetensors", {k: v.to(torch.bfloat16) for k, v in w.items()})
+    eng = Engine.from_folder(d, dtype, max_tokens=1024, max_seqs=3)
+    assert not eng.use_graphs                                       # the routed feed-forward reads the host: no replay
+    w = plain.read_safetensors(d / "model.safetensors")
+    act_round = (lambda t: t) if dtype == "float32" else (lambda t: t.to(torch.bfloat16).to(torch.float64))
+    reqs = [random_ids(n, 101, 730 + n) for n in (60, 9, 35)]           # seeds with routing margins above 0.06
+    want, margins = zip(*[routed_plain_logits(w, r, act_round) for r in reqs])
+    tol = TOL[dtype]
+    # whole; then a batch of unequal prompts followed by single tokens
+    for r, wl in zip(reqs, want):
+        s = eng.open()
+        assert rel_err(f64(eng.step([StepEntry(s, r, list(range(len(r))))])), wl) < tol
+        s.close()
+    seqs = [eng.open() for _ in reqs]
+    plens = [30, 9, 1]
+    got = {i: [] for i in range(3)}
+    out = eng.step([StepEntry(s, reqs[i][:plens[i]], list(range(plens[i]))) for i, s in enumerate(seqs)])
+    off = 0
+    for i in range(3):
+        got[i].append(f64(out[off:off + plens[i]]))
+        off += plens[i]
+    pos = dict(enumerate(plens))
+    live = {i: s for i, s in enumerate(seqs) if pos[i] < len(reqs[i])}
+    while live:
+        order = sorted(live)
+        out = eng.step([StepEntry(live[i], [reqs[i][pos[i]]], [0]) for i in order])
+        for j, i in enumerate(order):
+            got[i].append(f64(out[j:j + 1]))
+            pos[i] += 1
+            if pos[i] == len(reqs[i]):
+                live.pop(i).close()
+    for i in range(3):
+        assert rel_err(torch.cat(got[i]), want[i]) < tol, f"request {i}"
+    assert min(margins) > 0.05                                       # no routing decision hung on rounding
