@@ -187,6 +187,7 @@ class TensorCoreGemm:
         self.lib = load_library("gemm_tcgen05")
         self.lib.sllm_gemm_tc_bf16.restype = c_int
         self.lib.sllm_gemm_tc_skinny_bf16.restype = c_int
+        self.lib.sllm_gemm_tc_qkv_rope_bf16.restype = c_int
 
     @staticmethod
     def takes(a, w) -> bool:
@@ -213,6 +214,26 @@ class TensorCoreGemm:
             c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
             c_int(2 if accumulate else (1 if swiglu else 0)), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
 
+
+    QKV_ROPE_HEAD_DIMS = (64, 128)
+
+    def gemm_qkv_rope(self, a, w, qkv, err_flag, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv,
+                      head_dim, rot, interleaved):
+        """qkv[:, :n_heads*head_dim] = rotated queries of a @ w^T (w rows: q | k | v heads); the rotated
+        keys and the values go to each row's place in the cache pages and not to `qkv`."""
+        M, K = a.shape
+        N = (n_heads + 2 * n_kv) * head_dim
+        if tuple(w.shape) != (N, K) or qkv.shape[0] != M or qkv.shape[1] < n_heads * head_dim or qkv.stride(1) != 1:
+            raise KernelError(f"gemm_qkv_rope shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, qkv {tuple(qkv.shape)}")
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16:
+            raise KernelError("gemm_qkv_rope works in bfloat16")
+        _check(self.lib.sllm_gemm_tc_qkv_rope_bf16(
+            c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(qkv.data_ptr()), c_int(M), c_int(K), c_int(a.stride(0)),
+            c_int(w.stride(0)), c_int(qkv.stride(0)), _ptr(tok_pos, torch.int32, "tok_pos"), _ptr(tok_seq, torch.int32, "tok_seq"),
+            _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), _ptr(cos_sin, torch.float32, "cos_sin"),
+            _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"), c_int(n_heads), c_int(n_kv),
+            c_int(head_dim), c_int(rot), c_int(1 if interleaved else 0), _ptr(err_flag, torch.int32, "err_flag"), _stream()),
+            "gemm_qkv_rope")
 
     SKINNY_MAX_M = 128
 

@@ -23,6 +23,45 @@
 #define TC_EPI_STORE 0
 #define TC_EPI_SWIGLU 1
 #define TC_EPI_RESIDUAL 2   // C is the float residual stream: C += A B^T
+#define TC_EPI_QKV_ROPE 3   // C's columns are [q heads | k heads | v heads]: rotate q and k, put k and v into the cache
+
+// What the q|k|v epilogue needs besides the product: where each row (token) sits, the rotary
+// table, the paged cache of the layer. Queries are rotated and written to C; keys are rotated and
+// written, with the values, at the token's place in the cache (and not to C): the work of the
+// rotary kernel (float32_ops.go:174-188, model_f32.go:445-448) without reading q|k|v again.
+struct TcRope {
+  const int* tok_pos;       // [M] position of each row in its sequence
+  const int* tok_seq;       // [M] which row of the block table
+  const int* block_table;   // [sequences][max_pages]
+  int max_pages;
+  const float2* cs;         // [positions][rot/2] (cos, sin)
+  bf16* kpages;             // [pages][G][PAGE][hd]
+  bf16* vpages;
+  int H, G, hd, rot, interleaved;
+};
+
+__device__ __forceinline__ float bf16_round(uint32_t f32_bits) {
+  return __bfloat162float(__float2bfloat16_rn(__uint_as_float(f32_bits)));
+}
+
+// 32 consecutive columns of one row, already final: to C (a query head), or to the row's place in
+// the key or value pages.
+__device__ __forceinline__ void qkv_store32(const TcRope& rp, void* C, int ldc, int row, int col, size_t cache_row,
+                                            const float (&v)[32]) {
+  int hidx = col / rp.hd, d0 = col % rp.hd;
+  bf16* dst;
+  if (hidx < rp.H) dst = (bf16*)C + (size_t)row * ldc + col;
+  else if (hidx < rp.H + rp.G) dst = rp.kpages + (cache_row + (size_t)(hidx - rp.H) * SLLM_PAGE) * rp.hd + d0;
+  else dst = rp.vpages + (cache_row + (size_t)(hidx - rp.H - rp.G) * SLLM_PAGE) * rp.hd + d0;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+    o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+    *(uint4*)(dst + j) = o;
+  }
+}
 
 // Writes 32 consecutive accumulator columns of one row. EPI_STORE: as they are; EPI_SWIGLU: the 32
 // columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2).
@@ -104,7 +143,7 @@ __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, i
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ C,
-               int M, int N, int K, int ldc, int out_f32, int* __restrict__ err) {
+               int M, int N, int K, int ldc, int out_f32, int* __restrict__ err, const TcRope rp) {
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -192,6 +231,78 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       int row = m0 + q * 32 + lane;
+      if constexpr (EPI == TC_EPI_QKV_ROPE) {
+        const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN);
+        int pos = 0;
+        size_t cache_row = 0;                  // (page * G) * PAGE + place in the page; + g * PAGE, times hd, is the row's place
+        if (row < M) {
+          pos = rp.tok_pos[row];
+          int page = rp.block_table[(size_t)rp.tok_seq[row] * rp.max_pages + pos / SLLM_PAGE];
+          cache_row = (size_t)page * rp.G * SLLM_PAGE + (pos % SLLM_PAGE);
+        }
+        const float2* csr = rp.cs + (size_t)pos * (rp.rot >> 1);
+        if (rp.interleaved) {
+          // pairs of adjacent columns: a chunk of 32 columns holds 16 whole pairs
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (n0 + c0 >= N) break;
+            uint32_t r[32];
+            tmem_ld32(trow + (uint32_t)c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < M) {
+              int col = n0 + c0, d0 = col % rp.hd;
+              bool rotate = col / rp.hd < rp.H + rp.G;
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float x0 = bf16_round(r[j]), x1 = bf16_round(r[j + 1]);
+                if (rotate && d0 + j < rp.rot) {
+                  float2 cs = csr[(d0 + j) >> 1];
+                  v[j] = x0 * cs.x - x1 * cs.y;
+                  v[j + 1] = x0 * cs.y + x1 * cs.x;
+                } else {
+                  v[j] = x0;
+                  v[j + 1] = x1;
+                }
+              }
+              qkv_store32(rp, C, ldc, row, col, cache_row, v);
+            }
+            __syncwarp();
+          }
+        } else {
+          // pairs (i, i + hd/2), the whole head rotated: two chunks of 32 columns half a head apart
+          const int half = rp.hd >> 1;
+#pragma unroll 1
+          for (int h0 = 0; h0 < BN; h0 += rp.hd) {
+            if (n0 + h0 >= N) break;
+#pragma unroll 1
+            for (int i0 = 0; i0 < half; i0 += 32) {
+              uint32_t r0[32], r1[32];
+              tmem_ld32(trow + (uint32_t)(h0 + i0), r0);
+              tmem_ld32(trow + (uint32_t)(h0 + half + i0), r1);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+              if (row < M) {
+                int col = n0 + h0 + i0;
+                bool rotate = col / rp.hd < rp.H + rp.G;
+                float v0[32], v1[32];
+                const float4* c4 = (const float4*)(csr + i0);     // (cos, sin) of two pairs per load
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                  float4 cs = rotate ? c4[j >> 1] : make_float4(1.f, 0.f, 1.f, 0.f);
+                  float a0 = bf16_round(r0[j]), b0 = bf16_round(r1[j]), a1 = bf16_round(r0[j + 1]), b1 = bf16_round(r1[j + 1]);
+                  v0[j] = a0 * cs.x - b0 * cs.y;
+                  v1[j] = a0 * cs.y + b0 * cs.x;
+                  v0[j + 1] = a1 * cs.z - b1 * cs.w;
+                  v1[j + 1] = a1 * cs.w + b1 * cs.z;
+                }
+                qkv_store32(rp, C, ldc, row, col, cache_row, v0);
+                qkv_store32(rp, C, ldc, row, col + half, cache_row, v1);
+              }
+              __syncwarp();
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= N) break;               // uniform over the warp
@@ -199,6 +310,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
+      }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -216,7 +328,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ------------------------------------------------------------------ host side
 template <int BN, int STAGES, int EPI>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int out_f32,
-                     int* err, cudaStream_t stream) {
+                     int* err, cudaStream_t stream, const TcRope& rp = TcRope{}) {
   constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
   static bool raised = false;
   if (!raised) {
@@ -232,7 +344,7 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int 
   }
   int n_tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
   dim3 grid(n_tiles < sms ? n_tiles : sms);
-  gemm_tc_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err);
+  gemm_tc_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err, rp);
   SLLM_RETURN_LAST();
 }
 
@@ -259,6 +371,28 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
                : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);
   return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream)
              : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
+}
+
+// C[M, (H + 2G) hd] = A[M,K] B^T with the q|k|v epilogue: rotated queries to C (bfloat16, row stride
+// ldc), rotated keys and raw values to the rows' places in the cache. Pairing "half" needs the whole
+// head rotated (rot == hd) and hd 64 or 128; "interleaved" any even rot.
+SLLM_EXPORT int sllm_gemm_tc_qkv_rope_bf16(const void* A, const void* B, void* C, int M, int K, int lda, int ldb, int ldc,
+                                           const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
+                                           const void* cos_sin, void* kpages, void* vpages, int H, int G, int hd, int rot,
+                                           int interleaved, int* err, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  int N = (H + 2 * G) * hd;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
+    return SLLM_ERR_ARG;
+  if (H < 1 || G < 1 || (hd != 64 && hd != 128) || rot < 2 || rot > hd || (rot & 1) || (!interleaved && rot != hd)) return SLLM_ERR_ARG;
+  if (!tok_pos || !tok_seq || !block_table || !cos_sin || !kpages || !vpages || ((uintptr_t)cos_sin & 15)) return SLLM_ERR_ARG;
+  CUtensorMap ma, mb;
+  int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
+  if (rc) return rc;
+  rc = tc_make_map(&mb, B, N, K, ldb, 256);
+  if (rc) return rc;
+  TcRope rp{tok_pos, tok_seq, block_table, max_pages, (const float2*)cos_sin, (bf16*)kpages, (bf16*)vpages, H, G, hd, rot, interleaved};
+  return tc_launch<256, 4, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp);
 }
 
 // ------------------------------------------------------------------ few rows: the weights are the 128-row operand

@@ -55,11 +55,21 @@ class Attention(Mixer):
         kpages, vpages, block_table = ctx.unit_kv(unit)
         fast_decode = ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
         fusion = getattr(self.position, "decode_fusion", lambda: None)() if fast_decode else None
-        qkv = (self.qkv if writes else self.q_only).forward(x, ctx)
-        if fusion is None:
-            if writes:
+        tc = ctx.kernels.tensor_core if x.dtype == torch.bfloat16 else None
+        fused_product = None
+        if (tc is not None and writes and not fast_decode and x.shape[0] > tc.SKINNY_MAX_M and self.head_dim in tc.QKV_ROPE_HEAD_DIMS
+                and self.qkv.weight.dtype == torch.bfloat16 and tc.takes(x, self.qkv.weight)):
+            fused_product = getattr(self.position, "product_fusion", lambda: None)()
+        if fused_product is not None:
+            # a long prompt step: the q|k|v product rotates and fills the cache in its own epilogue
+            qkv = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
+            tc.gemm_qkv_rope(x, self.qkv.weight, qkv, ctx.err_flag, ctx.tok_pos, ctx.tok_seq, block_table, fused_product[0],
+                             kpages, vpages, self.n_heads, self.n_kv_heads, self.head_dim, fused_product[1], fused_product[2])
+        else:
+            qkv = (self.qkv if writes else self.q_only).forward(x, ctx)
+            if fusion is None and writes:
                 self.position.apply(qkv, ctx, self.n_heads, self.n_kv_heads, kpages, vpages, block_table)
-            else:
+            elif fusion is None:
                 self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
         attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
         if fast_decode:

@@ -66,6 +66,14 @@ class RotaryEncoding(PositionEncoding):
             return None
         return self.cos_sin, self.rotary_dim, interleaved
 
+    def product_fusion(self):
+        """(table, rotary width, interleaved) when the q|k|v product's own epilogue can rotate and fill
+        the cache (its 32-column chunks must hold whole pairs, or both halves of a fully rotated head)."""
+        interleaved = self.pairing == "interleaved"
+        if self.cos_sin is None or (not interleaved and self.rotary_dim != self.head_dim):
+            return None
+        return self.cos_sin, self.rotary_dim, interleaved
+
     def apply(self, qkv, ctx, n_heads: int, n_kv: int, kpages, vpages, block_table) -> None:
         """Rotate the q heads of `qkv` in place; rotate its k heads and store them with the v heads at
         each token's place in the cache (n_kv == 0: queries only)."""

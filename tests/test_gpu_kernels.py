@@ -183,6 +183,45 @@ def test_gemm_tensor_core_few_rows(kernel_sets, M, N, K):
     assert int(err) == 0
 
 
+@pytest.mark.parametrize("H, G, hd, rot, pairing", [(4, 2, 64, 64, "half"), (3, 1, 128, 128, "half"), (5, 5, 64, 24, "interleaved"),
+                                                    (2, 1, 128, 128, "interleaved")])
+def test_gemm_qkv_with_rotation_and_cache_write(kernel_sets, H, G, hd, rot, pairing):
+    """The q|k|v product whose epilogue rotates queries and keys and puts keys and values into the pages:
+    against product, rounding, rotation in plain float64; rows of two sequences at scattered positions."""
+    from scriptling_llm_lib_b200.parts.rotary import RotaryEncoding
+    tc = kernel_sets[torch.bfloat16].tensor_core
+    enc = RotaryEncoding(hd, rot, 54321.0, None, pairing)
+    enc.prepare(1024, "cuda")
+    table, r, inter = enc.product_fusion()
+    lens, pos0 = [150, 70], [60, 300]
+    T, K, N = sum(lens), 136, (H + 2 * G) * hd
+    a, w = dev(rand(T, K, seed=41), torch.bfloat16), dev(rand(N, K, seed=42, scale=0.1), torch.bfloat16)
+    raw = plain.linear(f64(a), f64(w)).to(torch.bfloat16).to(torch.float64)          # the product, stored in bfloat16
+    inv = plain.rope_inv_freq(rot, 54321.0)
+    tok_pos = torch.cat([torch.arange(p, p + n) for n, p in zip(lens, pos0)])
+    tok_seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)])
+    q_want = plain.apply_rope(raw[:, :H * hd].view(T, H, hd), tok_pos, inv, pairing).reshape(T, H * hd)
+    k_want = plain.apply_rope(raw[:, H * hd:(H + G) * hd].view(T, G, hd), tok_pos, inv, pairing)
+    v_want = raw[:, (H + G) * hd:].view(T, G, hd)
+    nan = lambda n: torch.full((n, G, hd), float("nan"))
+    kp, vp, bt = paged([nan(p + n) for n, p in zip(lens, pos0)], [nan(p + n) for n, p in zip(lens, pos0)],
+                       [p + n for n, p in zip(lens, pos0)], dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qkv = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    tc.gemm_qkv_rope(a, w, qkv, err, dev(tok_pos, torch.int32), dev(tok_seq, torch.int32), bt, table, kp, vp, H, G, hd, r, inter)
+    assert int(err) == 0
+    assert rel_err(qkv.cpu().float(), q_want) < TOL[torch.bfloat16]
+    row = 0
+    for b, (n, p) in enumerate(zip(lens, pos0)):
+        for t in (0, 1, n // 2, n - 1):
+            pos = p + t
+            pg = int(bt[b, pos // PAGE])
+            assert rel_err(f64(kp[pg, :, pos % PAGE]), k_want[row + t]) < TOL[torch.bfloat16]
+            assert rel_err(f64(vp[pg, :, pos % PAGE]), v_want[row + t]) < 1e-6
+        assert torch.isnan(kp[int(bt[b, 0]), :, 0].float()).all() if p > 0 else True     # places before the step untouched
+        row += n
+
+
 def test_gemm_small_m_refuses_what_it_cannot_take(kernel_sets):
     from scriptling_llm_lib_b200.csrc.bindings import KernelError
     dk = kernel_sets[torch.bfloat16].decode

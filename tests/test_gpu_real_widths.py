@@ -1,5 +1,6 @@
 """The SmolLM2-1.7B layer sizes (hidden 2048, 32 heads of 64, intermediate 8192, vocabulary 49152,
-theta 130000, tied head) with two layers and random weights: the widths at which the tensor-core
+theta 130000, tied head) and a Llama-3 style shape (grouped queries, heads of 128, rescaled rotary
+frequencies), each with two layers and random weights: the widths at which the tensor-core
 kernels of the bfloat16 path and the tiled kernels of the 32-bit path are actually used, whole
 prompt, then token by token, in a batch of unequal lengths, against the plain implementation."""
 import pytest
@@ -17,11 +18,24 @@ REAL = {
 }
 
 
-@pytest.fixture(scope="module")
-def real_model(tmp_path_factory):
-    d = make_model_dir(tmp_path_factory.mktemp("real"), REAL, 7)
+# Llama-3 style: grouped queries (4 query heads per key/value head), heads of 128, rescaled rotary
+# frequencies, a head of its own, a vocabulary that is no multiple of 128
+GROUPED = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 1024,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 2816,
+    "vocab_size": 32003, "rope_theta": 500000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 8192, "hidden_act": "silu",
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+}
+
+
+@pytest.fixture(scope="module", params=["mha64", "gqa128"])
+def real_model(request, tmp_path_factory):
+    raw = REAL if request.param == "mha64" else GROUPED
+    d = make_model_dir(tmp_path_factory.mktemp("real"), raw, 7)
     pm = plain_model(d)
-    reqs = [random_ids(n, 49152, 900 + n) for n in (300, 70, 1)]
+    reqs = [random_ids(n, raw["vocab_size"], 900 + n) for n in (300, 70, 1)]
     return d, reqs, [pm.logits(r) for r in reqs]
 
 
