@@ -229,7 +229,8 @@ def main():
     from scriptling_llm_lib_b200.engine.step import StepEntry
 
     pk = peaks()
-    cfg_raw = dict(shape, num_hidden_layers=args.layers)
+    cfg_raw = dict(shape, num_hidden_layers=args.layers,
+                   max_position_embeddings=max(shape["max_position_embeddings"], args.context + 64))
     nums = model_numbers(cfg_raw, args.layers)
     tmp = tempfile.mkdtemp(prefix="sllm_bench_")
     model_dir = os.path.join(tmp, "model")
