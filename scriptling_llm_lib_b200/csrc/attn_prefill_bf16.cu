@@ -73,7 +73,9 @@ __global__ void __launch_bounds__(FA_THREADS) attn_prefill_kernel(FaArgs p) {
   const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(fa_smem);
   const uint32_t sK = sQ + FA_BQ * HD * 2, sV = sK + 2 * TILE;
 
-  int b = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
+  // heads vary fastest, query tiles from the last (most keys) to the first: blocks start in the order
+  // of their length over the whole grid, so the long ones are not left for the end
+  int b = blockIdx.z, h = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
   int row0 = p.seq_start[b], S = p.seq_start[b + 1] - row0;
   int r0 = qt * FA_BQ;
   if (r0 >= S) return;
@@ -242,7 +244,7 @@ static int fa_launch(const FaArgs& a, int B, int max_new, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     raised = true;
   }
-  dim3 grid((max_new + FA_BQ - 1) / FA_BQ, a.H, B);
+  dim3 grid(a.H, (max_new + FA_BQ - 1) / FA_BQ, B);
   attn_prefill_kernel<HD><<<grid, FA_THREADS, smem, stream>>>(a);
   SLLM_RETURN_LAST();
 }

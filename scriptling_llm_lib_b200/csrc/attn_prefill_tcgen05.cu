@@ -61,7 +61,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 1 + 1 + 1);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
 
-  int b = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;     // long tiles first
+  // heads vary fastest, query tiles from the last (most keys) to the first: blocks start in the order
+  // of their length over the whole grid, so the long ones are not left for the end
+  int b = blockIdx.z, h = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
   int row0 = p.seq_start[b], S = p.seq_start[b + 1] - row0;
   int r0 = qt * FT_BQ;
   if (r0 >= S) return;
@@ -306,7 +308,7 @@ SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* 
     raised = true;
   }
   FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err};
-  dim3 grid((max_new + FT_BQ - 1) / FT_BQ, H, B);
+  dim3 grid(H, (max_new + FT_BQ - 1) / FT_BQ, B);
   attn_prefill_tc_kernel<<<grid, FT_THREADS, smem, stream>>>(mq, mk, mv, a);
   SLLM_RETURN_LAST();
 }
