@@ -69,3 +69,28 @@ def test_real_widths(real_model, dtype):
     for i, w in enumerate(want):
         assert rel_err(torch.cat(rows[i]), w) < tol, f"request {i}"
     assert int(eng.err_flag) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_twenty_sequences_decode_together(real_model, dtype):
+    """A decode step of 20 rows (the few-rows tensor-core products, replayed as a graph): unequal short
+    prompts in one step, then six tokens each, every row against the plain implementation."""
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    d, _, _ = real_model
+    pm = plain_model(d)
+    V = pm.cfg["vocab_size"]
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    reqs = [random_ids(3 + (7 * i) % 38 + 6, V, 1200 + i) for i in range(20)]
+    want = [pm.logits(r) for r in reqs]
+    eng = Engine.from_folder(d, dtype, max_tokens=20 * 64, max_seqs=20)
+    seqs = [eng.open() for _ in reqs]
+    heads = [len(r) - 6 for r in reqs]
+    out = eng.step([StepEntry(s, r[:h], [h - 1]) for s, r, h in zip(seqs, reqs, heads)]).cpu().double()
+    rows = [[out[i:i + 1]] for i in range(20)]
+    for t in range(6):
+        out = eng.step([StepEntry(s, [r[h + t]], [0]) for s, r, h in zip(seqs, reqs, heads)]).cpu().double()
+        for i in range(20):
+            rows[i].append(out[i:i + 1])
+    for i, (w, h) in enumerate(zip(want, heads)):
+        assert rel_err(torch.cat(rows[i]), w[h - 1:]) < tol, f"request {i}"
+    assert int(eng.err_flag) == 0
