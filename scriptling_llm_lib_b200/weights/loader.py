@@ -20,6 +20,7 @@ from .safetensors_io import SafetensorsError, SafetensorsFile
 from .spec import TensorSpec
 
 WEIGHTS_FILE = "model.safetensors"
+INDEX_FILE = "model.safetensors.index.json"     # {"weight_map": {tensor name: file name}}: the tensors are spread over several files
 
 
 class WeightError(ValueError):
@@ -56,23 +57,35 @@ def stored_to_kept(t: torch.Tensor, compute_dtype: torch.dtype) -> torch.Tensor:
 
 def load_weights(model_dir, specs: Iterable[TensorSpec], device, compute_dtype: torch.dtype,
                  ignore: Iterable[str] = ()) -> dict[str, torch.Tensor]:
-    """Read the tensors named by `specs` from `model_dir`/model.safetensors onto `device`.
+    """Read the tensors named by `specs` from `model_dir`/model.safetensors (or, where that file is
+    absent, from the files that model.safetensors.index.json names) onto `device`.
 
     `ignore`: names that may be present without being used (an output head beside a tied
     embedding). Raises WeightError listing every fault at once."""
     path = Path(model_dir) / WEIGHTS_FILE
-    if not path.is_file():
-        raise WeightError(path, [s.name for s in specs if not s.optional], [], [], [])
     specs = list(specs)
+    files = [path]
+    if not path.is_file():
+        index = Path(model_dir) / INDEX_FILE
+        if not index.is_file():
+            raise WeightError(path, [s.name for s in specs if not s.optional], [], [], [])
+        path, files = index, _shards(index)
     ignore = set(ignore)
-    with SafetensorsFile(path) as f:
+    opened = [SafetensorsFile(p) for p in files]
+    try:
+        entries, owner = {}, {}
+        for f in opened:
+            for n, e in f.entries.items():
+                if n in entries:
+                    raise SafetensorsError(f"{path}: tensor {n!r} is stored in two files")
+                entries[n], owner[n] = e, f
         wanted = {s.name: s for s in specs}
-        missing = [s.name for s in specs if s.name not in f.entries and not s.optional]
-        unexpected = [n for n in f.entries if n not in wanted and n not in ignore]
+        missing = [s.name for s in specs if s.name not in entries and not s.optional]
+        unexpected = [n for n in entries if n not in wanted and n not in ignore]
         misshapen, bad_dtype = [], []
         for s in specs:
-            if s.name in f.entries:
-                tdt, shape, _, _ = f.entries[s.name]
+            if s.name in entries:
+                tdt, shape, _, _ = entries[s.name]
                 if tuple(shape) != tuple(s.shape):
                     misshapen.append((s.name, tuple(shape), tuple(s.shape)))
                 if tdt not in _FLOATS + _INTS or (s.init != "integer_table" and tdt not in _FLOATS):
@@ -81,12 +94,30 @@ def load_weights(model_dir, specs: Iterable[TensorSpec], device, compute_dtype: 
             raise WeightError(path, missing, unexpected, misshapen, bad_dtype)
         out = {}
         for s in specs:
-            if s.name not in f.entries:
+            if s.name not in entries:
                 continue
-            t = f.tensor(s.name)
+            t = owner[s.name].tensor(s.name)
             # copy to the device first where that is lossless and smaller, then widen there
             out[s.name] = stored_to_kept(t.to(device, copy=True), compute_dtype).contiguous()
+    finally:
+        for f in opened:
+            f.close()
     return out
+
+
+def _shards(index: Path) -> list[Path]:
+    """The files an index names, in the order of their first mention."""
+    import json
+    try:
+        weight_map = json.loads(index.read_text())["weight_map"]
+        names = list(dict.fromkeys(str(v) for v in weight_map.values()))
+    except (ValueError, KeyError, AttributeError, TypeError) as e:
+        raise SafetensorsError(f"{index}: not an index of weight files ({e})") from None
+    files = [index.parent / n for n in names]
+    for f in files:
+        if not f.is_file() or f.parent.resolve() != index.parent.resolve():
+            raise SafetensorsError(f"{index}: names the file {f.name!r}, which is not in the model folder")
+    return files
 
 
 __all__ = ["WeightError", "SafetensorsError", "load_weights", "stored_to_kept", "WEIGHTS_FILE"]

@@ -126,3 +126,43 @@ def test_tied_model_tolerates_a_head_in_the_file_and_missing_file_is_an_error(tm
     (d / "model.safetensors").unlink()
     with pytest.raises(WeightError, match="missing tensors"):
         load_weights(d, specs_of(TINY_A), "cpu", torch.bfloat16)
+
+
+def test_weights_spread_over_several_files(tmp_path):
+    """A folder whose tensors lie in several safetensors files named by model.safetensors.index.json
+    loads to the same tensors; a tensor in two files, or an index that names a file outside the
+    folder or a missing one, is an error; a tensor missing from all files is listed as missing."""
+    from scriptling_llm_lib_b200.weights import SafetensorsError
+    d = make_model_dir(tmp_path / "s", TINY_B, 1)
+    want = load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    with SafetensorsFile(d / "model.safetensors") as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    (d / "model.safetensors").unlink()
+    names = sorted(tensors)
+    parts = {"model-00001-of-00003.safetensors": names[0::3], "model-00002-of-00003.safetensors": names[1::3],
+             "model-00003-of-00003.safetensors": names[2::3]}
+    for fn, ns in parts.items():
+        write_safetensors(d / fn, {n: tensors[n] for n in ns})
+    index = {"metadata": {}, "weight_map": {n: fn for fn, ns in parts.items() for n in ns}}
+    (d / "model.safetensors.index.json").write_text(json.dumps(index))
+    got = load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    assert set(got) == set(want) and all(torch.equal(got[k], want[k]) for k in want)
+    # one tensor absent from every file
+    write_safetensors(d / "model-00003-of-00003.safetensors", {n: tensors[n] for n in names[2::3][1:]})
+    with pytest.raises(WeightError) as e:
+        load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    assert e.value.missing == [names[2]]
+    # the same tensor in two files
+    write_safetensors(d / "model-00003-of-00003.safetensors", {n: tensors[n] for n in names[2::3] + names[:1]})
+    with pytest.raises(SafetensorsError, match="two files"):
+        load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    # an index that names a file that is not there, or not in the folder
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {names[0]: "nowhere.safetensors"}}))
+    with pytest.raises(SafetensorsError, match="not in the model folder"):
+        load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {names[0]: "../x.safetensors"}}))
+    with pytest.raises(SafetensorsError, match="not in the model folder"):
+        load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+    (d / "model.safetensors.index.json").write_text("[1, 2")
+    with pytest.raises(SafetensorsError, match="not an index"):
+        load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
