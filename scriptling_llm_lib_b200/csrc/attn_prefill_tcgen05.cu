@@ -1,5 +1,6 @@
 // Causal grouped-query attention of a prompt step over the paged cache on tcgen05 tensor cores
-// (bfloat16, head width 64).
+// (bfloat16, head width 64 or 128; a head of 128 is two 64-wide swizzled blocks side by side in
+// shared memory for Q, K and V alike, and O takes 128 columns of tensor memory).
 //
 // One block: 128 consecutive queries of one sequence and one query head. Warp 0 fetches the query
 // tile and, page by page, the keys and values of the sequence with TMA (128-byte swizzle, no
@@ -20,8 +21,6 @@
 
 #define FT_BQ 128
 #define FT_BK 64           // = SLLM_PAGE
-#define FT_HD 64
-#define FT_STAGES 3
 #define FT_THREADS 192       // warp 0: TMA, warp 1: MMA, warps 2-5: softmax (thread = query row)
 #define FT_LOG2E 1.4426950408889634f
 
@@ -45,10 +44,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+template <int FT_HD, int FT_STAGES>
 __global__ void __launch_bounds__(FT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, FtArgs p) {
+                       const __grid_constant__ CUtensorMap map_v, FtArgs p, uint32_t smem_bytes) {
   constexpr uint32_t Q_BYTES = FT_BQ * FT_HD * 2, KV_BYTES = FT_BK * FT_HD * 2, P_BYTES = FT_BQ * FT_BK * 2;
+  constexpr uint32_t QA = FT_BQ * 128, KA = FT_BK * 128;       // bytes of one 64-wide block of Q and of a K or V page
+  constexpr int NA = FT_HD / 64;                               // such blocks per head
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   // [Q][P][K stages][V stages][barriers]
@@ -60,6 +62,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                  b_ofull = b_pempty + 8;
   uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 1 + 1 + 1);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
+  if ((uint8_t*)(abort + 1) > smem_raw + smem_bytes) {      // the 1 KB alignment took more than the launch left room for
+    if (threadIdx.x == 0) atomicExch(p.err, 3);
+    return;
+  }
 
   // heads vary fastest, query tiles from the last (most keys) to the first: blocks start in the order
   // of their length over the whole grid, so the long ones are not left for the end
@@ -94,12 +100,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;          // columns: S0 0-63, S1 64-127, O 128-191
+  const uint32_t tmem_base = *tmem_slot;          // columns: S0 0-63, S1 64-127, O from 128 (one column per dim)
 
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(b_qfull, Q_BYTES);
-      tma_load_2d(sQ, &map_q, h * FT_HD, row0 + r0, b_qfull);
+#pragma unroll
+      for (int a = 0; a < NA; a++) tma_load_2d(sQ + a * QA, &map_q, h * FT_HD + 64 * a, row0 + r0, b_qfull);
       int issued = 0;
       for (int j = 0; j < n_tiles; j++) {
         int s = j % FT_STAGES;
@@ -107,8 +114,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         int page = bt[t_lo + j];
         int krow = (page * p.G + g) * FT_BK;
         mbar_expect_tx(b_kvfull + 8 * s, 2 * KV_BYTES);
-        tma_load_2d(sK + s * KV_BYTES, &map_k, 0, krow, b_kvfull + 8 * s);
-        tma_load_2d(sV + s * KV_BYTES, &map_v, 0, krow, b_kvfull + 8 * s);
+#pragma unroll
+        for (int a = 0; a < NA; a++) {
+          tma_load_2d(sK + s * KV_BYTES + a * KA, &map_k, 64 * a, krow, b_kvfull + 8 * s);
+          tma_load_2d(sV + s * KV_BYTES + a * KA, &map_v, 64 * a, krow, b_kvfull + 8 * s);
+        }
         issued = j + 1;
       }
       if (*abort) {
@@ -128,8 +138,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!mbar_wait(b_sempty + 8 * a, ((j >> 1) & 1) ^ 1, abort)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int k = 0; k < FT_HD / 16; k++)
-          umma_bf16(tmem_base + a * 64, umma_desc_sw128(sQ + k * 32), umma_desc_sw128(sK + s * KV_BYTES + k * 32), idesc_s, k ? 1u : 0u);
+        for (int k = 0; k < FT_HD / 16; k++)      // 16 dims a step: four steps in each 64-wide block
+          umma_bf16(tmem_base + a * 64, umma_desc_sw128(sQ + (k >> 2) * QA + (k & 3) * 32),
+                    umma_desc_sw128(sK + s * KV_BYTES + (k >> 2) * KA + (k & 3) * 32), idesc_s, k ? 1u : 0u);
         umma_commit(b_sfull + 8 * a);
         return true;
       };
@@ -142,7 +153,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int k = 0; k < FT_BK / 16; k++)
-          umma_bf16(tmem_base + 128, umma_desc_sw128(sP + k * 32), umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, 0),
+          umma_bf16(tmem_base + 128, umma_desc_sw128(sP + k * 32), umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, NA > 1 ? KA : 0),
                     idesc_o, (j | k) ? 1u : 0u);
         umma_commit(b_ofull);
         umma_commit(b_kvempty + 8 * s);
@@ -235,9 +246,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         int s = j % FT_STAGES, n_valid = q_hi + 1 - t * FT_BK;
         ok = mbar_wait(b_kvfull + 8 * s, (j / FT_STAGES) & 1, abort);
         if (!ok) break;
-        for (int e = (warp - 2) * 32 + lane; e < (FT_BK - n_valid) * 8; e += 128) {
-          int row = n_valid + e / 8, c = e % 8;
-          *(uint4*)(smem + Q_BYTES + P_BYTES + FT_STAGES * KV_BYTES + s * KV_BYTES + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+        for (int e = (warp - 2) * 32 + lane; e < (FT_BK - n_valid) * 8 * NA; e += 128) {
+          int a = e / ((FT_BK - n_valid) * 8), e1 = e % ((FT_BK - n_valid) * 8);
+          int row = n_valid + e1 / 8, c = e1 % 8;
+          *(uint4*)(smem + Q_BYTES + P_BYTES + FT_STAGES * KV_BYTES + s * KV_BYTES + a * KA + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       {
@@ -281,14 +293,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0 && *abort) atomicExch(p.err, 2);
 }
 
-// q: [T, q_ld] rotated queries (head h at columns h*64); out: [T, H*64]; kpages/vpages:
-// [n_pages][G][64][64] with n_pages the number of pages the storage holds.
+template <int HD, int STAGES>
+static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FtArgs& a, dim3 grid,
+                     cudaStream_t stream) {
+  // what the kernel lays out after aligning to 1 KB, and the most two blocks can have on an SM
+  constexpr size_t need = FT_BQ * HD * 2 + FT_BQ * FT_BK * 2 + 2 * STAGES * FT_BK * HD * 2 + 256;
+  constexpr size_t room = (233472 / 2 - 1024);
+  constexpr size_t smem = need + 1024 <= room ? need + 1024 : room;     // the slack for the alignment, as far as it fits
+  static_assert(need <= smem, "two blocks of this head width do not fit an SM");
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    raised = true;
+  }
+  attn_prefill_tc_kernel<HD, STAGES><<<grid, FT_THREADS, smem, stream>>>(mq, mk, mv, a, (uint32_t)smem);
+  SLLM_RETURN_LAST();
+}
+
+// q: [T, q_ld] rotated queries (head h at columns h*hd); out: [T, H*hd]; kpages/vpages:
+// [n_pages][G][64][hd] with n_pages the number of pages the storage holds; hd 64 or 128.
 SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* out, const int* seq_start, const int* seq_pos0,
                                           const int* block_table, int max_pages, const void* kpages, const void* vpages,
                                           long long n_pages, int B, int max_new, int H, int G, int hd, int window, float scale,
                                           int* err, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
-  if (hd != FT_HD || G < 1 || H % G != 0 || (q_ld & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+  if ((hd != 64 && hd != 128) || G < 1 || H % G != 0 || (q_ld & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15))
     return SLLM_ERR_ARG;
   long long kv_rows = n_pages * G * FT_BK;
@@ -296,19 +326,11 @@ SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* 
   CUtensorMap mq, mk, mv;
   int rc = tc_make_map(&mq, q, T, q_ld, q_ld, FT_BQ);
   if (rc) return rc;
-  rc = tc_make_map(&mk, kpages, (int)kv_rows, FT_HD, FT_HD, FT_BK);
+  rc = tc_make_map(&mk, kpages, (int)kv_rows, hd, hd, FT_BK);
   if (rc) return rc;
-  rc = tc_make_map(&mv, vpages, (int)kv_rows, FT_HD, FT_HD, FT_BK);
+  rc = tc_make_map(&mv, vpages, (int)kv_rows, hd, hd, FT_BK);
   if (rc) return rc;
-  constexpr size_t smem = FT_BQ * FT_HD * 2 + FT_BQ * FT_BK * 2 + 2 * FT_STAGES * FT_BK * FT_HD * 2 + 1024 + 256;
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    raised = true;
-  }
   FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err};
   dim3 grid(H, (max_new + FT_BQ - 1) / FT_BQ, B);
-  attn_prefill_tc_kernel<<<grid, FT_THREADS, smem, stream>>>(mq, mk, mv, a);
-  SLLM_RETURN_LAST();
+  return hd == 64 ? ft_launch<64, 3>(mq, mk, mv, a, grid, stream) : ft_launch<128, 2>(mq, mk, mv, a, grid, stream);
 }

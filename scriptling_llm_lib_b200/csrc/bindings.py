@@ -164,14 +164,6 @@ class KernelSet:
         return self._fa_tc
 
     @property
-    def prefill_attention(self) -> "PrefillAttention":
-        if self.dtype != torch.bfloat16:
-            raise KernelError("the tensor-core attention is bfloat16 only")
-        if getattr(self, "_fa", None) is None:
-            self._fa = PrefillAttention()
-        return self._fa
-
-    @property
     def decode(self) -> "DecodeKernels":
         if self.dtype != torch.bfloat16:
             raise KernelError("the decode kernels are bfloat16 only")
@@ -279,27 +271,9 @@ class TensorCoreGemm:
         return max(1, min(sm_count // tiles, k // 256, 16))
 
 
-class PrefillAttention:
-    """Tensor-core causal attention of a prompt step over the paged cache (bfloat16, head width 64 or 128)."""
-    HEAD_DIMS = (64, 128)
-
-    def __init__(self):
-        self.lib = load_library("attn_prefill_bf16")
-        self.lib.sllm_attn_prefill_bf16.restype = c_int
-
-    def attn(self, q, out, seq_start, seq_pos0, block_table, kpages, vpages, n_seqs, max_new, n_heads, n_kv, head_dim,
-             window, scale):
-        _check(self.lib.sllm_attn_prefill_bf16(
-            _ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), _ptr(out, torch.bfloat16, "out"),
-            _ptr(seq_start, torch.int32, "seq_start"), _ptr(seq_pos0, torch.int32, "seq_pos0"),
-            _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
-            _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"), c_int(n_seqs), c_int(max_new),
-            c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(window or 0), c_float(scale), _stream()), "attn_prefill")
-
-
 class PrefillAttentionTC:
-    """tcgen05 causal attention of a prompt step over the paged cache (bfloat16, head width 64)."""
-    HEAD_DIMS = (64,)
+    """tcgen05 causal attention of a prompt step over the paged cache (bfloat16, head width 64 or 128)."""
+    HEAD_DIMS = (64, 128)
 
     def __init__(self):
         self.lib = load_library("attn_prefill_tcgen05")

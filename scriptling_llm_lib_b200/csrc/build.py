@@ -31,7 +31,6 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "sampling": ("lib_sampling.cu", ("common.cuh",)),
     "decode_bf16": ("decode_bf16.cu", ("common.cuh", "attn_decode_noalloc.h")),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
-    "attn_prefill_bf16": ("attn_prefill_bf16.cu", ("common.cuh",)),
     "attn_prefill_tcgen05": ("attn_prefill_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
 }
 

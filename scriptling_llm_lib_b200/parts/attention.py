@@ -14,7 +14,7 @@ import math
 import torch
 
 from ..cache.needs import CacheNeed
-from ..csrc.bindings import DecodeKernels, PrefillAttention, PrefillAttentionTC
+from ..csrc.bindings import DecodeKernels, PrefillAttentionTC
 from .base import MIXERS, POSITION_ENCODINGS, Mixer, PartSpec
 from .linear import Linear
 
@@ -89,10 +89,6 @@ class Attention(Mixer):
             ctx.kernels.prefill_attention_tc.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
                                                   ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
                                                   self.window, self.scale, ctx.err_flag)
-        elif x.dtype == torch.bfloat16 and self.head_dim in PrefillAttention.HEAD_DIMS:
-            ctx.kernels.prefill_attention.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
-                                               ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
-                                               self.window, self.scale)
         else:
             ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
                                    ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
