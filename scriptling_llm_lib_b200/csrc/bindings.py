@@ -320,11 +320,12 @@ class DecodeKernels:
     def attention_splits(self, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, pages: int, sm_count: int) -> int:
         """Over how many blocks a decode step splits each sequence's keys: enough blocks to fill the
         GPU, never more than the longest sequence has pages. The tensor-core kernel (grouped queries,
-        or very few sequences) has fatter blocks: it wants about four per SM and at least four
-        pages each; the one-head kernel about six per SM."""
+        or very few sequences) has fatter blocks: it wants as many as are resident at once and at
+        least four pages each; the one-head kernel about six per SM."""
         pairs = max(1, n_seqs * n_kv_heads)
         if self.lib.sllm_attn_decode_uses_mma(c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim)):
-            want, cap = -(-4 * sm_count // pairs), max(1, pages // 4)
+            # one wave and no more: its registers allow four blocks per SM at width 64, two at width 128
+            want, cap = ((4 if head_dim <= 64 else 2) * sm_count) // pairs, max(1, pages // 4)
         else:
             want, cap = -(-6 * sm_count // pairs), pages
         return max(1, min(want, cap, DecodeKernels.MAX_SPLITS))
