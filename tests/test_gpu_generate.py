@@ -32,7 +32,7 @@ def near_maximum(model, prompt, out, tol):
     return True
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_through_the_entry_point(tmp_path, name):
     from scriptling_llm_lib_b200 import llm
     raw, seed = TINY[name]

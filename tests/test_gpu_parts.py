@@ -44,7 +44,7 @@ def engine_with_context(tmp_path, name, dtype, lens, pos0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_parts_alone(tmp_path, name, dtype):
     lens, pos0 = [9, 1, 40], [0, 70, 33]
     eng, ctx, d, olds, news = engine_with_context(tmp_path, name, dtype, lens, pos0)

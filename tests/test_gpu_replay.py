@@ -11,12 +11,13 @@ from helpers import (TINY, TOL_BF16, TOL_F32, Replay, make_model_dir, plain_mode
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 33, 5, 64, 1, 100, 47], "B": [40, 63, 1, 8, 129, 65, 200], "C": [90, 33, 150, 64, 17, 230, 128]}
+LENGTHS = {"A": [70, 33, 5, 64, 1, 100, 47], "B": [40, 63, 1, 8, 129, 65, 200], "C": [90, 33, 150, 64, 17, 230, 128],
+           "D": [300, 33, 150, 129, 17, 260, 128], "E": [40, 280, 1, 8, 160, 65, 200]}
 PROMPTS = [0.5, 1.0, 0.2, 0.9, 1.0, 0.33, 0.01]       # share of a request that is its prompt in the batched replay
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_replay_cuttings(tmp_path, name, dtype):
     raw, seed = TINY[name]
     d = make_model_dir(tmp_path / "model", raw, seed)
