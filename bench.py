@@ -23,14 +23,14 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: SmolLM2-1.7B shape
+# the benchmark's primary configuration: the SmolLM2-1.7B layer sizes
 SHAPE = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 24, "hidden_size": 2048,
     "num_attention_heads": 32, "num_key_value_heads": 32, "head_dim": 64, "intermediate_size": 8192,
     "vocab_size": 49152, "rope_theta": 130000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
     "max_position_embeddings": 8192, "hidden_act": "silu",
 }
-# further sizes of the family (BASELINE.json configs[3], configs[4]); the default run uses SHAPE
+# further sizes of the family (Llama-3.2-1B and Llama-3.1-8B layer sizes); the default run uses SHAPE
 OTHER_SHAPES = {
     "llama3.2-1b": dict(SHAPE, num_hidden_layers=16, num_key_value_heads=8, vocab_size=128256, rope_theta=500000.0,
                         rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
