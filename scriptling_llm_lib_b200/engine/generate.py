@@ -149,12 +149,14 @@ class Generator:
                     if step_no == 0:
                         t_ev[1].record()
                     ahead = None
+                    # the ids start their way to the host before the next step is put on the stream
+                    read = self.sampler.begin_read(toks_dev) if pipelined and hasattr(self.sampler, "begin_read") else toks_dev.tolist
                     if pipelined:
                         cont = [j for j, i in enumerate(live) if not state.ends_by_count(i, fed[j])]
                         if cont:
                             rows = toks_dev if len(cont) == len(live) else toks_dev[torch.as_tensor(cont, device=toks_dev.device)]
                             ahead = ([live[j] for j in cont], eng.decode_step_device([seqs[live[j]] for j in cont], rows))
-                    toks = toks_dev.tolist()
+                    toks = read()
                     for i in state.accept(live, fed, toks):
                         seqs.pop(i).close()
                     if on_step is not None and on_step(step_no, {batch[i]: t for i, t in zip(live, toks)}):

@@ -83,6 +83,23 @@ class Sampler:
         self._copied.record()
         return dev
 
+    def begin_read(self, tokens: torch.Tensor):
+        """Start copying sampled ids to the host; returns a function that waits for that copy alone and
+        gives the ids as a list. Called before later work is put on the stream, it lets the host read a
+        step's tokens while the next step is already running (a plain read would wait for all of it)."""
+        n = tokens.shape[0]
+        if getattr(self, "_host_ids", None) is None or self._host_ids.shape[0] < n:
+            self._host_ids = torch.empty(max(64, n), dtype=torch.int32).pin_memory()
+            self._ids_read = torch.cuda.Event()
+        host = self._host_ids[:n]
+        host.copy_(tokens, non_blocking=True)
+        self._ids_read.record()
+
+        def result():
+            self._ids_read.synchronize()
+            return host.tolist()
+        return result
+
     def sample(self, logits: torch.Tensor, options: SamplingOptions, seeds: list[int], draws: list[int],
                recent: list[list[int]] | None = None) -> torch.Tensor:
         """logits float32 [n, V] on the device -> int32 token ids [n] on the device.
