@@ -16,7 +16,10 @@
 //     group) to finish merges the splits. In raw mode the kernel also does the rotary step
 //     (float32_ops.go:174-188) for the queries and the new key and appends key and value to the
 //     cache (model_f32.go:445-448). Same mathematics as fusedAttentionHeadF32 with one query row
-//     (float32_ops.go:190-235).
+//     (float32_ops.go:190-235). Two kernels: attn_decode_split takes one query head at a time per
+//     group of lanes; attn_decode_mma (head width 64 or 128, grouped queries or very few
+//     sequences) puts the query heads of a group on the rows of mma.sync.m16n8k16 and feeds it
+//     keys and values straight from the pages.
 //
 // All kernels here are launched with programmatic stream serialisation (see common.cuh): they may
 // start while the previous kernel drains, and wait before touching what it wrote.
