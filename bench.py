@@ -299,7 +299,8 @@ def main():
                     torch.cuda.synchronize()
                     marks["t0"] = time.perf_counter()
                 return False
-            llm.generate(model_dir, prompts, 4, "greedy", temperature=0.0, stop_ids=[])          # warm-up
+            # warm-up with the same lengths: the cache is sized and the step's graph captured before the timed call
+            llm.generate(model_dir, prompts, args.steps + 1, "greedy", temperature=0.0, stop_ids=[])
             out = llm.generate(model_dir, prompts, args.steps + 1, "greedy", temperature=0.0, stop_ids=[], on_step=on_step)
             torch.cuda.synchronize()
             dt = time.perf_counter() - marks["t0"]
