@@ -94,3 +94,24 @@ def _stats(results: list[GenerationResult]) -> dict:
             "generated_tokens": [r.generated_tokens for r in results],
             "finish_reason": [r.finish_reason for r in results],
             "prefill_ms": [r.prefill_ms for r in results], "decode_ms": [r.decode_ms for r in results]}
+
+
+def random_model(config, seed: int, out_dir, dtype: str = "bfloat16"):
+    """Write a model folder (config.json, model.safetensors) with random weights drawn from `seed`
+    for `config`: a dict of config.json keys or the path of such a file. Returns the folder, which
+    `generate` and the command line then take like any other. Needs no GPU."""
+    import json
+    from pathlib import Path
+    import torch
+    from . import models  # noqa: F401  (registers the architectures)
+    from .config.registry import architecture_for
+    from .engine.model import DecoderModel
+    from .weights.random_init import write_random_model
+    where = "config"
+    if not isinstance(config, dict):
+        where = str(config)
+        config = json.loads(Path(config).read_text())
+    arch = architecture_for(config["architectures"][0] if config.get("architectures") else None)
+    cfg = arch.config_class.from_dict(config, where)
+    specs = DecoderModel(arch.layout(cfg)).tensor_specs()
+    return write_random_model(cfg, specs, int(seed), Path(out_dir), {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype])

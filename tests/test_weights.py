@@ -166,3 +166,18 @@ def test_weights_spread_over_several_files(tmp_path):
     (d / "model.safetensors.index.json").write_text("[1, 2")
     with pytest.raises(SafetensorsError, match="not an index"):
         load_weights(d, specs_of(TINY_B), "cpu", torch.bfloat16)
+
+
+def test_random_model_through_the_python_entry_point(tmp_path):
+    """llm.random_model writes a folder from a config (a dict or a file) and a seed; the same seed gives
+    the same bytes, an unknown architecture is named in the error."""
+    from scriptling_llm_lib_b200 import llm
+    from scriptling_llm_lib_b200.config import ConfigError
+    d1 = llm.random_model(TINY_A, 5, tmp_path / "r1")
+    (tmp_path / "cfg.json").write_text(json.dumps(TINY_A))
+    d2 = llm.random_model(tmp_path / "cfg.json", 5, tmp_path / "r2")
+    assert (d1 / "model.safetensors").read_bytes() == (d2 / "model.safetensors").read_bytes()
+    assert json.loads((d1 / "config.json").read_text())["hidden_size"] == 64
+    assert llm.random_model(TINY_A, 6, tmp_path / "r3").joinpath("model.safetensors").read_bytes() != (d1 / "model.safetensors").read_bytes()
+    with pytest.raises(ConfigError, match="not registered"):
+        llm.random_model(dict(TINY_A, architectures=["NoSuchModel"]), 0, tmp_path / "r4")
