@@ -40,7 +40,7 @@ TINY_C = {
     "hidden_act": "silu",
 }
 # Two more with the head widths that the tensor-core kernels of the bfloat16 path take (64 and 128):
-# grouped queries with a window that cuts long prompts, and one key/value head for six query heads
+# grouped queries with a window that cuts long prompts, and one key/value head for six query heads (also windowed)
 TINY_D = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "num_hidden_layers": 2, "hidden_size": 200, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
@@ -51,7 +51,8 @@ TINY_E = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "num_hidden_layers": 2, "hidden_size": 264, "num_attention_heads": 6, "num_key_value_heads": 1, "head_dim": 128,
     "intermediate_size": 136, "vocab_size": 777, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
-    "tie_word_embeddings": False, "max_position_embeddings": 512, "rope_pairing": "interleaved", "hidden_act": "silu",
+    "tie_word_embeddings": False, "max_position_embeddings": 512, "rope_pairing": "interleaved", "sliding_window": 200,
+    "hidden_act": "silu",
 }
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
