@@ -118,7 +118,7 @@ __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, i
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         float g = __uint_as_float(r[16 * t + j]), u = __uint_as_float(r[16 * t + 8 + j]);
-        h[8 * t + j] = g * (1.0f / (1.0f + __expf(-g))) * u;
+        h[8 * t + j] = __fdividef(g, 1.0f + __expf(-g)) * u;
       }
     if (ocol + 16 <= n_out && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
@@ -132,6 +132,97 @@ __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, i
     } else {
 #pragma unroll
       for (int j = 0; j < 16; j++) if (ocol + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
+    }
+  }
+}
+
+// One warp's share of a finished 128-row accumulator (tensor-memory columns from `acc`, lanes
+// 32 q .. 32 q + 31 = rows m0 + 32 q .., columns c_lo .. c_hi - 1 = output columns n0 + c_lo ..):
+// read back with tcgen05.ld and written as EPI says. c_lo and c_hi are multiples of 32, and of the
+// head width in the q|k|v epilogue.
+template <int EPI>
+__device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, int m0, int n0, int c_lo, int c_hi,
+                                                 void* __restrict__ C, int M, int N, int ldc, int out_f32, const TcRope& rp) {
+  int row = m0 + q * 32 + lane;
+  if constexpr (EPI == TC_EPI_QKV_ROPE) {
+    const uint32_t trow = acc + ((uint32_t)(q * 32) << 16);
+    int pos = 0;
+    size_t cache_row = 0;                  // (page * G) * PAGE + place in the page; + g * PAGE, times hd, is the row's place
+    if (row < M) {
+      pos = rp.tok_pos[row];
+      int page = rp.block_table[(size_t)rp.tok_seq[row] * rp.max_pages + pos / SLLM_PAGE];
+      cache_row = (size_t)page * rp.G * SLLM_PAGE + (pos % SLLM_PAGE);
+    }
+    const float2* csr = rp.cs + (size_t)pos * (rp.rot >> 1);
+    if (rp.interleaved) {
+      // pairs of adjacent columns: a chunk of 32 columns holds 16 whole pairs
+#pragma unroll 1
+      for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        uint32_t r[32];
+        tmem_ld32(trow + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+          int col = n0 + c0, d0 = col % rp.hd;
+          bool rotate = col / rp.hd < rp.H + rp.G;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float x0 = bf16_round(r[j]), x1 = bf16_round(r[j + 1]);
+            if (rotate && d0 + j < rp.rot) {
+              float2 cs = csr[(d0 + j) >> 1];
+              v[j] = x0 * cs.x - x1 * cs.y;
+              v[j + 1] = x0 * cs.y + x1 * cs.x;
+            } else {
+              v[j] = x0;
+              v[j + 1] = x1;
+            }
+          }
+          qkv_store32(rp, C, ldc, row, col, cache_row, v);
+        }
+        __syncwarp();
+      }
+    } else {
+      // pairs (i, i + hd/2), the whole head rotated: two chunks of 32 columns half a head apart
+      const int half = rp.hd >> 1;
+#pragma unroll 1
+      for (int h0 = c_lo; h0 < c_hi; h0 += rp.hd) {
+        if (n0 + h0 >= N) break;
+#pragma unroll 1
+        for (int i0 = 0; i0 < half; i0 += 32) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(trow + (uint32_t)(h0 + i0), r0);
+          tmem_ld32(trow + (uint32_t)(h0 + half + i0), r1);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row < M) {
+            int col = n0 + h0 + i0;
+            bool rotate = col / rp.hd < rp.H + rp.G;
+            float v0[32], v1[32];
+            const float4* c4 = (const float4*)(csr + i0);     // (cos, sin) of two pairs per load
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float4 cs = rotate ? c4[j >> 1] : make_float4(1.f, 0.f, 1.f, 0.f);
+              float a0 = bf16_round(r0[j]), b0 = bf16_round(r1[j]), a1 = bf16_round(r0[j + 1]), b1 = bf16_round(r1[j + 1]);
+              v0[j] = a0 * cs.x - b0 * cs.y;
+              v1[j] = a0 * cs.y + b0 * cs.x;
+              v0[j + 1] = a1 * cs.z - b1 * cs.w;
+              v1[j + 1] = a1 * cs.w + b1 * cs.z;
+            }
+            qkv_store32(rp, C, ldc, row, col, cache_row, v0);
+            qkv_store32(rp, C, ldc, row, col + half, cache_row, v1);
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+      if (n0 + c0 >= N) break;               // uniform over the warp
+      uint32_t r[32];
+      tmem_ld32(acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
     }
   }
 }
@@ -230,88 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int a = i & 1;
       if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      int row = m0 + q * 32 + lane;
-      if constexpr (EPI == TC_EPI_QKV_ROPE) {
-        const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN);
-        int pos = 0;
-        size_t cache_row = 0;                  // (page * G) * PAGE + place in the page; + g * PAGE, times hd, is the row's place
-        if (row < M) {
-          pos = rp.tok_pos[row];
-          int page = rp.block_table[(size_t)rp.tok_seq[row] * rp.max_pages + pos / SLLM_PAGE];
-          cache_row = (size_t)page * rp.G * SLLM_PAGE + (pos % SLLM_PAGE);
-        }
-        const float2* csr = rp.cs + (size_t)pos * (rp.rot >> 1);
-        if (rp.interleaved) {
-          // pairs of adjacent columns: a chunk of 32 columns holds 16 whole pairs
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            if (n0 + c0 >= N) break;
-            uint32_t r[32];
-            tmem_ld32(trow + (uint32_t)c0, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < M) {
-              int col = n0 + c0, d0 = col % rp.hd;
-              bool rotate = col / rp.hd < rp.H + rp.G;
-              float v[32];
-#pragma unroll
-              for (int j = 0; j < 32; j += 2) {
-                float x0 = bf16_round(r[j]), x1 = bf16_round(r[j + 1]);
-                if (rotate && d0 + j < rp.rot) {
-                  float2 cs = csr[(d0 + j) >> 1];
-                  v[j] = x0 * cs.x - x1 * cs.y;
-                  v[j + 1] = x0 * cs.y + x1 * cs.x;
-                } else {
-                  v[j] = x0;
-                  v[j + 1] = x1;
-                }
-              }
-              qkv_store32(rp, C, ldc, row, col, cache_row, v);
-            }
-            __syncwarp();
-          }
-        } else {
-          // pairs (i, i + hd/2), the whole head rotated: two chunks of 32 columns half a head apart
-          const int half = rp.hd >> 1;
-#pragma unroll 1
-          for (int h0 = 0; h0 < BN; h0 += rp.hd) {
-            if (n0 + h0 >= N) break;
-#pragma unroll 1
-            for (int i0 = 0; i0 < half; i0 += 32) {
-              uint32_t r0[32], r1[32];
-              tmem_ld32(trow + (uint32_t)(h0 + i0), r0);
-              tmem_ld32(trow + (uint32_t)(h0 + half + i0), r1);
-              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-              if (row < M) {
-                int col = n0 + h0 + i0;
-                bool rotate = col / rp.hd < rp.H + rp.G;
-                float v0[32], v1[32];
-                const float4* c4 = (const float4*)(csr + i0);     // (cos, sin) of two pairs per load
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                  float4 cs = rotate ? c4[j >> 1] : make_float4(1.f, 0.f, 1.f, 0.f);
-                  float a0 = bf16_round(r0[j]), b0 = bf16_round(r1[j]), a1 = bf16_round(r0[j + 1]), b1 = bf16_round(r1[j + 1]);
-                  v0[j] = a0 * cs.x - b0 * cs.y;
-                  v1[j] = a0 * cs.y + b0 * cs.x;
-                  v0[j + 1] = a1 * cs.z - b1 * cs.w;
-                  v1[j + 1] = a1 * cs.w + b1 * cs.z;
-                }
-                qkv_store32(rp, C, ldc, row, col, cache_row, v0);
-                qkv_store32(rp, C, ldc, row, col + half, cache_row, v1);
-              }
-              __syncwarp();
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= N) break;               // uniform over the warp
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
-      }
-      }
+      tc_epilogue_tile<EPI>(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, 0, BN, C, M, N, ldc, out_f32, rp);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * a) : "memory");
@@ -348,6 +358,178 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int 
   SLLM_RETURN_LAST();
 }
 
+// ------------------------------------------------------------------ two SMs on one tile
+// The two-SM form of the kernel above (tcgen05 cta_group::2): the two blocks of a cluster share a
+// 256 x 256 tile. Each block loads its own 128 rows of A and its own 128 of the tile's 256 rows of
+// B, the block of rank 0 issues the products for both, and each block finds its 128 rows of the
+// result in its own tensor memory. A k-block of 64 then costs an SM 32 KB of shared-memory traffic
+// for 128 x 256 x 64 products instead of 48 KB, which is what held the one-SM tile back, and the
+// ring is six stages deep in the same space. Hand-over as above, except that both blocks' copies
+// report to `full[s]` of rank 0, its commits arrive on `empty[s]` and `acc_full[a]` of both blocks,
+// and both blocks' epilogue warps arrive on `acc_empty[a]` of rank 0. The blocks leave together.
+#define TC2_BM 256
+#define TC2_BN 256
+#define TC2_THREADS 320   // warps 2-9 are the epilogue: one or two per quarter of tensor memory
+#define TC2_WIDE_NKB 32
+
+template <int STAGES, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC2_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ C,
+                    int M, int N, int K, int ldc, int out_f32, int* __restrict__ err, const TcRope rp) {
+  constexpr int BN = TC2_BN;
+  constexpr uint32_t A_BYTES = 128 * TC_BK * 2, B_BYTES = 128 * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+  volatile int* abort = (volatile int*)(tmem_slot + 1);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, acc_full0 = empty0 + 8 * STAGES, acc_empty0 = acc_full0 + 16;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_m = (M + TC2_BM - 1) / TC2_BM, tiles_n = (N + BN - 1) / BN, n_tiles = tiles_m * tiles_n;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  // A read of tensor memory waits behind the products already queued, some thousands of clocks
+  // each time, so with few k-blocks to a tile four warps would take longer over a tile's epilogue
+  // than the products of the next tile take: then all eight work, each on half of the columns.
+  const bool wide = nkb <= TC2_WIDE_NKB;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, wide ? 16 : 8); }
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    // one warp of each block of the pair, together; both blocks get the same columns
+    if (lane == 0) *tmem_slot = 0;
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                   // the other block's barriers are set up before anything arrives on them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        int m0 = (tile % tiles_m) * TC2_BM + (int)rank * 128, n0 = (tile / tiles_m) * BN + (int)rank * 128;
+        for (int kb = 0; kb < nkb; kb++, it++) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, abort);
+          if (!ok) break;
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);     // both blocks' bytes
+          uint32_t full_lead = mapa_shared(full0 + 8 * s, 0);
+          uint32_t a_dst = smem_base + s * STAGE_BYTES;
+          tma_load_2d_pair(a_dst, &map_a, kb * TC_BK, m0, full_lead);
+          tma_load_2d_pair(a_dst + A_BYTES, &map_b, kb * TC_BK, n0, full_lead);
+        }
+      }
+      if (*abort) {
+        // copies already issued still land in this block's shared memory. Rank 0 sees them on its
+        // own barriers; the other block cannot wait on those and gives its copies ample time instead.
+        if (rank == 0) {
+          volatile int never = 0;
+          for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1, &never);
+        } else {
+          uint64_t t0 = global_ns();
+          while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TC2_BM, BN);
+      int it = 0, i = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, i++) {
+        int a = i & 1;
+        ok = mbar_wait_cluster(acc_empty0 + 8 * a, ((i >> 1) & 1) ^ 1, abort);   // both blocks have drained this accumulator
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t acc = tmem_base + (uint32_t)(a * BN);
+        for (int kb = 0; kb < nkb; kb++, it++) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, abort);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          uint32_t a_addr = smem_base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; k++)
+            umma_bf16_pair(acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc, (kb | k) ? 1u : 0u);
+          umma_commit_pair(empty0 + 8 * s);
+        }
+        if (ok) umma_commit_pair(acc_full0 + 8 * a);
+      }
+    }
+  } else {
+    const int q = warp & 3, c_lo = warp < 6 ? 0 : BN / 2, c_hi = wide ? c_lo + BN / 2 : BN;
+    int i = 0;
+    for (int tile = pair; tile < n_tiles && (wide || warp < 6); tile += n_pairs, i++) {
+      int m0 = (tile % tiles_m) * TC2_BM + (int)rank * 128, n0 = (tile / tiles_m) * BN;
+      int a = i & 1;
+      if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      tc_epilogue_tile<EPI>(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, c_lo, c_hi, C, M, N, ldc, out_f32, rp);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty0 + 8 * a, 0));
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                   // nothing of the other block is still on its way to this one
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort) atomicExch(err, 2);
+}
+
+template <int STAGES, int EPI>
+static int tc_pair_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int out_f32,
+                          int* err, cudaStream_t stream, const TcRope& rp = TcRope{}) {
+  constexpr size_t smem = STAGES * (2 * 128 * TC_BK * 2) + 1024 + 256;
+  static int pairs = 0;                  // how many pairs of blocks the GPU holds at once
+  if (!pairs) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return SLLM_ERR_ARG - 3;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms & ~1);
+    cfg.blockDim = dim3(TC2_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<STAGES, EPI>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = sms / 2;
+    }
+    pairs = n < sms / 2 ? n : sms / 2;
+  }
+  int n_tiles = ((N + TC2_BN - 1) / TC2_BN) * ((M + TC2_BM - 1) / TC2_BM);
+  dim3 grid(2 * (n_tiles < pairs ? n_tiles : pairs));
+  gemm_tc_pair_kernel<STAGES, EPI><<<grid, TC2_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err, rp);
+  SLLM_RETURN_LAST();
+}
+
+// whether the two-SM kernel takes a product: more than one block's rows and wide enough for its tile
+static bool tc_use_pair(int M, int N) {
+  static int off = -1;
+  if (off < 0) { const char* e = getenv("SLLM_GEMM_ONE_SM"); off = e && *e && *e != '0'; }
+  return !off && M > 128 && N > 128;
+}
+
 // C[M,N] = A[M,K] B[N,K]^T. epilogue 0: C bfloat16 (or float when out_f32), row stride ldc;
 // epilogue 1: C[M,N/2] = silu(gate) * up for B's rows in tiles of 16 (8 gate rows, 8 up rows);
 // epilogue 2: C is a float matrix and the product is added to it (the residual sum).
@@ -361,6 +543,13 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
   int big = N > 128;
   int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
   if (rc) return rc;
+  if (tc_use_pair(M, N)) {
+    rc = tc_make_map(&mb, B, N, K, ldb, 128);
+    if (rc) return rc;
+    if (epilogue == TC_EPI_RESIDUAL) return tc_pair_launch<6, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream);
+    if (epilogue == TC_EPI_SWIGLU) return tc_pair_launch<6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);
+    return tc_pair_launch<6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
+  }
   rc = tc_make_map(&mb, B, N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
   if (epilogue == TC_EPI_RESIDUAL)
@@ -389,9 +578,14 @@ SLLM_EXPORT int sllm_gemm_tc_qkv_rope_bf16(const void* A, const void* B, void* C
   CUtensorMap ma, mb;
   int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
   if (rc) return rc;
+  TcRope rp{tok_pos, tok_seq, block_table, max_pages, (const float2*)cos_sin, (bf16*)kpages, (bf16*)vpages, H, G, hd, rot, interleaved};
+  if (tc_use_pair(M, N)) {
+    rc = tc_make_map(&mb, B, N, K, ldb, 128);
+    if (rc) return rc;
+    return tc_pair_launch<6, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp);
+  }
   rc = tc_make_map(&mb, B, N, K, ldb, 256);
   if (rc) return rc;
-  TcRope rp{tok_pos, tok_seq, block_table, max_pages, (const float2*)cos_sin, (bf16*)kpages, (bf16*)vpages, H, G, hd, rot, interleaved};
   return tc_launch<256, 4, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp);
 }
 
@@ -516,7 +710,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             float v = __uint_as_float(r[j]);
             float u = __shfl_xor_sync(0xffffffffu, v, 8);
             if (gate_lane && n < N && c0 + j < M)
-              ((bf16*)C)[(size_t)(c0 + j) * ldc + ocol] = __float2bfloat16_rn(v * (1.0f / (1.0f + __expf(-v))) * u);
+              ((bf16*)C)[(size_t)(c0 + j) * ldc + ocol] = __float2bfloat16_rn(__fdividef(v, 1.0f + __expf(-v)) * u);
           }
         } else {
           bf16* dst = (bf16*)C + n;

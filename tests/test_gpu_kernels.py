@@ -127,9 +127,12 @@ def test_gemm_small_m(kernel_sets, M, N, K):
 
 
 @pytest.mark.parametrize("M, N, K", [(128, 128, 64), (100, 200, 72), (130, 264, 520), (2048, 2048, 2048), (65, 1003 * 8, 136),
-                                     (300, 96, 8192)])
+                                     (300, 96, 8192), (257, 384, 136), (2304, 6400, 192), (1100, 4104, 2176)])
 def test_gemm_tensor_core(kernel_sets, M, N, K):
-    """The tcgen05 GEMM: bfloat16 and float outputs, the SiLU-gate epilogue, accumulation into a float matrix."""
+    """The tcgen05 GEMM: bfloat16 and float outputs, the SiLU-gate epilogue, accumulation into a float matrix.
+    More than 128 rows and columns go to the kernel that pairs two SMs on a 256 x 256 tile: sizes with
+    a ragged last tile, with several tiles to a pair (both accumulators, both phases), and with few
+    and many k-blocks to a tile (eight or four epilogue warps)."""
     tc = kernel_sets[torch.bfloat16].tensor_core
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     a, w = dev(rand(M, K, seed=14), torch.bfloat16), dev(rand(N, K, seed=15, scale=0.05), torch.bfloat16)
