@@ -1,13 +1,19 @@
 // bfloat16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T, float accumulation.
+// Three kernels, one set of epilogues:
+//   gemm_tc_pair_kernel    more than 128 rows and columns: two SMs (a cluster of two blocks,
+//                          cta_group::2) on one 256 x 256 tile;
+//   gemm_tc_kernel         the one-SM form, 128 x BN tiles: narrow outputs, and wide ones of few rows;
+//   gemm_tc_skinny_kernel  at most 128 rows: the weights are the 128-row operand.
 //
-// One block per SM walks over 128 x BN output tiles. Warp 0 feeds shared memory with TMA
-// (cp.async.bulk.tensor, 128-byte swizzle, no multicast), warp 1 issues tcgen05.mma from one thread
-// with the accumulator in tensor memory, warps 2-5 read the accumulator back with tcgen05.ld and
-// write the result (as bfloat16, as float, or through the SiLU gate when gate and up columns
-// alternate in groups of 8). Two accumulators take turns, so one tile's epilogue overlaps the next
-// tile's products. Hand-over is by mbarriers: TMA completes `full[s]`, the MMA's commit arrives on
-// `empty[s]`, a tile's last commit on `acc_full[a]`, the epilogue warps on `acc_empty[a]`. Rows and columns past M, N, K are zero-filled by TMA
-// and masked at the store, so every size with K % 8 == 0 is taken.
+// The one-SM kernel, which the others vary: one block per SM walks over 128 x BN output tiles. Warp
+// 0 feeds shared memory with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), warp 1
+// issues tcgen05.mma from one thread with the accumulator in tensor memory, warps 2-5 read the
+// accumulator back with tcgen05.ld and write the result (as bfloat16, as float, through the SiLU
+// gate when gate and up columns alternate in groups of 8, or as rotated queries and cache rows). Two
+// accumulators take turns, so one tile's epilogue overlaps the next tile's products. Hand-over is
+// by mbarriers: TMA completes `full[s]`, the MMA's commit arrives on `empty[s]`, a tile's last
+// commit on `acc_full[a]`, the epilogue warps on `acc_empty[a]`. Rows and columns past M, N, K are
+// zero-filled by TMA and masked at the store, so every size with K % 8 == 0 is taken.
 //
 // Replaces the reference's dense matmul (float32_ops.go:462-482) for the prompt step's
 // projections (model_f32.go:391-396, :469-470, :479-493, :519-524).

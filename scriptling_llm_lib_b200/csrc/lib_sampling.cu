@@ -98,10 +98,12 @@ sample_rows_kernel(const float* __restrict__ logits, int ldl, int V, const Sampl
   int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
   int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
 
-  // ---- maximum and its first index
+  // ---- maximum and its first index (threads stride over the row here: neighbouring lanes read
+  // neighbouring logits, several loads in flight; the running sums below need index order instead)
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = i0; i < i1; i++) {
+#pragma unroll 8
+  for (int i = tid; i < V; i += SAMPLE_THREADS) {
     float v = lg[i];
     if (v > best || best_i == 0x7fffffff) { best = v; best_i = i; }
   }
