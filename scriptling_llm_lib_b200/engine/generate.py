@@ -13,7 +13,6 @@ plain Python over token ids, so they can be tested with a scripted step function
 """
 from __future__ import annotations
 
-import time
 from dataclasses import dataclass, field
 from typing import Callable, Sequence as Seq
 

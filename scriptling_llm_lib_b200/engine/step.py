@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from ..cache import PAGE, CacheFull, SequenceCache, pages_for
+from ..cache import PAGE, SequenceCache, pages_for
 from ..config.registry import load_config
 from ..csrc.bindings import CastKernels, KernelSet
 from ..weights.loader import load_weights

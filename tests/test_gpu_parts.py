@@ -2,7 +2,6 @@
 embedding and head), and that layers are data: another mixer with state of its own, defined here,
 is registered, built and stepped without a change to the library; a schedule may name a layer
 twice or let a layer read another layer's cache."""
-import math
 from dataclasses import dataclass
 
 import numpy as np

@@ -1,11 +1,8 @@
 """Trace replay on the GPU: the same requests whole, with the last 32 tokens one by one, and in
 batches of unequal lengths one after another on reused slots, in 32-bit and in bfloat16, all
 against the plain implementation."""
-import numpy as np
 import pytest
-import torch
 
-import plain_llama as plain
 from helpers import (TINY, TOL_BF16, TOL_F32, Replay, make_model_dir, plain_model, random_ids, rel_err, replay_batch,
                      replay_tail_stepwise, replay_whole)
 
