@@ -377,6 +377,19 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int 
 #define TC2_BN 256
 #define TC2_THREADS 320   // warps 2-9 are the epilogue: one or two per quarter of tensor memory
 #define TC2_WIDE_NKB 32
+#define TC2_BAND 8          // tiles are walked in bands of 8 tile rows (2,048 rows of A)
+
+// Where tile number `tile` lies. Within a band of TC2_BAND tile rows the row index runs fastest, so
+// the pairs that work at the same time share one or two tiles of B, and a band's rows of A
+// (2,048 x K) stay in L2 while all of B passes by once per band; without bands, A as a whole
+// would pass by once per tile column, from DRAM as soon as it is larger than L2.
+__device__ __forceinline__ void tc2_tile_origin(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band_tiles = TC2_BAND * tiles_n;
+  const int band = tile / band_tiles, r = tile - band * band_tiles;
+  const int rows = min(TC2_BAND, tiles_m - band * TC2_BAND);
+  tm = band * TC2_BAND + r % rows;
+  tn = r / rows;
+}
 
 template <int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC2_THREADS, 1)
@@ -427,7 +440,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        int m0 = (tile % tiles_m) * TC2_BM + (int)rank * 128, n0 = (tile / tiles_m) * BN + (int)rank * 128;
+        int tm, tn;
+        tc2_tile_origin(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * TC2_BM + (int)rank * 128, n0 = tn * BN + (int)rank * 128;
         for (int kb = 0; kb < nkb; kb++, it++) {
           int s = it % STAGES;
           uint32_t ph = (it / STAGES) & 1;
@@ -482,7 +497,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int q = warp & 3, c_lo = warp < 6 ? 0 : BN / 2, c_hi = wide ? c_lo + BN / 2 : BN;
     int i = 0;
     for (int tile = pair; tile < n_tiles && (wide || warp < 6); tile += n_pairs, i++) {
-      int m0 = (tile % tiles_m) * TC2_BM + (int)rank * 128, n0 = (tile / tiles_m) * BN;
+      int tm, tn;
+      tc2_tile_origin(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * TC2_BM + (int)rank * 128, n0 = tn * BN;
       int a = i & 1;
       if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
