@@ -1,14 +1,22 @@
 #!/usr/bin/env python3
-"""Decode and prefill throughput of the SmolLM2-1.7B-shaped model with random weights on one B200.
+"""Decode and prefill throughput of the family's three benchmark shapes with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape smollm2-1.7b|llama3.2-1b|llama3.1-8b] [--dtype bfloat16|float32]
+                    [--batch B] [--context C] [--prompts uniform:LO-HI] [--layers L]
 
 A step is one decode step of a batch of 8 sequences; the K timed steps end at the benchmark
 context length (prompts of context - W - K tokens are prefilled first). `value` is decoded tokens
 per second, timed on the device with the sampled ids fed to the next step on the device; `e2e` is
-the same through the Python entry point (`llm.generate`) with host token ids in and out every step; `prefill` is one 2,048-token prompt; `roofline`
-relates the bytes a decode step has to read (every weight once, the cache of the live requests) to
-the measured copy bandwidth; `points` holds decoding at batch 1 and 64. One JSON line on stdout.
+the same through the Python entry point (`llm.generate`) with host token ids in and out every
+step; `prefill` is one 2,048-token prompt; `roofline` relates the bytes a decode step has to read
+(every weight once, the cache of the live requests) to the measured copy bandwidth; `points` holds
+decoding at batch 1 and 64. The default run adds `f32`, the same measurements on the true 32-bit
+path (its prompt step against a float fused-multiply-add rate measured here), and `shapes`: the
+Llama-3.2-1B sizes on a batch of unequal prompts (lengths uniform in 128..2048, seeded; one packed
+prompt step, then decoding) and the Llama-3.1-8B sizes at batch 1, 8 and 64. One JSON line on stdout.
+
+Weights are drawn on the device (`random:<config.json>:seed`), nothing is written but a config.json.
 """
 import argparse
 import json
@@ -30,7 +38,7 @@ SHAPE = {
     "vocab_size": 49152, "rope_theta": 130000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
     "max_position_embeddings": 8192, "hidden_act": "silu",
 }
-# further sizes of the family (Llama-3.2-1B and Llama-3.1-8B layer sizes); the default run uses SHAPE
+# further sizes of the family (Llama-3.2-1B and Llama-3.1-8B layer sizes); the default run's headline uses SHAPE
 OTHER_SHAPES = {
     "llama3.2-1b": dict(SHAPE, num_hidden_layers=16, num_key_value_heads=8, vocab_size=128256, rope_theta=500000.0,
                         rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
@@ -42,7 +50,9 @@ OTHER_SHAPES = {
 }
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+UNEQUAL = "uniform:128-2048"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+WIDTH = {"bfloat16": 2, "float32": 4}
 
 
 def peaks():
@@ -104,218 +114,313 @@ def model_numbers(cfg, n_layers):
     per_layer = d * (H + 2 * G) * hd + H * hd * d + 3 * d * F          # matrix weights of one layer
     head = V * d
     norms = (2 * n_layers + 1) * d
-    return {"layer_params": per_layer, "head_params": head, "norm_params": norms,
-            "kv_bytes_per_token": 2 * G * hd * n_layers * 2}
+    return {"layer_params": per_layer, "head_params": head, "norm_params": norms, "kv_per_token": 2 * G * hd * n_layers}
 
 
-def decode_bytes(nums, n_layers, batch, contexts):
-    """Bytes one decode step must read in bfloat16: every matrix once (the tied head is the
-    embedding matrix), the norm weights, the embedding rows of the batch, and the cached keys and
-    values of every live sequence."""
-    weights = 2 * (nums["layer_params"] * n_layers + nums["head_params"] + nums["norm_params"])
-    return weights + nums["kv_bytes_per_token"] * sum(contexts)
+def decode_bytes(nums, n_layers, contexts, width):
+    """Bytes one decode step must read at `width` bytes an element: every matrix once (the output head
+    once, tied or not), the norm weights, and the cached keys and values of every live sequence."""
+    weights = width * (nums["layer_params"] * n_layers + nums["head_params"] + nums["norm_params"])
+    return weights + width * nums["kv_per_token"] * sum(contexts)
 
 
-def prefill_flops(cfg, n_layers, T, logit_rows=1):
+def prefill_flops(cfg, n_layers, lengths, logit_rows=None):
+    """Products of a prompt step over sequences of `lengths` tokens: 2 per weight and token, the head
+    on `logit_rows` rows (default one per sequence), and causal attention (Q K^T and P V, half the
+    square each) within each sequence."""
     nums = model_numbers(cfg, n_layers)
-    linear = 2 * T * nums["layer_params"] * n_layers + 2 * logit_rows * nums["head_params"]
-    attn = 2 * T * T * cfg["num_attention_heads"] * cfg["head_dim"] * n_layers     # causal: QK^T and PV, half the square each
+    T = sum(lengths)
+    rows = len(lengths) if logit_rows is None else logit_rows
+    linear = 2 * T * nums["layer_params"] * n_layers + 2 * rows * nums["head_params"]
+    attn = sum(2 * n * n * cfg["num_attention_heads"] * cfg["head_dim"] * n_layers for n in lengths)
     return linear + attn
 
 
-def flush_l2(torch, buf):
+def flush_l2(buf):
     buf.add_(1)       # 512 MB read + written: more than the 126 MB L2
 
 
-def write_model(tmp, cfg_raw, seed):
-    import torch
-    from scriptling_llm_lib_b200 import models  # noqa: F401
-    from scriptling_llm_lib_b200.config.registry import architecture_for
-    from scriptling_llm_lib_b200.engine.model import DecoderModel
-    from scriptling_llm_lib_b200.weights.random_init import random_tensors
-    from scriptling_llm_lib_b200.weights.safetensors_io import write_safetensors
-    arch = architecture_for(cfg_raw["architectures"][0])
-    cfg = arch.config_class.from_dict(cfg_raw, "bench config")
-    specs = DecoderModel(arch.layout(cfg)).tensor_specs()
-    tensors = random_tensors(specs, seed, torch.bfloat16, "cuda:0")
-    os.makedirs(tmp, exist_ok=True)
-    open(os.path.join(tmp, "config.json"), "w").write(json.dumps(cfg.to_json_dict()))
-    write_safetensors(os.path.join(tmp, "model.safetensors"), {k: v.cpu() for k, v in tensors.items()})
-    del tensors
-    torch.cuda.empty_cache()
-    return cfg
+def parse_prompts(text):
+    """'uniform:LO-HI' -> (LO, HI)."""
+    kind, _, rng = text.partition(":")
+    lo, _, hi = rng.partition("-")
+    if kind != "uniform" or not lo.isdigit() or not hi.isdigit() or int(lo) < 1 or int(hi) < int(lo):
+        raise SystemExit(f"--prompts {text!r}: expected uniform:LO-HI with 1 <= LO <= HI")
+    return int(lo), int(hi)
 
 
-def time_decode(torch, eng, sampler, batch, context, steps, warmup, seed):
-    """Prefill `batch` prompts so that warmup + steps decode steps end at `context`; returns
-    (ms per step, contexts seen per timed step, launches per step)."""
-    import numpy as np
-    from scriptling_llm_lib_b200.csrc import bindings
-    from scriptling_llm_lib_b200.engine.step import StepEntry
-    from scriptling_llm_lib_b200.sampling.sampler import SamplingOptions
-    V = eng.layout.vocab_size
-    prompt_len = context - steps - warmup
-    rng = np.random.default_rng(seed)
-    seqs = [eng.open() for _ in range(batch)]
-    greedy = SamplingOptions()
-    try:
-        # prompts go in a few sequences at a time to bound the activations of one step
-        group = max(1, 16384 // prompt_len)
-        toks = None
-        last = []
-        for i in range(0, batch, group):
-            part = seqs[i:i + group]
-            logits = eng.step([StepEntry(s, rng.integers(0, V, prompt_len).tolist()) for s in part])
-            last.extend(sampler.sample(logits, greedy, [0] * len(part), [0] * len(part)).tolist())
-        toks = last
-        # the sampled ids stay on the device and feed the next step there: what is timed is the GPU's
-        # work, one replayed step and one sampling kernel after another, with no host round trip between
-        ids_dev = torch.tensor(toks, dtype=torch.int32, device=eng.device)
+class Bench:
+    def __init__(self, args, pk, tmp):
+        import numpy as np
+        import torch
+        from scriptling_llm_lib_b200 import llm
+        from scriptling_llm_lib_b200.csrc import bindings
+        self.np, self.torch, self.llm, self.bindings = np, torch, llm, bindings
+        self.args, self.pk, self.tmp = args, pk, tmp
+        self.l2 = None
+        self._fma = None
 
-        def one():
-            nonlocal ids_dev
-            logits = eng.decode_step_device(seqs, ids_dev)
-            ids_dev = sampler.sample(logits, greedy, [0] * batch, [0] * batch)
-        for _ in range(warmup):
-            one()
-        torch.cuda.synchronize()
-        l0 = bindings.LAUNCHES[0]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            one()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        launches = (bindings.LAUNCHES[0] - l0) / steps
-        first = prompt_len + warmup + 1               # keys read by the first timed step
-        contexts = [first + i for i in range(steps)]
-        return ms, contexts, launches
-    finally:
-        for s in seqs:
-            s.close()
+    # ------------------------------------------------------------------ models
+    def config(self, shape_name, layers=None):
+        shape = SHAPE if shape_name == "smollm2-1.7b" else OTHER_SHAPES[shape_name]
+        n_layers = layers or shape["num_hidden_layers"]
+        raw = dict(shape, num_hidden_layers=n_layers,
+                   max_position_embeddings=max(shape["max_position_embeddings"], self.args.context + 64))
+        path = os.path.join(self.tmp, f"{shape_name}-{n_layers}.json")
+        if not os.path.isfile(path):
+            with open(path, "w") as f:
+                json.dump(raw, f)
+        return raw, n_layers, f"random:{path}:0"
 
+    def load(self, spec, dtype, max_tokens, max_seqs):
+        import gc
+        self.llm.unload()
+        self.l2 = None
+        gc.collect()                 # an engine and its captured steps refer to each other
+        self.torch.cuda.empty_cache()
+        eng, sampler = self.llm.load(spec, dtype, "cuda:0", max_tokens=max_tokens, max_seqs=max_seqs)
+        self.l2 = self.torch.zeros(128 * 1024 * 1024, dtype=self.torch.float32, device="cuda:0")
+        return eng, sampler
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--shape", default="smollm2-1.7b", choices=["smollm2-1.7b"] + sorted(OTHER_SHAPES),
-                    help="layer sizes to run (default: the SmolLM2-1.7B shape of the headline metric)")
-    ap.add_argument("--layers", type=int, default=None,
-                    help="run fewer layers of the same sizes (named in config as layers_run / layers_full)")
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=CONTEXT)
-    ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
-                    help="run one part only (a small case to profile); the JSON line then holds that part alone")
-    args = ap.parse_args()
-    shape = SHAPE if args.shape == "smollm2-1.7b" else OTHER_SHAPES[args.shape]
-    if args.layers is None:
-        args.layers = shape["num_hidden_layers"]
+    def fma_peak(self):
+        if self._fma is None:
+            self._fma = self.bindings.ProbeKernels().fma_tflops()
+        return self._fma
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go package (go.mod) with CPU-only code; "
-                          "pip cannot install it and no Go toolchain is in the image"}))
-        return 0
-    if args.gpus != 1:
-        print(json.dumps({"error": "this library runs on one GPU; bench.py measures N=1 only", "n_gpus": args.gpus}))
-        return 2
-    args.warmup = max(3, args.warmup)
-
-    import numpy as np
-    import torch
-    from scriptling_llm_lib_b200 import llm
-    from scriptling_llm_lib_b200.csrc import bindings
-    from scriptling_llm_lib_b200.engine.step import StepEntry
-
-    pk = peaks()
-    cfg_raw = dict(shape, num_hidden_layers=args.layers,
-                   max_position_embeddings=max(shape["max_position_embeddings"], args.context + 64))
-    nums = model_numbers(cfg_raw, args.layers)
-    tmp = tempfile.mkdtemp(prefix="sllm_bench_")
-    model_dir = os.path.join(tmp, "model")
-    clocks = ClockSampler()
-    try:
-        write_model(model_dir, cfg_raw, seed=0)
-        biggest = 64 if not (args.no_points or args.only != "all") else args.batch
-        eng, sampler = llm.load(model_dir, "bfloat16", "cuda:0", max_tokens=biggest * args.context, max_seqs=biggest)
-        l2 = torch.zeros(128 * 1024 * 1024, dtype=torch.float32, device="cuda:0")
-        rng = np.random.default_rng(1)
-        V = cfg_raw["vocab_size"]
-
-        # ---- prefill of 2,048 tokens, L2 flushed between runs
+    # ------------------------------------------------------------------ prompt steps
+    def time_prompt_step(self, eng, lengths, seed, repeats=5, warm=3):
+        """Median device time of one packed prompt step over sequences of `lengths` tokens, L2 flushed
+        between runs; the logits of each sequence's last place are computed."""
+        from scriptling_llm_lib_b200.engine.step import StepEntry
+        torch = self.torch
+        rng = self.np.random.default_rng(seed)
+        V = eng.layout.vocab_size
         times = []
-        for i in range((3 + 5) if args.only != "decode" else 0):
-            flush_l2(torch, l2)
-            s = eng.open()
+        for i in range(warm + repeats):
+            flush_l2(self.l2)
+            seqs = [eng.open() for _ in lengths]
+            ids = [rng.integers(0, V, n).tolist() for n in lengths]
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ids = rng.integers(0, V, PREFILL_TOKENS).tolist()
             torch.cuda.synchronize()
             e0.record()
-            eng.step([StepEntry(s, ids)])
+            eng.step([StepEntry(s, t) for s, t in zip(seqs, ids)])
             e1.record()
             torch.cuda.synchronize()
-            s.close()
-            if i >= 3:
+            for s in seqs:
+                s.close()
+            if i >= warm:
                 times.append(e0.elapsed_time(e1))
-        pre_ms = statistics.median(times) if times else float("nan")
-        pre_flops = prefill_flops(cfg_raw, args.layers, PREFILL_TOKENS)
-        prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
-                   "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        return statistics.median(times)
 
+    def prefill_record(self, eng, cfg, n_layers, lengths, dtype, seed=1):
+        ms = self.time_prompt_step(eng, lengths, seed)
+        flops = prefill_flops(cfg, n_layers, lengths)
+        T = sum(lengths)
+        if dtype == "bfloat16":
+            peak, name = self.pk["bf16_tflops"], f"bf16 tensor ({self.pk['source']})"
+        else:
+            peak, name = self.fma_peak(), "float FMA (measured here)"
+        return {"value": round(T / ms * 1e3, 1), "tokens": T, "ms": round(ms, 3),
+                "frac": round(flops / (ms * 1e-3) / (peak * 1e12), 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+                "peak_tflops": round(peak, 1), "peak": name}
+
+    # ------------------------------------------------------------------ decode steps
+    def time_decode(self, eng, sampler, prompt_lens, steps, warmup, seed):
+        """Prefill one prompt per entry of `prompt_lens`, then warmup + steps decode steps with the
+        sampled ids fed back on the device; returns (ms per step, mean keys read per sequence and
+        timed step, launches per step)."""
+        from scriptling_llm_lib_b200.engine.step import StepEntry
+        from scriptling_llm_lib_b200.sampling.sampler import SamplingOptions
+        torch, np = self.torch, self.np
+        V = eng.layout.vocab_size
+        batch = len(prompt_lens)
+        rng = np.random.default_rng(seed)
+        seqs = [eng.open() for _ in range(batch)]
+        greedy = SamplingOptions()
+        try:
+            # prompts go in a few sequences at a time to bound the activations of one step
+            last, i = [], 0
+            while i < batch:
+                j, tok = i, 0
+                while j < batch and (j == i or tok + prompt_lens[j] <= 16384):
+                    tok += prompt_lens[j]
+                    j += 1
+                logits = eng.step([StepEntry(s, rng.integers(0, V, n).tolist()) for s, n in zip(seqs[i:j], prompt_lens[i:j])])
+                last.extend(sampler.sample(logits, greedy, [0] * (j - i), [0] * (j - i)).tolist())
+                i = j
+            ids_dev = torch.tensor(last, dtype=torch.int32, device=eng.device)
+
+            def one():
+                nonlocal ids_dev
+                logits = eng.decode_step_device(seqs, ids_dev)
+                ids_dev = sampler.sample(logits, greedy, [0] * batch, [0] * batch)
+            for _ in range(warmup):
+                one()
+            torch.cuda.synchronize()
+            l0 = self.bindings.LAUNCHES[0]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            eng.check_errors()
+            ms = e0.elapsed_time(e1) / steps
+            launches = (self.bindings.LAUNCHES[0] - l0) / steps
+            # the first timed step reads prompt + warmup + 1 keys of each sequence, each later step one more
+            contexts = [n + warmup + 1 + (steps - 1) / 2 for n in prompt_lens]
+            return ms, contexts, launches
+        finally:
+            for s in seqs:
+                s.close()
+
+    def decode_record(self, eng, sampler, cfg, n_layers, prompt_lens, steps, warmup, seed, dtype):
+        ms, contexts, launches = self.time_decode(eng, sampler, prompt_lens, steps, warmup, seed)
+        nums = model_numbers(cfg, n_layers)
+        achieved = decode_bytes(nums, n_layers, contexts, WIDTH[dtype]) / (ms * 1e-3) / 1e9
+        return {"value": round(len(prompt_lens) / ms * 1e3, 1), "ms": round(ms, 4), "gbs": round(achieved, 1),
+                "frac": round(achieved / self.pk["hbm_gbs"], 4)}, launches
+
+    def equal_prompts(self, batch, steps, warmup):
+        return [self.args.context - steps - warmup] * batch
+
+
+def run(args):
+    import numpy as np
+    import torch
+    pk = peaks()
+    tmp = tempfile.mkdtemp(prefix="sllm_bench_")
+    clocks = ClockSampler()
+    b = Bench(args, pk, tmp)
+    llm = b.llm
+    dtype = args.dtype
+    line = None
+    try:
+        cfg, n_layers, spec = b.config(args.shape, args.layers)
+        full_layers = (SHAPE if args.shape == "smollm2-1.7b" else OTHER_SHAPES[args.shape])["num_hidden_layers"]
+        nums = model_numbers(cfg, n_layers)
+        want_points = not args.no_points and args.only == "all" and args.prompts is None
+        biggest = max(64 if want_points else 1, args.batch)
+        eng, sampler = b.load(spec, dtype, biggest * args.context, biggest)
+        V = cfg["vocab_size"]
+
+        # ---- the prompt step: 2,048 tokens, or a batch of unequal prompts in one packed step
+        if args.prompts is not None:
+            lo, hi = parse_prompts(args.prompts)
+            lengths = np.random.default_rng(7).integers(lo, hi + 1, args.batch).tolist()
+        else:
+            lengths = [PREFILL_TOKENS]
+        prefill = b.prefill_record(eng, cfg, n_layers, lengths, dtype) if args.only != "decode" else None
+        if args.prompts is not None and prefill is not None:
+            prefill["prompts"] = {"dist": args.prompts, "seed": 7, "n": len(lengths), "min": min(lengths), "max": max(lengths)}
         if args.only == "prefill":
-            print(json.dumps({"only": "prefill", "layers_run": args.layers, "prefill": prefill}))
+            print(json.dumps({"only": "prefill", "shape": args.shape, "dtype": dtype, "layers_run": n_layers, "prefill": prefill}))
             return 0
+
         # ---- the decode step at the headline batch, clocks sampled meanwhile
         clocks.start()
         time.sleep(0.5)
         c0 = clocks.mark()
-        ms, contexts, launches = time_decode(torch, eng, sampler, args.batch, args.context, args.steps, args.warmup, 2)
+        prompt_lens = lengths if args.prompts is not None else b.equal_prompts(args.batch, args.steps, args.warmup)
+        head, launches = b.decode_record(eng, sampler, cfg, n_layers, prompt_lens, args.steps, args.warmup, 2, dtype)
         c1 = clocks.mark()
-        value = args.batch / ms * 1e3
-        step_bytes = decode_bytes(nums, args.layers, args.batch, [statistics.mean(contexts)] * args.batch)
-        achieved = step_bytes / (ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
-
-        points = {}
+        ms, value = head["ms"], head["value"]
+        roofline = {"bound": "hbm", "achieved": head["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": head["frac"],
+                    "peaks": pk["source"]}
         if args.only == "decode":
-            print(json.dumps({"only": "decode", "layers_run": args.layers, "batch": args.batch, "ms_per_step": round(ms, 4),
-                              "value": round(value, 1), "roofline": roofline}))
+            print(json.dumps({"only": "decode", "shape": args.shape, "dtype": dtype, "layers_run": n_layers, "batch": args.batch,
+                              "ms_per_step": ms, "value": value, "roofline": roofline}))
             return 0
+
         # ---- end to end through the Python entry point: host ids in, host ids out, every step
         e2e = None
         if not args.no_e2e:
-            prompt_len = args.context - args.steps - 1
-            prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(args.batch)]
+            rng = np.random.default_rng(1)
+            e2e_lens = prompt_lens if args.prompts is not None else [args.context - args.steps - 2] * args.batch
+            prompts = [rng.integers(0, V, n).tolist() for n in e2e_lens]
             marks = {}
 
             def on_step(i, toks):
+                # called when the first sampled token of every sequence has reached the host; the loop has
+                # already queued decode step 1 by then, and the synchronize lets it finish before the clock starts
                 if i == 0:
                     torch.cuda.synchronize()
                     marks["t0"] = time.perf_counter()
                 return False
             # warm-up with the same lengths: the cache is sized and the step's graph captured before the timed call
-            llm.generate(model_dir, prompts, args.steps + 1, "greedy", temperature=0.0, stop_ids=[])
-            out = llm.generate(model_dir, prompts, args.steps + 1, "greedy", temperature=0.0, stop_ids=[], on_step=on_step)
+            llm.generate(spec, prompts, args.steps + 2, "greedy", temperature=0.0, stop_ids=[], dtype=dtype)
+            out = llm.generate(spec, prompts, args.steps + 2, "greedy", temperature=0.0, stop_ids=[], dtype=dtype, on_step=on_step)
             torch.cuda.synchronize()
             dt = time.perf_counter() - marks["t0"]
-            assert all(len(o) == args.steps + 1 for o in out)
+            assert all(len(o) == args.steps + 2 for o in out)
             n_pages = -(-args.context // 64)
             e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
-                   "h2d_bytes_per_step": 4 * (args.batch * (5 + n_pages) + 1), "d2h_bytes_per_step": 4 * args.batch}
+                   "h2d_bytes_per_step": 4 * (args.batch * (5 + n_pages) + 1), "d2h_bytes_per_step": 4 * args.batch,
+                   "window": f"decode steps 2..{args.steps + 1} of a generation of {args.steps + 2} tokens: {args.steps} steps, "
+                             "wall clock, from after the first decode step to the last token on the host"}
         c1 = clocks.mark()          # the clock samples cover the device-timed steps and the end-to-end run
-        if not args.no_points:
-            for b in (1, 64):
-                k = max(8, args.steps // 4) if b == 64 else args.steps
-                pms, _, _ = time_decode(torch, eng, sampler, b, args.context, k, args.warmup, 3 + b)
-                points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
 
+        points = {}
+        if want_points:
+            for bb in (1, 64):
+                k = max(8, args.steps // 4) if bb == 64 else args.steps
+                rec, _ = b.decode_record(eng, sampler, cfg, n_layers, b.equal_prompts(bb, k, args.warmup), k, args.warmup, 3 + bb, dtype)
+                points[f"decode_b{bb}"] = rec["value"]
+                points[f"decode_b{bb}_frac"] = rec["frac"]
         clk = clocks.summary(c0, c1)
+
+        line = {
+            "metric": f"decode tokens/s ({args.shape} shape, random weights, batch {args.batch}, context {args.context})",
+            "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if dtype == "bfloat16" else "f32",
+            "data": "synthetic: uniform random token ids, random-init weights N(0,0.02) drawn on the device",
+            "impl": "ours",
+            "config": {"model": f"{args.shape} shape", "layers_run": n_layers, "layers_full": full_layers,
+                       "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                       "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                       "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                       "rope_theta": cfg["rope_theta"], "rms_eps": cfg["rms_norm_eps"], "tied": cfg["tie_word_embeddings"],
+                       "global_batch": args.batch, "seq_len": args.context,
+                       "prompt_len": args.prompts or (args.context - args.steps - args.warmup),
+                       "parallelism": "1gpu", "l2": "step inputs (weights+cache) exceed L2; prefill flushes L2",
+                       "sampling": "greedy"},
+            "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+            "gpu_launches": int(round(launches * args.steps)), "clocks": clk,
+        }
+
+        # ---- the same model on the true 32-bit path
+        if args.f32 and dtype == "bfloat16" and args.prompts is None:
+            eng = sampler = None     # the bfloat16 engine's weights and cache go before the next one comes
+            eng, sampler = b.load(spec, "float32", 64 * args.context, 64)
+            f32 = {"prefill": b.prefill_record(eng, cfg, n_layers, [PREFILL_TOKENS], "float32"), "fma_peak_tflops": round(b.fma_peak(), 1)}
+            for bb in (1, 8, 64):
+                k = max(8, args.steps // 4) if bb == 64 else args.steps
+                rec, _ = b.decode_record(eng, sampler, cfg, n_layers, b.equal_prompts(bb, k, args.warmup), k, args.warmup, 40 + bb, "float32")
+                f32[f"decode_b{bb}"] = rec
+            line["f32"] = f32
+
+        # ---- the two further shapes of the family
+        if args.shapes and dtype == "bfloat16" and args.prompts is None and args.shape == "smollm2-1.7b" and args.layers is None:
+            shapes = {}
+            lo, hi = parse_prompts(UNEQUAL)
+            cfg2, L2, spec2 = b.config("llama3.2-1b")
+            lengths = np.random.default_rng(7).integers(lo, hi + 1, 8).tolist()
+            eng = sampler = None
+            eng, sampler = b.load(spec2, "bfloat16", 8 * args.context, 8)
+            rec = {"prompts": UNEQUAL, "batch": 8, "prefill": b.prefill_record(eng, cfg2, L2, lengths, "bfloat16")}
+            rec["decode"], _ = b.decode_record(eng, sampler, cfg2, L2, lengths, args.steps, args.warmup, 50, "bfloat16")
+            shapes["llama3.2-1b"] = rec
+            cfg3, L3, spec3 = b.config("llama3.1-8b")
+            eng = sampler = None
+            eng, sampler = b.load(spec3, "bfloat16", 64 * args.context, 64)
+            rec = {"context": args.context, "prefill": b.prefill_record(eng, cfg3, L3, [PREFILL_TOKENS], "bfloat16")}
+            for bb in (1, 8, 64):
+                k = max(8, args.steps // 4) if bb == 64 else args.steps
+                rec[f"decode_b{bb}"], _ = b.decode_record(eng, sampler, cfg3, L3, b.equal_prompts(bb, k, args.warmup), k,
+                                                          args.warmup, 60 + bb, "bfloat16")
+            shapes["llama3.1-8b"] = rec
+            line["shapes"] = shapes
     finally:
         clocks.stop()
         try:
@@ -324,26 +429,43 @@ def main():
             shutil.rmtree(tmp, ignore_errors=True)
         except Exception:
             pass
-
-    line = {
-        "metric": f"decode tokens/s ({args.shape} shape, random weights, batch {args.batch}, context {args.context})",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: uniform random token ids, random-init weights N(0,0.02)",
-        "impl": "ours",
-        "config": {"model": f"{args.shape} shape", "layers_run": args.layers, "layers_full": shape["num_hidden_layers"],
-                   "hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
-                   "kv_heads": shape["num_key_value_heads"], "head_dim": shape["head_dim"],
-                   "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
-                   "rope_theta": shape["rope_theta"], "rms_eps": shape["rms_norm_eps"], "tied": shape["tie_word_embeddings"],
-                   "global_batch": args.batch, "seq_len": args.context, "prompt_len": args.context - args.steps - args.warmup,
-                   "parallelism": "1gpu", "l2": "step inputs (weights+cache) exceed L2; prefill flushes L2",
-                   "sampling": "greedy"},
-        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
-        "gpu_launches": int(round(launches * args.steps)), "clocks": clk,
-    }
     print(json.dumps(line))
     return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shape", default="smollm2-1.7b", choices=["smollm2-1.7b"] + sorted(OTHER_SHAPES),
+                    help="layer sizes of the headline run (default: the SmolLM2-1.7B shape of the headline metric)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="precision of the headline run; float32 is the true 32-bit path")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="run fewer layers of the same sizes (named in config as layers_run / layers_full)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--prompts", default=None, metavar="uniform:LO-HI",
+                    help="a batch of unequal prompts, lengths uniform in LO..HI (seeded): one packed prompt step, then "
+                         "decoding from there (instead of equal prompts that end at --context)")
+    ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-f32", dest="f32", action="store_false", help="skip the 32-bit path's measurements")
+    ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the Llama-3.2-1B and Llama-3.1-8B sizes")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
+                    help="run one part only (a small case to profile); the JSON line then holds that part alone")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go package (go.mod) with CPU-only code; "
+                          "pip cannot install it and no Go toolchain is in the image"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": "this library runs on one GPU; bench.py measures N=1 only", "n_gpus": args.gpus}))
+        return 2
+    args.warmup = max(3, args.warmup)
+    return run(args)
 
 
 if __name__ == "__main__":

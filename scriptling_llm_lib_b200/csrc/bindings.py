@@ -105,15 +105,30 @@ class KernelSet:
 
     # ------------------------------------------------------------------ matrix products
     def gemm_nt(self, a, w, out):
-        """out[M,N] = a[M,K] @ w[N,K]^T; `out` is of this set's dtype or float32."""
+        """out[M,N] = a[M,K] @ w[N,K]^T; `out` is of this set's dtype or float32. A float32 `out` of
+        shape [P,M,N] receives P partial sums (K cut into P parts); the reader adds them."""
         M, K = a.shape
         N = w.shape[0]
-        if w.shape[1] != K or tuple(out.shape) != (M, N):
-            raise KernelError(f"gemm_nt shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        ksplit = out.shape[0] if out.dim() == 3 else 1
+        if w.shape[1] != K or tuple(out.shape[-2:]) != (M, N) or (out.dim() == 3 and out.dtype != torch.float32):
+            raise KernelError(f"gemm_nt shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
         out_f32 = 1 if (out.dtype == torch.float32 and self.dtype != torch.float32) else 0
         _check(self._fn("gemm_nt")(_ptr(a, self.dtype, "a"), _ptr(w, self.dtype, "w"),
                                    _ptr(out, torch.float32 if out_f32 else self.dtype, "out"), c_int(M), c_int(N),
-                                   c_int(K), c_int(K), c_int(K), c_int(N), c_int(out_f32), _stream()), "gemm_nt")
+                                   c_int(K), c_int(a.stride(0)), c_int(w.stride(0)), c_int(N), c_int(out_f32),
+                                   c_int(ksplit), _stream()), "gemm_nt")
+
+    @staticmethod
+    def gemm_nt_split(m: int, n_out: int, k: int, sm_count: int) -> int:
+        """Into how many parts the generic product cuts K when its reader takes partial sums: none for
+        up to 8 rows (a block per four columns fills the GPU already) or when the 128-column tiles
+        fill it; else enough parts for about two blocks per SM, each at least 256 deep."""
+        if m <= 8 or k % 4:
+            return 1
+        tiles = -(-n_out // 128) * -(-m // (64 if m <= 64 else 128))
+        if tiles >= sm_count:
+            return 1
+        return max(1, min(2 * sm_count // tiles, k // 256, 16))
 
     # ------------------------------------------------------------------ rotary + cache write
     def rope_kv_write(self, qkv, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv, head_dim, rot,
@@ -137,6 +152,32 @@ class KernelSet:
                                       _ptr(kpages, self.dtype, "kpages"), _ptr(vpages, self.dtype, "vpages"),
                                       c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv), c_int(head_dim),
                                       c_int(window or 0), c_float(scale), _stream()), "attn_paged")
+
+    def attn_decode_split(self, q, out, seq_pos0, block_table, kpages, vpages, part, n_seqs, n_heads, n_kv, head_dim,
+                          window, scale, n_split):
+        """One query per sequence, each sequence's keys split over `n_split` blocks (then merged);
+        `part`: float32 scratch of n_seqs * n_heads * n_split * (head_dim + 2) elements, or None for one split."""
+        need = n_seqs * n_heads * n_split * (head_dim + 2) if n_split > 1 else 0
+        if need and (part is None or part.numel() < need):
+            raise KernelError(f"attn_decode_split scratch holds {0 if part is None else part.numel()} floats, needs {need}")
+        _check(self._fn("attn_decode_split")(_ptr(q, self.dtype, "q") if q.is_contiguous() else c_void_p(q.data_ptr()),
+                                             c_int(q.stride(0)), _ptr(out, self.dtype, "out"),
+                                             _ptr(seq_pos0, torch.int32, "seq_pos0"),
+                                             _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
+                                             _ptr(kpages, self.dtype, "kpages"), _ptr(vpages, self.dtype, "vpages"),
+                                             _ptr(part, torch.float32, "part"), c_int(n_seqs), c_int(n_heads), c_int(n_kv),
+                                             c_int(head_dim), c_int(window or 0), c_float(scale), c_int(n_split), _stream()),
+               "attn_decode_split")
+
+    @staticmethod
+    def attn_decode_split_takes(head_dim: int, q_ld: int) -> bool:
+        return head_dim % 4 == 0 and 4 <= head_dim <= 512 and q_ld % 4 == 0
+
+    @staticmethod
+    def attn_decode_splits(n_seqs: int, n_heads: int, pages: int, sm_count: int) -> int:
+        """Blocks per (sequence, head): enough for about six blocks of four warps per SM, at most one per page."""
+        want = -(-6 * sm_count // max(1, n_seqs * n_heads))
+        return max(1, min(want, pages, 64))
 
     # ------------------------------------------------------------------ feed-forward
     def swiglu(self, gate_up, out, tiled=False):
@@ -411,6 +452,52 @@ class CastKernels:
         fn.restype = c_int
         _check(fn(_ptr(src, torch.float32, "src"), _ptr(dst, torch.bfloat16, "dst"), c_longlong(src.numel()), _stream()),
                "cast_f32_to_bf16")
+
+
+class RandomKernels:
+    """Fills tensors with the counter-based generator of random-weights mode (lib_random.cu)."""
+
+    def __init__(self):
+        self.lib = load_library("random")
+        self.lib.sllm_fill_normal.restype = c_int
+        self.lib.sllm_fill_integer.restype = c_int
+
+    def fill_normal(self, out, seed: int, index: int, mean: float, std: float):
+        if out.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"fill_normal writes float32 or bfloat16, not {out.dtype}")
+        _check(self.lib.sllm_fill_normal(_ptr(out, None, "out"), c_int(0 if out.dtype == torch.float32 else 1),
+                                         c_longlong(out.numel()), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+                                         ctypes.c_uint(index), ctypes.c_double(mean), ctypes.c_double(std), _stream()),
+               "fill_normal")
+
+    def fill_integer(self, out, seed: int, index: int, modulus: int):
+        _check(self.lib.sllm_fill_integer(_ptr(out, torch.int32, "out"), c_longlong(out.numel()),
+                                          ctypes.c_ulonglong(seed & (2 ** 64 - 1)), ctypes.c_uint(index),
+                                          ctypes.c_uint(modulus), _stream()), "fill_integer")
+
+
+class ProbeKernels:
+    """Measuring sticks for benchmarks (lib_probe.cu)."""
+
+    def __init__(self):
+        self.lib = load_library("probe")
+        self.lib.sllm_fma_loop.restype = c_int
+
+    def fma_tflops(self, device="cuda:0", blocks_per_sm: int = 8, iters: int = 1 << 15, repeats: int = 5) -> float:
+        """Best-of-`repeats` rate of float fused multiply-adds (2 operations each) in TFLOP/s."""
+        dev = torch.device(device)
+        blocks = torch.cuda.get_device_properties(dev).multi_processor_count * blocks_per_sm
+        out = torch.empty(blocks * 256, dtype=torch.float32, device=dev)
+        best = 0.0
+        for i in range(repeats + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _check(self.lib.sllm_fma_loop(_ptr(out, torch.float32, "out"), c_int(blocks), c_int(iters), _stream()), "fma_loop")
+            e1.record()
+            e1.synchronize()
+            if i:
+                best = max(best, blocks * 256 * iters * 16 / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        return best
 
 
 class SamplingKernels:

@@ -28,7 +28,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"
 LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "f32": ("lib_f32.cu", ("common.cuh", "generic_kernels.cuh", "generic_launchers.inc")),
     "bf16": ("lib_bf16.cu", ("common.cuh", "generic_kernels.cuh", "generic_launchers.inc")),
-    "sampling": ("lib_sampling.cu", ("common.cuh",)),
+    "sampling": ("lib_sampling.cu", ("common.cuh", "philox.cuh")),
+    "random": ("lib_random.cu", ("common.cuh", "philox.cuh")),
+    "probe": ("lib_probe.cu", ("common.cuh",)),
     "decode_bf16": ("decode_bf16.cu", ("common.cuh", "attn_decode_noalloc.h")),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
     "attn_prefill_tcgen05": ("attn_prefill_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
@@ -65,25 +67,73 @@ def _source_hash(name: str) -> str:
     return h.hexdigest()[:20]
 
 
-def build_dir() -> Path:
-    """csrc/_build when it can be written, else a per-user folder under the system's temp dir."""
+def _fallback_dir() -> Path:
+    """A per-user folder for built objects when the package folder cannot be written: under
+    $XDG_CACHE_HOME or ~/.cache, else under the system's temp folder."""
+    base = os.environ.get("XDG_CACHE_HOME") or (os.path.join(os.path.expanduser("~"), ".cache")
+                                                if os.path.expanduser("~") not in ("", "~", "/") else "")
+    if base:
+        try:
+            os.makedirs(base, mode=0o700, exist_ok=True)
+            if os.access(base, os.W_OK | os.X_OK):
+                return Path(base) / "sllm_b200_build"
+        except OSError:
+            pass
+    return Path(tempfile.gettempdir()) / f"sllm_b200_build_{os.getuid()}"
+
+
+def _private_dir(d: Path, create: bool) -> bool:
+    """True when `d` is a real folder (no symlink) owned by this user that nobody else can write:
+    objects are loaded into the process from it, so a folder anyone could have prepared is refused."""
+    if create:
+        try:
+            os.mkdir(d, 0o700)
+        except FileExistsError:
+            pass
+        except OSError:
+            return False
+    try:
+        st = os.lstat(d)
+    except OSError:
+        return False
+    import stat
+    return stat.S_ISDIR(st.st_mode) and st.st_uid == os.getuid() and not (st.st_mode & 0o022)
+
+
+def _tree_writable() -> bool:
     d = CSRC / "_build"
     try:
         d.mkdir(exist_ok=True)
         probe = d / f".probe{os.getpid()}"
         probe.write_text("")
         probe.unlink()
-        return d
+        return True
     except OSError:
-        d = Path(tempfile.gettempdir()) / f"sllm_b200_build_{os.getuid()}"
-        d.mkdir(exist_ok=True)
-        return d
+        return False
+
+
+def build_dir() -> Path:
+    """csrc/_build when it can be written; else a private per-user folder (mode 0700, checked)."""
+    if _tree_writable():
+        return CSRC / "_build"
+    d = _fallback_dir()
+    if not _private_dir(d, create=True):
+        raise KernelBuildError(f"{CSRC / '_build'} cannot be written and the fallback folder {d} is not a private "
+                               f"folder of this user (it must be a real directory owned by uid {os.getuid()} that no "
+                               "one else can write); remove it or set XDG_CACHE_HOME")
+    return d
 
 
 def library_path(name: str) -> Path | None:
-    """An up-to-date object for `name`, if one is there already."""
+    """An up-to-date object for `name`, if one is there already: in csrc/_build, and only when
+    that folder cannot be written also in the private fallback folder."""
     tag = _source_hash(name)
-    for d in (CSRC / "_build", Path(tempfile.gettempdir()) / f"sllm_b200_build_{os.getuid()}"):
+    dirs = [CSRC / "_build"]
+    if not _tree_writable():
+        fb = _fallback_dir()
+        if _private_dir(fb, create=False):
+            dirs.append(fb)
+    for d in dirs:
         so, stamp = d / f"sllm_{name}.so", d / f"sllm_{name}.hash"
         if so.is_file() and stamp.is_file() and stamp.read_text().strip() == tag:
             return so

@@ -181,28 +181,180 @@ gemm_nt_tiled_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __r
   }
 }
 
-// Few rows (M <= MT): every weight row is read once and used for all M rows. One warp per output
-// column; lanes stride over k; warp-shuffle sum.
-template <typename TI, typename TO, int MT>
-__global__ void gemv_nt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restrict__ C, int M, int N,
-                               int K, int lda, int ldb, int ldc) {
-  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int n = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (n >= N) return;
-  const TI* brow = B + (size_t)n * ldb;
-  float acc[MT];
+// The same product for many rows with register tiles: a block of 256 threads owns a BM x 128 tile of
+// C, a thread (BM/16) x 8 outputs as (BM/64) x 2 groups of 4 x 4, 64 columns / rows apart so that its
+// operands are 16-byte shared-memory loads. A and B tiles of 16 k are fetched from global memory as
+// 16-byte vectors into registers while the previous tile is multiplied, then stored k-major
+// (transposed) into the other of two shared buffers: one barrier per tile. Each output is still one
+// ascending-k chain of fused multiply-adds in float. Needs K, lda, ldb in multiples of 4 elements
+// and 16-byte (float) / 8-byte (bfloat16) aligned rows; the launcher falls back to the kernel above
+// otherwise. With several blocks along blockIdx.z, block z takes the z-th contiguous part of K
+// (k_per_split elements, a multiple of 16) and C receives float partial sums at C + z * M * ldc.
+template <typename TI, typename TO, int BM>
+__global__ void __launch_bounds__(256, 2)
+gemm_nt_regtile_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restrict__ C, int M, int N, int K,
+                       int lda, int ldb, int ldc, int k_per_split) {
+  constexpr int BN = 128, BK = 16, TMG = BM / 64;          // TMG groups of 4 rows per thread
+  constexpr int A_VEC = BM * BK / 4 / 256;                 // 16-byte vectors of the A tile per thread (1 or 2)
+  constexpr int B_VEC = BN * BK / 4 / 256;                 // 2
+  __shared__ __align__(16) float As[2][BK][BM];
+  __shared__ __align__(16) float Bs[2][BK][BN];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int k_begin = blockIdx.z * k_per_split, k_end = min(K, k_begin + k_per_split);
+  TO* Cz = C + (size_t)blockIdx.z * M * ldc;
+
+  float acc[TMG * 4][8];
 #pragma unroll
-  for (int m = 0; m < MT; m++) acc[m] = 0.f;
-  for (int k = lane; k < K; k += 32) {
-    float b = to_f32(brow[k]);
+  for (int i = 0; i < TMG * 4; i++)
 #pragma unroll
-    for (int m = 0; m < MT; m++)
-      if (m < M) acc[m] = fmaf(to_f32(A[(size_t)m * lda + k]), b, acc[m]);
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+
+  // vector v of this thread: row = (tid + 256 v) % rows, k quad = (tid + 256 v) / rows: a warp reads 32
+  // consecutive rows at one k quad, and stores 32 consecutive floats of one k row (no bank conflict)
+  float4 ra[A_VEC], rb[B_VEC];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int v = 0; v < A_VEC; v++) {
+      int e = tid + 256 * v, row = e % BM, kq = e / BM;
+      int gm = m0 + row, gk = k0 + kq * 4;
+      ra[v] = (gm < M && gk < k_end) ? ld4(A + (size_t)gm * lda + gk) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int v = 0; v < B_VEC; v++) {
+      int e = tid + 256 * v, row = e % BN, kq = e / BN;
+      int gn = n0 + row, gk = k0 + kq * 4;
+      rb[v] = (gn < N && gk < k_end) ? ld4(B + (size_t)gn * ldb + gk) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int v = 0; v < A_VEC; v++) {
+      int e = tid + 256 * v, row = e % BM, kq = e / BM;
+      As[buf][kq * 4 + 0][row] = ra[v].x; As[buf][kq * 4 + 1][row] = ra[v].y;
+      As[buf][kq * 4 + 2][row] = ra[v].z; As[buf][kq * 4 + 3][row] = ra[v].w;
+    }
+#pragma unroll
+    for (int v = 0; v < B_VEC; v++) {
+      int e = tid + 256 * v, row = e % BN, kq = e / BN;
+      Bs[buf][kq * 4 + 0][row] = rb[v].x; Bs[buf][kq * 4 + 1][row] = rb[v].y;
+      Bs[buf][kq * 4 + 2][row] = rb[v].z; Bs[buf][kq * 4 + 3][row] = rb[v].w;
+    }
+  };
+
+  fetch(k_begin);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = k_begin; k0 < k_end; k0 += BK) {
+    const bool more = k0 + BK < k_end;
+    if (more) fetch(k0 + BK);
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[TMG * 4], b[8];
+#pragma unroll
+      for (int g = 0; g < TMG; g++) {
+        float4 t = *(const float4*)&As[buf][kk][g * 64 + ty * 4];
+        a[4 * g] = t.x; a[4 * g + 1] = t.y; a[4 * g + 2] = t.z; a[4 * g + 3] = t.w;
+      }
+#pragma unroll
+      for (int g = 0; g < 2; g++) {
+        float4 t = *(const float4*)&Bs[buf][kk][g * 64 + tx * 4];
+        b[4 * g] = t.x; b[4 * g + 1] = t.y; b[4 * g + 2] = t.z; b[4 * g + 3] = t.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TMG * 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (more) stash(buf ^ 1);
+    __syncthreads();
+    buf ^= 1;
   }
+  const bool vec_out = (ldc & 3) == 0 && ((uintptr_t)Cz % (4 * sizeof(TO))) == 0;
 #pragma unroll
-  for (int m = 0; m < MT; m++) {
-    float v = warp_sum(acc[m]);
-    if (lane == 0 && m < M) C[(size_t)m * ldc + n] = from_f32<TO>(v);
+  for (int i = 0; i < TMG * 4; i++) {
+    int gm = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int g = 0; g < 2; g++) {
+      int gn = n0 + g * 64 + tx * 4;
+      TO* dst = Cz + (size_t)gm * ldc + gn;
+      if (vec_out && gn + 3 < N) {
+        st4(dst, make_float4(acc[i][4 * g], acc[i][4 * g + 1], acc[i][4 * g + 2], acc[i][4 * g + 3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (gn + j < N) dst[j] = from_f32<TO>(acc[i][4 * g + j]);
+      }
+    }
+  }
+}
+
+// Few rows (M <= MT): every weight row is read from memory once and used for all M rows. A block of
+// 256 threads owns NC output columns; its threads split K in 16-byte vectors (thread t takes elements
+// 4t.., 4(t+256)..), so the block streams NC weight rows with every load of the warp contiguous; the
+// M x NC partial sums of a thread are folded across the warp by a reduce-scatter (31 shuffles for 32
+// sums) and across the warps through shared memory in a fixed order. With KSPLIT blocks along
+// blockIdx.y, block y takes the y-th contiguous part of K and C receives float partial sums at
+// C + y * M * ldc (the reader, a norm, adds them). Needs K, lda, ldb in multiples of 4 elements.
+template <typename TI, typename TO, int MT, int NC>
+__global__ void __launch_bounds__(256)
+gemv_nt_block_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restrict__ C, int M, int N, int K,
+                     int lda, int ldb, int ldc, int k_per_split) {
+  constexpr int NV = MT * NC;                              // sums per thread; a power of two <= 32
+  __shared__ float red[8][NV];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n0 = blockIdx.x * NC;
+  const int k_begin = blockIdx.y * k_per_split, k_end = min(K, k_begin + k_per_split);
+  TO* Cz = C + (size_t)blockIdx.y * M * ldc;
+  float acc[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) acc[i] = 0.f;
+  const TI* brow[NC];
+#pragma unroll
+  for (int c = 0; c < NC; c++) brow[c] = B + (size_t)min(n0 + c, N - 1) * ldb;
+
+  for (int k = k_begin + tid * 4; k < k_end; k += 256 * 4) {
+    float4 b[NC];
+#pragma unroll
+    for (int c = 0; c < NC; c++) b[c] = ld4(brow[c] + k);
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+      float4 a = (m < M) ? ld4(A + (size_t)m * lda + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < NC; c++) {
+        float s = acc[m * NC + c];
+        s = fmaf(a.x, b[c].x, s); s = fmaf(a.y, b[c].y, s); s = fmaf(a.z, b[c].z, s); s = fmaf(a.w, b[c].w, s);
+        acc[m * NC + c] = s;
+      }
+    }
+  }
+  // reduce-scatter over the warp: after the step with offset o a lane keeps the half of its sums that
+  // its bit o selects; after log2(NV) steps it holds one sum, whose index its upper lane bits spell
+  int held = 0;
+#pragma unroll
+  for (int n = NV, o = 16; n > 1; n >>= 1, o >>= 1) {
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; i++) {
+      float keep = up ? acc[i + n / 2] : acc[i];
+      float send = up ? acc[i] : acc[i + n / 2];
+      acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+    if (up) held += n / 2;
+  }
+  float v = acc[0];
+#pragma unroll
+  for (int o = 16 / NV; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);   // lanes that hold the same index
+  if ((lane & (32 / NV - 1)) == 0) red[warp][held] = v;
+  __syncthreads();
+  if (tid < NV) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) t += red[w][tid];
+    int m = tid / NC, c = tid % NC;
+    if (m < M && n0 + c < N) Cz[(size_t)m * ldc + n0 + c] = from_f32<TO>(t);
   }
 }
 
@@ -447,6 +599,332 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_paged_kernel(AttnArgs p) {
       int dd = lane + 32 * a;
       if (dd < hd) out[(size_t)(row0 + r0 + qi) * ((size_t)p.H * hd) + (size_t)h * hd + dd] = from_f32<A>(acc[i][a] * inv);
     }
+  }
+}
+
+// ------------------------------------------------------------------ the same attention with register tiles
+// One block of 256 threads: 64 consecutive queries of one sequence and one query head against tiles of
+// 64 keys. Thread (ty = tid / 16, tx = tid % 16) owns queries 4ty..4ty+3; of the scores it owns keys
+// 4tx..4tx+3 of the tile, of the output the dims 4(tx + 16g)..+3. Scores S = Q K^T and the output
+// O += P V are small FMA products out of shared memory with 16-byte loads: Q and the key tile are
+// kept k-major (transposed: Qs[d][query], Ks[d][key]), the values row-major, the probabilities
+// row-major with a padded stride. Softmax statistics live in registers, the row maximum and sum are
+// folded over the 16 lanes that share a query. The same mathematics and masks as the kernel above;
+// head widths in multiples of 4 up to 64 * NG.
+#define ATT2_BQ 64
+#define ATT2_BK 64
+#define ATT2_PS (ATT2_BK + 4)
+
+template <typename A, int NG>
+__global__ void __launch_bounds__(256) attn_paged_tiled_kernel(AttnArgs p) {
+  extern __shared__ __align__(16) float att_sm[];
+  const int hd = p.hd;
+  float* Qs = att_sm;                          // [hd][64]
+  float* Ks = Qs + hd * ATT2_BQ;               // [hd][64]
+  float* Vs = Ks + hd * ATT2_BK;               // [64][hd]
+  float* Ps = Vs + ATT2_BK * hd;               // [64][68]
+  const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  const int row0 = p.seq_start[b], S = p.seq_start[b + 1] - row0;
+  const int r0 = qt * ATT2_BQ;
+  if (r0 >= S) return;
+  const int nq = min(ATT2_BQ, S - r0);
+  const int pos0 = p.seq_pos0[b];
+  const int g = h / (p.H / p.G);
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const A* q = (const A*)p.q;
+  const A* kp = (const A*)p.kpages;
+  const A* vp = (const A*)p.vpages;
+  const int vec_per_row = hd >> 2;
+
+  for (int e = tid; e < ATT2_BQ * vec_per_row; e += 256) {
+    int qi = e % ATT2_BQ, dq = e / ATT2_BQ;
+    float4 v = qi < nq ? ld4(q + (size_t)(row0 + r0 + qi) * p.q_ld + (size_t)h * hd + dq * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    Qs[(dq * 4 + 0) * ATT2_BQ + qi] = v.x; Qs[(dq * 4 + 1) * ATT2_BQ + qi] = v.y;
+    Qs[(dq * 4 + 2) * ATT2_BQ + qi] = v.z; Qs[(dq * 4 + 3) * ATT2_BQ + qi] = v.w;
+  }
+
+  float m[4], l[4], o[4][NG][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int gg = 0; gg < NG; gg++)
+#pragma unroll
+      for (int c = 0; c < 4; c++) o[i][gg][c] = 0.f;
+  }
+  const int k_hi = pos0 + r0 + nq;
+  int k_lo = p.window > 0 ? max(0, pos0 + r0 - p.window + 1) : 0;
+  k_lo = (k_lo / ATT2_BK) * ATT2_BK;
+  const int* bt = p.block_table + (size_t)b * p.max_pages;
+
+  for (int kt = k_lo; kt < k_hi; kt += ATT2_BK) {
+    const int page = bt[kt / SLLM_PAGE];               // a tile is one page (both are 64 keys)
+    const size_t base = ((size_t)max(page, 0) * p.G + g) * SLLM_PAGE * hd;
+    __syncthreads();
+    for (int e = tid; e < ATT2_BK * vec_per_row; e += 256) {
+      int kk = e % ATT2_BK, dq = e / ATT2_BK;
+      bool ok = page >= 0 && kt + kk < k_hi;
+      float4 v = ok ? ld4(kp + base + (size_t)kk * hd + dq * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      Ks[(dq * 4 + 0) * ATT2_BK + kk] = v.x; Ks[(dq * 4 + 1) * ATT2_BK + kk] = v.y;
+      Ks[(dq * 4 + 2) * ATT2_BK + kk] = v.z; Ks[(dq * 4 + 3) * ATT2_BK + kk] = v.w;
+    }
+    for (int e = tid; e < ATT2_BK * vec_per_row; e += 256) {
+      int kk = e / vec_per_row, dq = e % vec_per_row;
+      bool ok = page >= 0 && kt + kk < k_hi;
+      float4 v = ok ? ld4(vp + base + (size_t)kk * hd + dq * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      *(float4*)(Vs + kk * hd + dq * 4) = v;
+    }
+    __syncthreads();
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) s[i][j] = 0.f;
+#pragma unroll 4
+    for (int dd = 0; dd < hd; dd++) {
+      float4 qa = *(const float4*)(Qs + dd * ATT2_BQ + ty * 4);
+      float4 kb = *(const float4*)(Ks + dd * ATT2_BK + tx * 4);
+      const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, kv[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) s[i][j] = fmaf(qv[i], kv[j], s[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int qi = ty * 4 + i, qpos = pos0 + r0 + qi;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        int kpos = kt + tx * 4 + j;
+        bool seen = page >= 0 && qi < nq && kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+        s[i][j] = seen ? s[i][j] * p.scale : -INFINITY;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int off = 1; off < 16; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      float m_new = fmaxf(m[i], mx);
+      float corr = (m_new == -INFINITY) ? 1.f : expf(m[i] - m_new);     // exp(-inf) = 0 on the first tile seen
+      float pr[4], rs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        pr[j] = (s[i][j] == -INFINITY) ? 0.f : expf(s[i][j] - m_new);
+        rs += pr[j];
+      }
+      l[i] = l[i] * corr + rs;                                          // this lane's share of the row sum
+      m[i] = m_new;
+#pragma unroll
+      for (int gg = 0; gg < NG; gg++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) o[i][gg][c] *= corr;
+      *(float4*)(Ps + qi * ATT2_PS + tx * 4) = make_float4(pr[0], pr[1], pr[2], pr[3]);
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int k4 = 0; k4 < ATT2_BK; k4 += 4) {
+      float pv[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        float4 t = *(const float4*)(Ps + (ty * 4 + i) * ATT2_PS + k4);
+        pv[i][0] = t.x; pv[i][1] = t.y; pv[i][2] = t.z; pv[i][3] = t.w;
+      }
+#pragma unroll
+      for (int gg = 0; gg < NG; gg++) {
+        const int d0 = (tx + 16 * gg) * 4;
+        if (d0 >= hd) continue;
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {
+          float4 vv = *(const float4*)(Vs + (k4 + kk) * hd + d0);
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            o[i][gg][0] = fmaf(pv[i][kk], vv.x, o[i][gg][0]);
+            o[i][gg][1] = fmaf(pv[i][kk], vv.y, o[i][gg][1]);
+            o[i][gg][2] = fmaf(pv[i][kk], vv.z, o[i][gg][2]);
+            o[i][gg][3] = fmaf(pv[i][kk], vv.w, o[i][gg][3]);
+          }
+        }
+      }
+    }
+  }
+  A* out = (A*)p.out;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int qi = ty * 4 + i;
+    float ls = l[i];
+#pragma unroll
+    for (int off = 1; off < 16; off <<= 1) ls += __shfl_xor_sync(0xffffffffu, ls, off);
+    if (qi >= nq) continue;
+    const float inv = ls > 0.f ? 1.0f / ls : 0.f;
+#pragma unroll
+    for (int gg = 0; gg < NG; gg++) {
+      const int d0 = (tx + 16 * gg) * 4;
+      if (d0 >= hd) continue;
+      st4(out + (size_t)(row0 + r0 + qi) * ((size_t)p.H * hd) + (size_t)h * hd + d0,
+          make_float4(o[i][gg][0] * inv, o[i][gg][1] * inv, o[i][gg][2] * inv, o[i][gg][3] * inv));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ one query per sequence, keys split over blocks
+// The decode step of the generic path: block (split, head, sequence) streams its share of the
+// sequence's pages once, LPK lanes per key with 4 dims each per pass (NV passes for wide heads),
+// online softmax per lane group in float (exponentials as 2^x of scores scaled by log2 e), folded
+// over the warp and the block. With one split the block writes the output row; otherwise it leaves
+// (unnormalised sum, maximum, sum) in `part` [B][H][n_split][hd + 2] for the merge kernel below.
+struct AttnSplitArgs {
+  const void* q;        // [B, q_ld] rotated queries of this step
+  int q_ld;
+  void* out;            // [B, H*hd]
+  const int* seq_pos0;  // [B] position of the query: the cache holds keys 0..pos
+  const int* block_table;
+  int max_pages;
+  const void* kpages;
+  const void* vpages;
+  float* part;
+  int H, G, hd, window, n_split;
+  float scale;
+};
+#define ATT_LOG2E 1.4426950408889634f
+
+template <typename A, int LPK, int NV>
+__global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSplitArgs p) {
+  constexpr int KPW = 32 / LPK;                 // keys a warp reads per load
+  constexpr int UN = NV == 1 ? 4 : (NV == 2 ? 2 : 1);   // loads in flight per lane group
+  extern __shared__ __align__(16) float ad_sm[];        // [4][hd] partial outputs, then [4][2] (m, l)
+  const int hd = p.hd;
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (p.H / p.G);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = lane / LPK, dl = (lane % LPK) * 4;
+  const int pos = p.seq_pos0[b];
+  const int k_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int pb = k_begin / SLLM_PAGE, pe = pos / SLLM_PAGE;
+  const int pps = (pe - pb + p.n_split) / p.n_split;
+  const int p0 = pb + split * pps, p1 = min(pe + 1, p0 + pps);
+  const int k_lo = max(k_begin, p0 * SLLM_PAGE), k_hi = min(pos + 1, p1 * SLLM_PAGE);
+  const int* bt = p.block_table + (size_t)b * p.max_pages;
+  const A* kp = (const A*)p.kpages;
+  const A* vp = (const A*)p.vpages;
+  const A* qrow = (const A*)p.q + (size_t)b * p.q_ld + (size_t)h * hd;
+
+  float qv[NV][4], acc[NV][4], m = -INFINITY, l = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    int d = dl + v * LPK * 4;
+    float4 t = d < hd ? ld4(qrow + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float sc = p.scale * ATT_LOG2E;
+    qv[v][0] = t.x * sc; qv[v][1] = t.y * sc; qv[v][2] = t.z * sc; qv[v][3] = t.w * sc;
+    acc[v][0] = acc[v][1] = acc[v][2] = acc[v][3] = 0.f;
+  }
+  for (int kb = k_lo + warp * KPW * UN; kb < k_hi; kb += 4 * KPW * UN) {
+    float4 kr[UN][NV], vr[UN][NV];
+    bool ok[UN];
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+      int key = kb + u * KPW + slot;
+      ok[u] = key < k_hi;
+      int kk = ok[u] ? key : k_lo;
+      int page = bt[kk / SLLM_PAGE];
+      size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * hd;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        int d = dl + v * LPK * 4;
+        kr[u][v] = d < hd ? ld4(kp + off + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        vr[u][v] = d < hd ? ld4(vp + off + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    float s[UN], m_new = m;
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+      float d = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        d = fmaf(qv[v][0], kr[u][v].x, d); d = fmaf(qv[v][1], kr[u][v].y, d);
+        d = fmaf(qv[v][2], kr[u][v].z, d); d = fmaf(qv[v][3], kr[u][v].w, d);
+      }
+#pragma unroll
+      for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      s[u] = ok[u] ? d : -INFINITY;
+      m_new = fmaxf(m_new, s[u]);
+    }
+    if (m_new == -INFINITY) continue;
+    float corr = exp2f(m - m_new);
+    m = m_new;
+    l *= corr;
+#pragma unroll
+    for (int v = 0; v < NV; v++) { acc[v][0] *= corr; acc[v][1] *= corr; acc[v][2] *= corr; acc[v][3] *= corr; }
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+      float pr = exp2f(s[u] - m_new);
+      l += pr;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        acc[v][0] = fmaf(pr, vr[u][v].x, acc[v][0]); acc[v][1] = fmaf(pr, vr[u][v].y, acc[v][1]);
+        acc[v][2] = fmaf(pr, vr[u][v].z, acc[v][2]); acc[v][3] = fmaf(pr, vr[u][v].w, acc[v][3]);
+      }
+    }
+  }
+  // fold the key slots of the warp, then the warps
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+    float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
+    float mn = fmaxf(m, mo);
+    float c1 = mn == -INFINITY ? 0.f : exp2f(m - mn), c2 = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+    l = l * c1 + lo * c2;
+    m = mn;
+#pragma unroll
+    for (int v = 0; v < NV; v++)
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        float ao = __shfl_xor_sync(0xffffffffu, acc[v][c], o);
+        acc[v][c] = acc[v][c] * c1 + ao * c2;
+      }
+  }
+  float* sm_acc = ad_sm;                // [4][hd]
+  float* sm_ml = ad_sm + 4 * hd;        // [4][2]
+  if (lane < LPK) {
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      int d = dl + v * LPK * 4;
+      if (d < hd) *(float4*)(sm_acc + warp * hd + d) = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+    }
+    if (lane == 0) { sm_ml[warp * 2] = m; sm_ml[warp * 2 + 1] = l; }
+  }
+  __syncthreads();
+  float mn = fmaxf(fmaxf(sm_ml[0], sm_ml[2]), fmaxf(sm_ml[4], sm_ml[6]));
+  float cw[4], ls = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    cw[w] = mn == -INFINITY ? 0.f : exp2f(sm_ml[2 * w] - mn);
+    ls += sm_ml[2 * w + 1] * cw[w];
+  }
+  float* dst = p.part + (((size_t)b * p.H + h) * p.n_split + split) * (hd + 2);
+  A* orow = (A*)p.out + ((size_t)b * p.H + h) * hd;
+  for (int dd = threadIdx.x; dd < hd; dd += 128) {
+    float a = sm_acc[dd] * cw[0] + sm_acc[hd + dd] * cw[1] + sm_acc[2 * hd + dd] * cw[2] + sm_acc[3 * hd + dd] * cw[3];
+    if (p.n_split == 1) orow[dd] = from_f32<A>(ls > 0.f ? a / ls : 0.f);
+    else dst[dd] = a;
+  }
+  if (p.n_split > 1 && threadIdx.x == 0) { dst[hd] = mn; dst[hd + 1] = ls; }
+}
+
+// out[b, h*hd + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits added in order
+template <typename A>
+__global__ void attn_split_merge_kernel(const float* __restrict__ part, A* __restrict__ out, int H, int hd, int n_split) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* src = part + ((size_t)b * H + h) * n_split * (hd + 2);
+  float mn = -INFINITY;
+  for (int s2 = 0; s2 < n_split; s2++) mn = fmaxf(mn, src[(size_t)s2 * (hd + 2) + hd]);
+  for (int dd = threadIdx.x; dd < hd; dd += blockDim.x) {
+    float a = 0.f, ls = 0.f;
+    for (int s2 = 0; s2 < n_split; s2++) {
+      const float* ps = src + (size_t)s2 * (hd + 2);
+      float c = (mn == -INFINITY || ps[hd] == -INFINITY) ? 0.f : exp2f(ps[hd] - mn);
+      a += ps[dd] * c;
+      ls += ps[hd + 1] * c;
+    }
+    out[((size_t)b * H + h) * hd + dd] = from_f32<A>(ls > 0.f ? a / ls : 0.f);
   }
 }
 

@@ -12,6 +12,7 @@
 // first. The uniform draw comes from Philox4x32-10 keyed by the sequence's seed with the
 // sequence's draw index as the counter, so a sequence samples the same tokens alone or in a batch.
 #include "common.cuh"
+#include "philox.cuh"
 
 #define SAMPLE_THREADS 1024
 
@@ -24,17 +25,8 @@ struct SampleParams {
 };
 
 __device__ __forceinline__ double philox_uniform(unsigned seed_lo, unsigned seed_hi, unsigned c0, unsigned c1) {
-  const unsigned M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
-  unsigned c[4] = {c0, c1, 0u, 0u}, k0 = seed_lo, k1 = seed_hi;
-#pragma unroll
-  for (int r = 0; r < 10; r++) {
-    unsigned hi0 = __umulhi(M0, c[0]), lo0 = M0 * c[0];
-    unsigned hi1 = __umulhi(M1, c[2]), lo1 = M1 * c[2];
-    unsigned n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
-    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
-    k0 += W0; k1 += W1;
-  }
-  unsigned long long bits = (((unsigned long long)c[0] << 32) | c[1]) >> 11;
+  Philox4 r = philox4x32_10(c0, c1, 0u, 0u, seed_lo, seed_hi);
+  unsigned long long bits = (((unsigned long long)r.w[0] << 32) | r.w[1]) >> 11;
   return (double)bits * (1.0 / 9007199254740992.0);
 }
 

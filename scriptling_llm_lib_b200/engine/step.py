@@ -15,15 +15,23 @@ import numpy as np
 import torch
 
 from ..cache import PAGE, SequenceCache, pages_for
-from ..config.registry import load_config
+from ..config.registry import architecture_for, load_config
 from ..csrc.bindings import CastKernels, KernelSet
-from ..weights.loader import load_weights
+from ..weights.loader import load_weights, stored_to_kept
 from .graphs import DecodeGraphs
 from .layout import ModelLayout
 from .model import DecoderModel
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _draw_one(ts, spec, index, device):
+    from ..weights.random_init import draw_device
+    if device.type != "cuda":
+        raise StepError(f"the engine runs on a CUDA device, not on {device}")
+    with torch.cuda.device(device):
+        return draw_device(ts, spec.seed, index, spec.dtype, device)
 
 
 class StepError(ValueError):
@@ -126,6 +134,10 @@ class Engine:
                                    self.device)
         self.max_positions = min(self.layout.max_positions, n_pages * PAGE)
         self.model.prepare(self.max_positions, self.device)
+        padded = 1
+        while padded < n_slots:
+            padded <<= 1
+        self.tickets(padded * max([g.need.kv_heads for g in self.cache.groups] or [1]))
 
     def bytes_per_page(self) -> int:
         """Device bytes one page of PAGE tokens costs over all cache units."""
@@ -137,11 +149,32 @@ class Engine:
     @classmethod
     def from_folder(cls, model_dir, dtype="bfloat16", max_tokens: int = 4096, max_seqs: int | None = None,
                     device="cuda:0", use_graphs: bool = True) -> "Engine":
+        """`model_dir`: a folder with config.json and model.safetensors, or a model that exists only as
+        a configuration and a seed, `random:<config.json>[:seed[:bfloat16|float32]]`: its weights are
+        drawn on the device and equal those of the folder that random-weights mode writes for the
+        same configuration, seed and storage precision."""
         from .. import models  # noqa: F401  (registers the architectures)
-        arch, cfg = load_config(model_dir)
-        layout = arch.layout(cfg)
-        specs = DecoderModel(layout).tensor_specs()
-        tensors = load_weights(model_dir, specs, torch.device(device), DTYPES[dtype], ignore=layout.ignorable_tensors)
+        from ..weights.random_init import is_random_spec, parse_random_spec
+        dev = torch.device(device)
+        if is_random_spec(model_dir):
+            import json
+            spec = parse_random_spec(model_dir)
+            with open(spec.config_path) as f:
+                raw = json.load(f)
+            archs = raw.get("architectures") or [None]
+            arch = architecture_for(archs[0])
+            cfg = arch.config_class.from_dict(raw, spec.config_path)
+            layout = arch.layout(cfg)
+            specs = DecoderModel(layout).tensor_specs()
+            tensors = {}
+            for i, ts in enumerate(specs):          # one at a time: the stored form of a tensor is dropped once widened
+                t = _draw_one(ts, spec, i, dev)
+                tensors[ts.name] = stored_to_kept(t, DTYPES[dtype]).contiguous()
+        else:
+            arch, cfg = load_config(model_dir)
+            layout = arch.layout(cfg)
+            specs = DecoderModel(layout).tensor_specs()
+            tensors = load_weights(model_dir, specs, dev, DTYPES[dtype], ignore=layout.ignorable_tensors)
         eng = cls(layout, tensors, dtype, max_tokens, max_seqs, device, use_graphs)
         eng.config = cfg
         return eng
@@ -164,8 +197,16 @@ class Engine:
 
     def tickets(self, n: int) -> torch.Tensor:
         """Zeroed int32 counters that kernels of one stream draw tickets from and leave zero (which
-        of several blocks finishes last). One buffer for the engine: its kernels run one after another."""
+        of several blocks finishes last). One buffer for the engine: its kernels run one after another.
+        It is sized when the cache is (slots padded to a power of two x the most key/value heads of any
+        cache unit), because captured decode steps hold its address: should a caller ever need more,
+        the captured steps are dropped before the buffer is replaced, and are captured again on use."""
         if self._tickets is None or self._tickets.numel() < n:
+            if torch.cuda.is_current_stream_capturing():
+                raise StepError(f"a part asked for {n} ticket counters while a decode step was being captured; the "
+                                f"engine holds {0 if self._tickets is None else self._tickets.numel()} (ask for more "
+                                "in the part's prepare())")
+            self.decode_graphs.clear()
             self._tickets = torch.zeros(max(4096, 2 * n), dtype=torch.int32, device=self.device)
         return self._tickets
 

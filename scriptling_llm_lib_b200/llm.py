@@ -26,8 +26,8 @@ _run_locks: dict[int, threading.Lock] = {}      # one generation at a time per e
 
 
 def load(model_dir, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096, max_seqs: int | None = None):
-    """The cached (engine, sampler) of a model folder."""
-    key = (os.path.realpath(str(model_dir)), str(DTYPES[dtype]), str(device))
+    """The cached (engine, sampler) of a model folder, or of `random:<config.json>[:seed[:dtype]]`."""
+    key = (_model_key(model_dir), str(DTYPES[dtype]), str(device))
     with _models_lock:
         if key not in _models:
             eng = Engine.from_folder(model_dir, dtype, max_tokens, max_seqs, device)
@@ -35,10 +35,15 @@ def load(model_dir, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096, m
         return _models[key]
 
 
+def _model_key(model_dir) -> str:
+    from .weights.random_init import is_random_spec
+    return str(model_dir) if is_random_spec(model_dir) else os.path.realpath(str(model_dir))
+
+
 def unload(model_dir=None) -> None:
     """Drop one cached model, or all of them."""
     with _models_lock:
-        for key in [k for k in _models if model_dir is None or k[0] == os.path.realpath(str(model_dir))]:
+        for key in [k for k in _models if model_dir is None or k[0] == _model_key(model_dir)]:
             _run_locks.pop(id(_models[key][0]), None)
             del _models[key]
 

@@ -51,11 +51,14 @@ class Linear:
                 out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
                 ctx.kernels.decode.gemm_small_m(x, w, out)
                 return out
-            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
             if x.dtype == torch.bfloat16 and ctx.kernels.tensor_core.takes(x, w):
+                out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
                 ctx.kernels.tensor_core.gemm(x, w, out, ctx.err_flag)
-            else:
-                ctx.kernels.gemm_nt(x, w, out)
+                return out
+            split = ctx.kernels.gemm_nt_split(x.shape[0], w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
+            shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
+            out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
+            ctx.kernels.gemm_nt(x, w, out)
             return out
         if w.dtype == torch.float32 and x.dtype == torch.bfloat16:
             # a matrix kept in 32-bit inside a bfloat16 model: widen the rows, multiply in 32-bit

@@ -8,10 +8,9 @@ from dataclasses import dataclass
 class TensorSpec:
     """One named tensor: its shape, and how random-weights mode draws it.
 
-    init: "matrix" (normal, std 0.02), "norm_weight" (1 + normal*0.02), "integer_table".
-    optional: the file may leave it out (the loader then gives None); alias_of names the tensor
-    used in its place (a tied output head reads the embedding, as the reference falls back to the
-    embedding when output.weight is absent, model_f32.go:147-162).
+    init: the name of the law random-weights mode draws it by (weights.random_init.INIT_LAWS:
+    "matrix" normal with std 0.02, "norm_weight" 1 + that, "integer_table"; parts may register more).
+    optional: the file may leave it out; the part then finds no entry under the name.
     """
     name: str
     shape: tuple[int, ...]

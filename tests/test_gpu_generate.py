@@ -183,3 +183,59 @@ def test_command_line(tmp_path):
     assert "prefill" in run.stderr and "decode" in run.stderr and "t/s" in run.stderr
     bad = subprocess.run([sys.executable, str(ROOT / "bin" / "sllm-b200"), "-prompt", "1,2"], capture_output=True, text=True)
     assert bad.returncode == 1 and "-model is required" in bad.stderr
+
+
+@pytest.mark.parametrize("stored", [torch.bfloat16, torch.float32])
+def test_random_mode_on_the_device_equals_the_written_folder(tmp_path, stored):
+    """The fill kernel and the host statement of the generator give the same bits: every tensor of
+    a model drawn on the device equals the tensor in the folder that random-weights mode writes,
+    in bfloat16 and in 32-bit storage, odd sizes and norm weights included."""
+    from scriptling_llm_lib_b200.engine.model import DecoderModel
+    from scriptling_llm_lib_b200.config.registry import architecture_for
+    from scriptling_llm_lib_b200.weights.random_init import draw_device, draw_host, random_tensors
+    from scriptling_llm_lib_b200.weights.spec import TensorSpec
+    raw, _ = TINY["C"]                                                   # vocabulary 1003, hidden 144: nothing a power of two
+    arch = architecture_for(raw["architectures"][0])
+    specs = DecoderModel(arch.layout(arch.config_class.from_dict(raw, "test"))).tensor_specs()
+    host = random_tensors(specs, 11, stored, "cpu")
+    devt = random_tensors(specs, 11, stored, "cuda:0")
+    for s in specs:
+        assert devt[s.name].dtype == stored and torch.equal(devt[s.name].cpu(), host[s.name]), s.name
+    # a larger matrix (more than one pass of the host's chunks is not needed: 3 million elements), an odd
+    # element count, a seed with a high word, an integer table
+    for spec, seed, index in [(TensorSpec("w", (1501, 2003)), 2 ** 40 + 3, 77), (TensorSpec("w", (7,)), 5, 0),
+                              (TensorSpec("t", (1001,), init="integer_table"), 9, 3)]:
+        a, b = draw_host(spec, seed, index, stored), draw_device(spec, seed, index, stored, "cuda:0").cpu()
+        assert torch.equal(a, b), spec
+
+
+def test_random_model_spec_runs_like_its_folder(tmp_path):
+    """`random:<config.json>:seed` through the entry point, trace replay and the command line gives what
+    the written folder of the same configuration and seed gives."""
+    import json
+    from scriptling_llm_lib_b200 import llm
+    raw, _ = TINY["B"]
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(raw))
+    d = llm.random_model(raw, 21, tmp_path / "folder")
+    prompts = [random_ids(n, raw["vocab_size"], 70 + n) for n in (9, 30)]
+    for dtype in ("float32", "bfloat16"):
+        want = llm.generate(d, prompts, 10, "greedy", stop_ids=[], dtype=dtype)
+        got = llm.generate(f"random:{cfg_path}:21", prompts, 10, "greedy", stop_ids=[], dtype=dtype)
+        assert got == want
+    other = llm.generate(f"random:{cfg_path}:22", prompts, 10, "greedy", stop_ids=[], dtype="float32")
+    assert other != llm.generate(d, prompts, 10, "greedy", stop_ids=[], dtype="float32")
+    # trace replay takes the spec where it takes a folder
+    from helpers import Replay, replay_whole
+    ids = random_ids(40, raw["vocab_size"], 5)
+    outs = []
+    for model in (str(d), f"random:{cfg_path}:21"):
+        rp = Replay(model, "float32", tmp_path / ("out" + str(len(outs))), 64, raw["vocab_size"])
+        outs.append(replay_whole(rp, "a", ids))
+        assert rp.close() == 0
+    assert (outs[0] == outs[1]).all()
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "sllm-b200"), "-model", f"random:{cfg_path}:21", "-prompt",
+                        " ".join(map(str, prompts[0])), "-tokens", "10", "-stop", "", "-dtype", "float32"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.split()] == llm.generate(d, prompts[0], 10, "greedy", stop_ids=[], dtype="float32")

@@ -87,17 +87,41 @@ def test_add_rmsnorm(kernel_sets, dtype, d, eps, w32):
 
 # --------------------------------------------------------------------------- matrix products
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M, N, K", [(1, 33, 19), (3, 100, 72), (8, 64, 1000), (9, 130, 65), (70, 257, 136), (200, 96, 520)])
+@pytest.mark.parametrize("M, N, K", [(1, 33, 19), (3, 100, 72), (8, 64, 1000), (9, 130, 65), (70, 257, 136), (200, 96, 520),
+                                     # K in multiples of 4: the 16-byte kernels (a block per four columns up to 8
+                                     # rows, 64- and 128-row register tiles beyond), ragged edges everywhere
+                                     (1, 35, 20), (2, 1003, 2048), (4, 6, 4100), (7, 515, 264), (9, 130, 64), (64, 300, 2048),
+                                     (65, 129, 136), (300, 515, 264), (130, 1000, 24)])
 def test_gemm_nt_generic(kernel_sets, dtype, M, N, K):
     ks = kernel_sets[dtype]
     a, w = dev(rand(M, K, seed=6), dtype), dev(rand(N, K, seed=7, scale=0.1), dtype)
     want = plain.linear(f64(a), f64(w))
     out = torch.empty(M, N, dtype=dtype, device="cuda")
     ks.gemm_nt(a, w, out)
-    assert rel_err(out.cpu().float(), want) < TOL[dtype]
-    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    # float accumulation, float output: one ascending chain of K fused multiply-adds per output, whose
+    # rounding error grows like sqrt(K) (2e-6 holds up to about a thousand terms)
+    tol32 = 2e-6 * max(1.0, math.sqrt(K / 1024))
+    if dtype == torch.float32:
+        assert rel_err(out.cpu().float(), want) < tol32
+    else:
+        assert rel_err(out.cpu().float(), want) < TOL[dtype]
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
     ks.gemm_nt(a, w, out32)
-    assert rel_err(out32.cpu(), want) < 2e-6                           # float accumulation, float output
+    assert rel_err(out32.cpu(), want) < tol32
+    if K % 4 == 0:
+        for split in (2, 5):                                            # K cut into parts, partial sums for the reader
+            parts = torch.full((split, M, N), float("nan"), dtype=torch.float32, device="cuda")
+            ks.gemm_nt(a, w, parts)
+            assert rel_err(parts.sum(0).cpu(), want) < tol32
+
+
+def test_gemm_nt_generic_split_choice():
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    assert KernelSet.gemm_nt_split(8, 2048, 8192, 148) == 1             # few rows: no cut
+    assert KernelSet.gemm_nt_split(64, 2048, 8192, 148) == 16           # 16 tiles on 148 SMs: cut K
+    assert KernelSet.gemm_nt_split(64, 2048, 2048, 148) == 8
+    assert KernelSet.gemm_nt_split(2048, 8192, 2048, 148) == 1          # enough tiles
+    assert KernelSet.gemm_nt_split(20, 96, 200, 148) == 1               # too shallow to cut
 
 
 @pytest.mark.parametrize("M, N, K", [(1, 64, 64), (3, 100, 72), (8, 176, 64), (9, 1003, 144), (16, 2048, 2048),
@@ -461,21 +485,62 @@ def test_attn_decode_with_rotation_and_cache_write_fused(kernel_sets, H, G, hd, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, G, hd, window", [(4, 2, 16, None), (3, 1, 32, 40), (6, 3, 48, None), (32, 32, 64, None),
+                                              (2, 2, 80, 100), (8, 2, 128, 300), (2, 1, 256, None), (2, 2, 320, 65)])
+@pytest.mark.parametrize("n_split", [1, 3, 16])
+def test_attn_decode_split_generic(kernel_sets, dtype, H, G, hd, window, n_split):
+    """The decode attention of the generic path (all of the 32-bit decode step): head widths in
+    steps of 4 elements up to 512, any grouping, windows, one or many splits (also more splits than
+    a short sequence has pages)."""
+    ks = kernel_sets[dtype]
+    pos0 = [0, 63, 64, 700, 257]
+    B = len(pos0)
+    qs, kk, vv = attention_case(H, G, hd, [1] * B, pos0, 44)
+    rnd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.bfloat16().float())
+    qs, kk, vv = [rnd(t) for t in qs], [rnd(t) for t in kk], [rnd(t) for t in vv]
+    kp, vp, bt = paged(kk, vv, [p + 1 for p in pos0], dtype=dtype)
+    q = dev(torch.cat([t.reshape(1, -1) for t in qs]), dtype)
+    assert ks.attn_decode_split_takes(hd, q.stride(0))
+    out = torch.full((B, H * hd), float("nan"), dtype=dtype, device="cuda")
+    part = torch.full((B * H * n_split * (hd + 2),), float("nan"), dtype=torch.float32, device="cuda") if n_split > 1 else None
+    ks.attn_decode_split(q, out, dev(pos0, torch.int32), bt, kp, vp, part, B, H, G, hd, window, 1.0 / math.sqrt(hd), n_split)
+    want = torch.cat([plain.attention(f64(qs[b]), f64(kk[b]), f64(vv[b]), torch.tensor([pos0[b]]),
+                                      torch.arange(pos0[b] + 1), window).reshape(1, -1) for b in range(B)])
+    assert rel_err(out.cpu().float(), want) < TOL[dtype]
+
+
+FAR_CASES = [(3, None, True), (517, None, True), (899 - 199, 200, True), (899 - 200, 200, False),
+             (640, 260, True), (639, 260, False)]     # the last two: the window's edge (key 640) on a page and tile boundary
+
+
+def far_key_case(H, G, hd, n, far, dtype, n_new=1):
+    """`n` keys; the queries at the last `n_new` positions all point at key `far`, whose score towers
+    over the others: the output must be that key's value if and only if the key is seen."""
+    k = rand(n, G, hd, seed=60, scale=0.1)
+    v = rand(n, G, hd, seed=61)
+    q = rand(n_new, H, hd, seed=62, scale=0.1)
+    nrep = H // G
+    for g in range(G):
+        k[far, g] = q[-1, g * nrep] * (2260.0 / math.sqrt(hd))          # score about 22 above the others
+    for h in range(H):
+        q[:, h] = q[-1, (h // nrep) * nrep]                              # every head of a group, every row: the same query
+    rnd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.bfloat16().float())
+    return rnd(q), rnd(k), rnd(v)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key_and_respects_the_windows_edge(kernel_sets, dtype):
     """Random keys would hide a key read from the wrong place: one key among 900 gets a score far
     above the rest, so the output must be that key's value; with a window, the key at distance
-    window-1 is seen and the key at distance window is not."""
+    window-1 is seen and the key at distance window is not. Through the generic kernels of both
+    element types: the one-query form, the register-tiled form (several new rows on a non-empty
+    cache) and the split-key decode form."""
     ks = kernel_sets[dtype]
     H = G = 2
     hd, n = 32, 900
     scale = 1.0 / math.sqrt(hd)
-    for far, window, seen in [(3, None, True), (517, None, True), (n - 1 - 199, 200, True), (n - 1 - 200, 200, False)]:
-        k = rand(n, G, hd, seed=60, scale=0.1)
-        v = rand(n, G, hd, seed=61)
-        q = rand(1, H, hd, seed=62, scale=0.1)
-        k[far] = q[0] * 400.0                                            # score of `far` towers over the others
-        rnd = (lambda t: t) if dtype == torch.float32 else (lambda t: t.bfloat16().float())
-        q, k, v = rnd(q), rnd(k), rnd(v)
+    for far, window, seen in FAR_CASES:
+        q, k, v = far_key_case(H, G, hd, n, far, dtype)
         kp, vp, bt = paged([k], [v], [n], dtype=dtype, seed=far)
         out = torch.empty(1, H * hd, dtype=dtype, device="cuda")
         qd = dev(q.reshape(1, -1), dtype)
@@ -484,12 +549,80 @@ def test_attention_finds_one_far_key_and_respects_the_windows_edge(kernel_sets, 
         assert rel_err(out.cpu().float(), want) < TOL[dtype]
         hit = rel_err(out.cpu().float(), f64(v[far]).reshape(1, -1)) < 1e-2
         assert hit == seen
+        for n_split in (1, 5):
+            part = torch.empty(H * n_split * (hd + 2), dtype=torch.float32, device="cuda")
+            out.fill_(float("nan"))
+            ks.attn_decode_split(qd, out, dev([n - 1], torch.int32), bt, kp, vp, part, 1, H, G, hd, window, scale, n_split)
+            assert rel_err(out.cpu().float(), want) < TOL[dtype]
+            assert (rel_err(out.cpu().float(), f64(v[far]).reshape(1, -1)) < 1e-2) == seen
         if dtype == torch.bfloat16:
             for n_split in (1, 5):
                 scratch = torch.empty(H * n_split * (hd + 2), dtype=torch.float32, device="cuda")
                 ks.decode.attn_decode(qd, out, dev([n - 1], torch.int32), bt, kp, vp, scratch, 1, H, G, hd, window, scale, n_split)
                 assert rel_err(out.cpu().float(), want) < TOL[dtype]
                 assert (rel_err(out.cpu().float(), f64(v[far]).reshape(1, -1)) < 1e-2) == seen
+        # the register-tiled form: the last 7 rows are new, the far key lies in an earlier page of the cache
+        n_new = 7
+        q7, k7, v7 = far_key_case(H, G, hd, n, far, dtype, n_new)
+        out7 = torch.empty(n_new, H * hd, dtype=dtype, device="cuda")
+        ks.attn_paged(dev(q7.reshape(n_new, -1), dtype), out7, dev([0, n_new], torch.int32), dev([n - n_new], torch.int32), bt,
+                      kp, vp, 1, n_new, H, G, hd, window, scale)
+        want7 = plain.attention(f64(q7), f64(k7), f64(v7), torch.arange(n - n_new, n), torch.arange(n), window).reshape(n_new, -1)
+        assert rel_err(out7.cpu().float(), want7) < TOL[dtype]
+        assert (rel_err(out7[-1:].cpu().float(), f64(v[far]).reshape(1, -1)) < 1e-2) == seen
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("H, G", [(4, 2), (24, 2), (3, 3)])
+def test_fast_bfloat16_attention_finds_one_far_key_and_respects_the_windows_edge(kernel_sets, hd, H, G):
+    """The same through the kernels that generation uses at real head widths: the tcgen05 prompt
+    attention with new rows on a non-empty cache (the far key in an earlier page, the window's edge
+    inside a 64-key tile and on a tile boundary), the decode attention on mma.sync with grouped
+    queries (4 and 24 heads on 2 key/value heads: its lower rows only, and its upper rows too) and
+    its one-head form, with one and five splits, and the decode form that rotates and writes the
+    cache itself (identity rotation: position table of angle 0)."""
+    ks = kernel_sets[torch.bfloat16]
+    n = 900
+    scale = 1.0 / math.sqrt(hd)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ident = torch.zeros(n, hd // 2, 2, dtype=torch.float32, device="cuda")
+    ident[..., 0] = 1.0                                                  # cos 1, sin 0 at every position
+    for far, window, seen in FAR_CASES:
+        q, k, v = far_key_case(H, G, hd, n, far, torch.bfloat16)
+        kp, vp, bt = paged([k], [v], [n], dtype=torch.bfloat16, seed=far)
+        qd = dev(q.reshape(1, -1), torch.bfloat16)
+        want = plain.attention(f64(q), f64(k), f64(v), torch.tensor([n - 1]), torch.arange(n), window).reshape(1, -1)
+        vfar = torch.cat([f64(v[far, h // (H // G)]) for h in range(H)]).reshape(1, -1)
+        tickets = torch.zeros(G, dtype=torch.int32, device="cuda")
+        for n_split in (1, 5):
+            scratch = torch.empty(H * n_split * (hd + 2), dtype=torch.float32, device="cuda")
+            out = torch.full((1, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ks.decode.attn_decode(qd, out, dev([n - 1], torch.int32), bt, kp, vp, scratch, 1, H, G, hd, window, scale, n_split,
+                                  tickets=tickets)
+            assert rel_err(out.cpu().float(), want) < 1.2e-2
+            assert (rel_err(out.cpu().float(), vfar) < 1e-2) == seen
+            # rotation and cache write fused: raw row [q | k | v] of the last position, the cache holds the rest
+            raw = torch.cat([q.reshape(1, -1), k[n - 1].reshape(1, -1), v[n - 1].reshape(1, -1)], dim=1)
+            kp2, vp2 = kp.clone(), vp.clone()
+            pg = int(bt[0, (n - 1) // PAGE])
+            kp2[pg, :, (n - 1) % PAGE] = float("nan")
+            vp2[pg, :, (n - 1) % PAGE] = float("nan")
+            out.fill_(float("nan"))
+            ks.decode.attn_decode_rope(dev(raw, torch.bfloat16), out, dev([n - 1], torch.int32), bt, kp2, vp2, scratch, tickets,
+                                       ident, hd, False, True, 1, H, G, hd, window, scale, n_split)
+            assert rel_err(out.cpu().float(), want) < 1.2e-2
+            assert (rel_err(out.cpu().float(), vfar) < 1e-2) == seen
+            assert torch.equal(kp2[pg, :, (n - 1) % PAGE], kp[pg, :, (n - 1) % PAGE])
+        # prompt attention: 70 new rows on 830 cached keys; the last row's far key lies pages back
+        n_new = 70
+        q7, k7, v7 = far_key_case(H, G, hd, n, far, torch.bfloat16, n_new)
+        out7 = torch.full((n_new, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ks.prefill_attention_tc.attn(dev(q7.reshape(n_new, -1), torch.bfloat16), out7, dev([0, n_new], torch.int32),
+                                     dev([n - n_new], torch.int32), bt, kp, vp, 1, n_new, H, G, hd, window, scale, err)
+        want7 = plain.attention(f64(q7), f64(k7), f64(v7), torch.arange(n - n_new, n), torch.arange(n), window).reshape(n_new, -1)
+        assert int(err) == 0
+        assert rel_err(out7.cpu().float(), want7) < 1.2e-2
+        assert (rel_err(out7[-1:].cpu().float(), vfar) < 1e-2) == seen
 
 
 # --------------------------------------------------------------------------- sampling

@@ -11,6 +11,7 @@ from scriptling_llm_lib_b200 import models  # noqa: F401
 from scriptling_llm_lib_b200.config import LlamaConfig
 from scriptling_llm_lib_b200.engine.model import DecoderModel
 from scriptling_llm_lib_b200.models.llama import llama_layout
+from scriptling_llm_lib_b200.weights.spec import TensorSpec
 from scriptling_llm_lib_b200.weights import (SafetensorsError, SafetensorsFile, WeightError, load_weights,
                                               write_safetensors)
 
@@ -181,3 +182,58 @@ def test_random_model_through_the_python_entry_point(tmp_path):
     assert llm.random_model(TINY_A, 6, tmp_path / "r3").joinpath("model.safetensors").read_bytes() != (d1 / "model.safetensors").read_bytes()
     with pytest.raises(ConfigError, match="not registered"):
         llm.random_model(dict(TINY_A, architectures=["NoSuchModel"]), 0, tmp_path / "r4")
+
+
+def test_random_generator_is_the_stated_one():
+    """The host statement of random-weights mode: Philox4x32-10 keyed by (seed, tensor number),
+    a counter per four elements, Box-Muller with series for the logarithm and the sine/cosine whose
+    values agree with the library functions to a few units in the last place of a double."""
+    import numpy as np
+    from scriptling_llm_lib_b200.weights import random_init as ri
+    # the block function against the scalar statement beside the plain implementation
+    c = [7, 1, 0x89ABCDEF, 0]
+    w = ri.philox4x32_10(np.array([c[0]]), np.array([c[1]]), np.array([c[2]]), np.array([c[3]]), 0x12345678, 42)
+    assert [int(x[0]) for x in w] == plain.philox4x32(c, [0x12345678, 42])
+    # the normal pair against numpy's own functions
+    a = np.array([0, 1, 2 ** 31, 2 ** 32 - 1, 12345678, 3000000000], dtype=np.uint64)
+    b = np.array([0, 2 ** 30, 2 ** 31 + 5, 2 ** 32 - 1, 987654321, 2 ** 29 + 1], dtype=np.uint64)
+    z0, z1 = ri._normal_pair(a, b)
+    u1, u2 = (a.astype(np.float64) + 0.5) / 2 ** 32, b.astype(np.float64) / 2 ** 32
+    r = np.sqrt(-2 * np.log(u1))
+    assert np.abs(z0 - r * np.cos(2 * np.pi * u2)).max() < 1e-14 and np.abs(z1 - r * np.sin(2 * np.pi * u2)).max() < 1e-14
+    # a tensor's values depend on (seed, number, element) only: a longer tensor starts with the shorter one
+    short = ri.draw_host(TensorSpec("t", (10, 7)), 3, 5, torch.float32)
+    longer = ri.draw_host(TensorSpec("t", (30, 7)), 3, 5, torch.float32)
+    assert torch.equal(short, longer[:10])
+    assert not torch.equal(short, ri.draw_host(TensorSpec("t", (10, 7)), 3, 6, torch.float32))
+    assert not torch.equal(short, ri.draw_host(TensorSpec("t", (10, 7)), 3 + 2 ** 32, 5, torch.float32))   # the seed's high word counts
+    big = ri.draw_host(TensorSpec("t", (400, 500)), 1, 0, torch.float32).double() / ri.MATRIX_STD
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01 and float(big.abs().max()) < 6.0
+    assert abs(float((big ** 4).mean()) - 3.0) < 0.1                   # a normal's fourth moment
+    ints = ri.draw_host(TensorSpec("t", (1000,), init="integer_table"), 1, 0, torch.float32)
+    assert ints.dtype == torch.int32 and int(ints.min()) >= 0 and int(ints.max()) < 2 ** 15 and len(set(ints.tolist())) > 900
+
+
+def test_init_laws_are_a_registry():
+    from scriptling_llm_lib_b200.weights import random_init as ri
+    with pytest.raises(ValueError, match="unknown init law"):
+        ri.draw_host(TensorSpec("t", (4,), init="no_such_law"), 0, 0, torch.float32)
+    ri.register_init("test_wide", ri.Normal(5.0, 2.0), replace=True)
+    t = ri.draw_host(TensorSpec("t", (5000,), init="test_wide"), 0, 0, torch.float32)
+    assert abs(float(t.mean()) - 5.0) < 0.1 and abs(float(t.std()) - 2.0) < 0.1
+    with pytest.raises(ValueError, match="already registered"):
+        ri.register_init("matrix", ri.Normal(0.0, 1.0))
+    plain_norm = ri.draw_host(TensorSpec("n", (5000,), init="norm_weight"), 0, 0, torch.float32, norm_init="plain")
+    assert abs(float(plain_norm.mean())) < 0.01
+
+
+def test_random_model_spec_is_parsed():
+    from scriptling_llm_lib_b200.weights.random_init import RandomSpec, is_random_spec, parse_random_spec
+    assert parse_random_spec("random:/a/b.json") == RandomSpec("/a/b.json", 0, torch.bfloat16)
+    assert parse_random_spec("random:cfg.json:7") == RandomSpec("cfg.json", 7, torch.bfloat16)
+    assert parse_random_spec("random:c:/x/cfg.json:7:float32") == RandomSpec("c:/x/cfg.json", 7, torch.float32)
+    assert is_random_spec("random:x") and not is_random_spec("/a/random:x") and not is_random_spec(None)
+    with pytest.raises(ValueError):
+        parse_random_spec("random:")
+    with pytest.raises(ValueError):
+        parse_random_spec("/a/folder")
