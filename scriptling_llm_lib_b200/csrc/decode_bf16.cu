@@ -912,8 +912,10 @@ SLLM_EXPORT const char* sllm_attn_decode_noalloc_strerror(int code) {
       return "attn_decode_noalloc: B * H * n_split * (head_dim + 2) floats exceed the built-in scratch "
              "(SLLM_NOALLOC_SCRATCH_FLOATS); use fewer splits or the entry point that takes caller scratch";
     case SLLM_NOALLOC_ERR_DEVICE: return "attn_decode_noalloc: the current device's ordinal is beyond the table of 64 devices";
-    case SLLM_ERR_ARG: return "attn_decode_noalloc: bad arguments (head counts, alignment of q, or n_split < 1)";
-    default: return code > 0 ? "attn_decode_noalloc: CUDA error (see cudaError_t)" : "attn_decode_noalloc: unsupported head width";
+    case SLLM_ERR_ARG:
+      return "attn_decode_noalloc: bad arguments (head counts, a head width other than 16, 32, 64, 128 or 256, "
+             "alignment of q, or n_split < 1)";
+    default: return code > 0 ? "attn_decode_noalloc: CUDA error (see cudaError_t)" : "attn_decode_noalloc: unknown error code";
   }
 }
 

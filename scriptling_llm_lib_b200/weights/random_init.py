@@ -136,23 +136,23 @@ def _host_words(n: int, seed: int, index: int, first_counter: int, n_counters: i
                          seed & 0xFFFFFFFF, index & 0xFFFFFFFF)
 
 
-_HOST_CHUNK = 1 << 20        # counters per pass: bounds the host's working memory
+_HOST_CHUNK = 1 << 15        # counters per pass: the working arrays of a pass stay in the cache
+_HOST_THREADS = max(1, min(16, os.cpu_count() or 1))
 
 
 def draw_host(spec: TensorSpec, seed: int, index: int, dtype: torch.dtype, norm_init: str = "one_plus") -> torch.Tensor:
-    """Tensor `index` of a model drawn on the host (numpy)."""
+    """Tensor `index` of a model drawn on the host (numpy; passes of 32 Ki counters spread over threads)."""
     law = law_for(spec, norm_init)
     n = int(np.prod(spec.shape)) if spec.shape else 1
     n_counters = (n + 3) // 4
-    if isinstance(law, UniformInteger):
-        out = np.empty(n_counters * 4, dtype=np.int32)
-    else:
-        out = np.empty(n_counters * 4, dtype=np.float32)
-    for c0 in range(0, n_counters, _HOST_CHUNK):
+    integer = isinstance(law, UniformInteger)
+    out = np.empty(n_counters * 4, dtype=np.int32 if integer else np.float32)
+
+    def one_pass(c0: int) -> None:
         nc = min(_HOST_CHUNK, n_counters - c0)
         w = _host_words(n, seed, index, c0, nc)
         view = out[c0 * 4:(c0 + nc) * 4].reshape(nc, 4)
-        if isinstance(law, UniformInteger):
+        if integer:
             for j in range(4):
                 view[:, j] = (w[j] % np.uint64(law.modulus)).astype(np.int32)
         else:
@@ -160,10 +160,17 @@ def draw_host(spec: TensorSpec, seed: int, index: int, dtype: torch.dtype, norm_
             z2, z3 = _normal_pair(w[2], w[3])
             for j, z in enumerate((z0, z1, z2, z3)):
                 view[:, j] = (law.mean + law.std * z).astype(np.float32)
+
+    starts = range(0, n_counters, _HOST_CHUNK)
+    if len(starts) > 1 and _HOST_THREADS > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(_HOST_THREADS) as pool:
+            list(pool.map(one_pass, starts))
+    else:
+        for c0 in starts:
+            one_pass(c0)
     t = torch.from_numpy(out[:n].reshape(spec.shape))
-    if isinstance(law, UniformInteger):
-        return t
-    return t.to(dtype)
+    return t if integer else t.to(dtype)
 
 
 def draw_device(spec: TensorSpec, seed: int, index: int, dtype: torch.dtype, device, norm_init: str = "one_plus") -> torch.Tensor:
@@ -194,12 +201,13 @@ def random_tensors(specs: Iterable[TensorSpec], seed: int, dtype: torch.dtype, d
 
 
 def write_random_model(config, specs: Iterable[TensorSpec], seed: int, out_dir, dtype=torch.bfloat16,
-                       norm_init: str = "one_plus") -> Path:
-    """Write `out_dir`/config.json and `out_dir`/model.safetensors; returns out_dir."""
+                       norm_init: str = "one_plus", device="cpu") -> Path:
+    """Write `out_dir`/config.json and `out_dir`/model.safetensors; returns out_dir. `device`: where
+    the values are drawn (a CUDA device is much faster for large models; the file is the same)."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     (out_dir / "config.json").write_text(json.dumps(config.to_json_dict(), indent=1))
-    tensors = random_tensors(specs, seed, dtype, "cpu", norm_init)
+    tensors = {k: v.cpu() for k, v in random_tensors(specs, seed, dtype, device, norm_init).items()}
     write_safetensors(out_dir / WEIGHTS_FILE, tensors, {"format": "pt", "seed": seed})
     return out_dir
 

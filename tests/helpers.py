@@ -57,8 +57,11 @@ TINY_E = {
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
-def make_model_dir(tmp, raw_cfg: dict, seed: int, dtype=torch.bfloat16, norm_init="one_plus") -> Path:
-    """Write a random-weights model folder with the library's own random mode."""
+def make_model_dir(tmp, raw_cfg: dict, seed: int, dtype=torch.bfloat16, norm_init="one_plus", device=None) -> Path:
+    """Write a random-weights model folder with the library's own random mode (values drawn on the
+    GPU where there is one: the same bits as on the host, which its own test shows, and faster)."""
+    if device is None:
+        device = "cuda:0" if torch.cuda.is_available() else "cpu"
     from scriptling_llm_lib_b200 import models  # noqa: F401
     from scriptling_llm_lib_b200.config.registry import architecture_for
     from scriptling_llm_lib_b200.engine.model import DecoderModel
@@ -66,12 +69,37 @@ def make_model_dir(tmp, raw_cfg: dict, seed: int, dtype=torch.bfloat16, norm_ini
     arch = architecture_for(raw_cfg["architectures"][0])
     cfg = arch.config_class.from_dict(raw_cfg, "test config")
     specs = DecoderModel(arch.layout(cfg)).tensor_specs()
-    return write_random_model(cfg, specs, seed, Path(tmp), dtype, norm_init)
+    return write_random_model(cfg, specs, seed, Path(tmp), dtype, norm_init, device)
 
 
 def plain_model(model_dir, act_round=None, schedule=None) -> "plain.PlainLlama":
     cfg, weights = plain.load_folder(model_dir)
     return plain.PlainLlama(cfg, weights, act_round=act_round, schedule=schedule)
+
+
+def plain_model_bf16(model_dir, schedule=None) -> "plain.PlainLlama":
+    """The plain implementation rounding to bfloat16 where the engine's bfloat16 path writes an
+    activation to memory: norm outputs, q, k, v before and after rotation, attention output, the
+    gated activation, o and down outputs; gate and up are not rounded on their own (the gate is
+    applied in the product's epilogue)."""
+    return plain_model(model_dir, act_round=plain.bf16_activations(skip=("gate", "up")), schedule=schedule)
+
+
+def check_logits(got, want, want16, dtype: str, what: str = "") -> None:
+    """32-bit: against the plain implementation within TOL_F32. bfloat16: against the plain
+    implementation with rounded activations within TOL_BF16_ROUNDED and against the unrounded one
+    within TOL_BF16."""
+    if dtype == "float32":
+        e = rel_err(got, want)
+        assert e < TOL_F32, f"{what}: {e:.3g}"
+        return
+    e16, e = rel_err(got, want16), rel_err(got, want)
+    assert e16 < TOL_BF16_ROUNDED, f"{what} against the rounding plain implementation: {e16:.3g}"
+    assert e < TOL_BF16, f"{what}: {e:.3g}"
+    MEASURED.append((what, e16, e))
+
+
+MEASURED: list = []       # (what, error against the rounding oracle, against the unrounded): printed with -s
 
 
 def random_ids(n: int, vocab: int, seed: int) -> list[int]:
@@ -98,6 +126,10 @@ def rel_err(got, want) -> float:
 # stores them (8 mantissa bits: 2^-9 relative per rounding, a few dozen roundings deep)
 TOL_F32 = 1e-4
 TOL_BF16 = 3e-2
+# bfloat16 against the plain implementation that rounds to bfloat16 where the engine stores
+# activations (`plain_model_bf16`): what is left is the order of sums, the probabilities' rounding
+# before P V and the products whose partial sums stay in 32-bit.
+TOL_BF16_ROUNDED = 1.5e-2
 
 
 # --------------------------------------------------------------------------- trace replay client

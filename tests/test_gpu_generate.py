@@ -9,7 +9,8 @@ import pytest
 import torch
 
 import plain_llama as plain
-from helpers import TINY, TOL_BF16, TOL_F32, make_model_dir, plain_model, random_ids, rel_err
+from helpers import (MEASURED, TINY, TOL_BF16, TOL_F32, check_logits, make_model_dir, plain_model, plain_model_bf16, random_ids,
+                     rel_err)
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -95,7 +96,9 @@ def test_sampling_strategies_match_the_plain_samplers_in_32_bit(tmp_path):
             assert got[i] == want, f"{strategy} {kw} request {i}"
         alone = llm.generate(d, [prompts[2]], 10, strategy, seed=11, stop_ids=[], dtype="float32", **kw)
         again = llm.generate(d, prompts[:1] + [prompts[2]], 10, strategy, seed=11, stop_ids=[], dtype="float32", **kw)
-        assert alone[0] != got[2] or True                                # (stream of request index 0 vs 2: may differ)
+        # a request's stream is (seed + its index in the call): alone, prompt 2 is request 0 and draws what
+        # the plain implementation draws for seed 11 + 0
+        assert alone[0] == plain.generate(pm, prompts[2], 10, strategy, stop_ids=(), seed=11, **kw)
         assert again[0] == got[0]                                        # same request index, same seed: same tokens
     a = llm.generate(d, prompts[3], 10, "temperature", temperature=0.8, seed=1, stop_ids=[], dtype="float32")
     b = llm.generate(d, prompts[3], 10, "temperature", temperature=0.8, seed=2, stop_ids=[], dtype="float32")
@@ -110,15 +113,65 @@ def test_long_decoding_and_the_first_tokens(tmp_path, dtype):
     raw = dict(TINY["B"][0], max_position_embeddings=512)
     d = make_model_dir(tmp_path / "m", raw, 1)
     ids = random_ids(300, 384, 77)
-    want = plain_model(d).logits(ids)
+    want, want16 = plain_model(d).logits(ids), plain_model_bf16(d).logits(ids)
     eng = Engine.from_folder(d, dtype, max_tokens=1024)
     s, other = eng.open(), eng.open()
     eng.step([StepEntry(other, random_ids(130, 384, 78))])               # a neighbour in the cache
     rows = [eng.step([StepEntry(s, [t], [0])]).cpu().to(torch.float64) for t in ids]
-    tol = TOL_F32 if dtype == "float32" else TOL_BF16
     got = torch.cat(rows)
-    assert rel_err(got[:8], want[:8]) < tol                             # the first tokens of a sequence
-    assert rel_err(got, want) < tol
+    check_logits(got[:8], want[:8], want16[:8], dtype, "the first tokens of a sequence")
+    check_logits(got, want, want16, dtype, "300 tokens one by one")
+    MEASURED.clear()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_the_width_of_a_captured_step(tmp_path, dtype):
+    """A captured decode step is sized for a block table of 8, 16, 32, ... pages: a sequence that grows
+    from 500 to 530 tokens leaves the step captured for 8 pages (512 tokens) for the one of 16, while
+    a short neighbour decodes beside it; every step's logits against the plain implementation."""
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    raw = dict(TINY["D"][0], max_position_embeddings=2048, sliding_window=None)
+    d = make_model_dir(tmp_path / "m", raw, 3)
+    V = raw["vocab_size"]
+    long_ids, short_ids = random_ids(530, V, 81), random_ids(40, V, 82)
+    pm, pm16 = plain_model(d), plain_model_bf16(d)
+    eng = Engine.from_folder(d, dtype, max_tokens=2048, max_seqs=4)
+    a, b = eng.open(), eng.open()
+    eng.step([StepEntry(a, long_ids[:500], []), StepEntry(b, short_ids[:10], [])])
+    rows_a, rows_b = [], []
+    for t in range(30):
+        out = eng.step([StepEntry(a, [long_ids[500 + t]], [0]), StepEntry(b, [short_ids[10 + t]], [0])]).cpu().double()
+        rows_a.append(out[0:1])
+        rows_b.append(out[1:2])
+    if eng.use_graphs:
+        assert sorted(w for _, w in eng.decode_graphs.graphs) == [8, 16]
+    check_logits(torch.cat(rows_a), pm.logits(long_ids)[500:], pm16.logits(long_ids)[500:], dtype, "the long sequence")
+    check_logits(torch.cat(rows_b), pm.logits(short_ids)[10:], pm16.logits(short_ids)[10:], dtype, "its short neighbour")
+    MEASURED.clear()
+    assert int(eng.err_flag) == 0
+
+
+def test_one_sequence_ends_by_capacity_while_others_go_on(tmp_path):
+    """The generation loop launches the next decode step before it has read the last one's tokens,
+    for the sequences that cannot end by count. With 128 positions a prompt of 120 tokens ends after
+    its ninth token for want of room while two shorter requests run to their length and a third to
+    its stop token: every request's tokens equal the plain implementation's."""
+    from scriptling_llm_lib_b200 import llm
+    raw, seed = TINY["A"]                                                # 128 positions
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm = plain_model(d)
+    prompts = [random_ids(n, 256, 130 + n) for n in (120, 20, 5, 64)]
+    kw = dict(strategy="temperature", temperature=1.0, repeat_penalty=0.0)
+    free = [plain.generate(pm, p, 30, stop_ids=(), seed=9 + i, **kw) for i, p in enumerate(prompts)]
+    stop = free[2][11]                                                   # request 2 stops at its 12th token at the latest
+    want = [plain.generate(pm, p, 30, stop_ids=(stop,), seed=9 + i, **kw)[:128 - len(p) + 1] for i, p in enumerate(prompts)]
+    got, st = llm.generate(d, prompts, 30, "temperature", temperature=1.0, repeat_penalty=0.0, seed=9, stop_ids=[stop],
+                           dtype="float32", stats=True)
+    assert got == want
+    reasons = ["stop" if w[-1] == stop else ("capacity" if len(p) + len(w) - 1 >= 128 else "length") for p, w in zip(prompts, want)]
+    assert st["finish_reason"] == reasons and reasons[0] == "capacity" and "length" in reasons
+    eng, _ = llm.load(d, "float32")
+    assert eng.use_graphs and eng.cache.slots.n_held == 0
 
 
 def test_stale_cache_contents_change_nothing(tmp_path):

@@ -6,7 +6,7 @@ prompt, then token by token, in a batch of unequal lengths, against the plain im
 import pytest
 import torch
 
-from helpers import TOL_BF16, TOL_F32, make_model_dir, plain_model, random_ids, rel_err
+from helpers import MEASURED, check_logits, make_model_dir, plain_model, plain_model_bf16, random_ids
 
 pytestmark = pytest.mark.gpu
 
@@ -34,23 +34,37 @@ GROUPED = {
 def real_model(request, tmp_path_factory):
     raw = REAL if request.param == "mha64" else GROUPED
     d = make_model_dir(tmp_path_factory.mktemp("real"), raw, 7)
-    pm = plain_model(d)
+    pm, pm16 = plain_model(d), plain_model_bf16(d)
     reqs = [random_ids(n, raw["vocab_size"], 900 + n) for n in (300, 70, 1)]
-    return d, reqs, [pm.logits(r) for r in reqs]
+    return d, reqs, [pm.logits(r) for r in reqs], [pm16.logits(r) for r in reqs]
+
+
+def report(what):
+    if MEASURED:
+        print(f"\n[{what}] largest error against the rounding / the unrounded plain implementation: "
+              f"{max(m[1] for m in MEASURED):.3g} / {max(m[2] for m in MEASURED):.3g}")
+        MEASURED.clear()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_real_widths(real_model, dtype):
     from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
-    d, reqs, want = real_model
-    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    d, reqs, want, want16 = real_model
     eng = Engine.from_folder(d, dtype, max_tokens=1024)
     # whole, alone
-    for r, w in zip(reqs, want):
+    for i, r in enumerate(reqs):
         s = eng.open()
         got = eng.step([StepEntry(s, r, list(range(len(r))))]).cpu().double()
         s.close()
-        assert rel_err(got, w) < tol
+        check_logits(got, want[i], want16[i], dtype, f"request {i} whole")
+    # the longest prompt in two portions, the second (200 rows: the two-SM product whose epilogue rotates
+    # and fills the cache) onto 100 cached tokens; and in three, the last of 129 rows onto 171
+    for cuts in ([100], [64, 171]):
+        s = eng.open()
+        edges = [0] + cuts + [len(reqs[0])]
+        got = torch.cat([eng.step([StepEntry(s, reqs[0][a:b], list(range(b - a)))]) for a, b in zip(edges, edges[1:])]).cpu().double()
+        s.close()
+        check_logits(got, want[0], want16[0], dtype, f"request 0 in portions cut at {cuts}")
     # a batch of unequal prompts, then 12 tokens one by one
     seqs = [eng.open() for _ in reqs]
     heads = [max(1, len(r) - 12) for r in reqs]
@@ -66,31 +80,35 @@ def test_real_widths(real_model, dtype):
         for j, i in enumerate(live):
             rows[i].append(out[j:j + 1])
             pos[i] += 1
-    for i, w in enumerate(want):
-        assert rel_err(torch.cat(rows[i]), w) < tol, f"request {i}"
+    for i in range(len(reqs)):
+        check_logits(torch.cat(rows[i]), want[i], want16[i], dtype, f"request {i} in a batch, then one by one")
     assert int(eng.err_flag) == 0
+    report(f"real widths {dtype}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_twenty_sequences_decode_together(real_model, dtype):
-    """A decode step of 20 rows (the few-rows tensor-core products, replayed as a graph): unequal short
-    prompts in one step, then six tokens each, every row against the plain implementation."""
+@pytest.mark.parametrize("n", [20, 64, 100])
+def test_many_sequences_decode_together(real_model, dtype, n):
+    """Decode steps of 20, 64 and 100 rows (the few-rows tensor-core products up to 64 rows replayed as a
+    graph, the one-SM product beyond; in 32-bit the 64- and 128-row register tiles): unequal short
+    prompts in one step, then a few tokens each, every row against the plain implementation."""
     from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
-    d, _, _ = real_model
-    pm = plain_model(d)
+    d, _, _, _ = real_model
+    pm, pm16 = plain_model(d), plain_model_bf16(d)
     V = pm.cfg["vocab_size"]
-    tol = TOL_F32 if dtype == "float32" else TOL_BF16
-    reqs = [random_ids(3 + (7 * i) % 38 + 6, V, 1200 + i) for i in range(20)]
-    want = [pm.logits(r) for r in reqs]
-    eng = Engine.from_folder(d, dtype, max_tokens=20 * 64, max_seqs=20)
+    n_dec = 6 if n == 20 else 3
+    span = 38 if n == 20 else 9
+    reqs = [random_ids(3 + (7 * i) % span + n_dec, V, 1200 + i) for i in range(n)]
+    eng = Engine.from_folder(d, dtype, max_tokens=n * 64, max_seqs=n)
     seqs = [eng.open() for _ in reqs]
-    heads = [len(r) - 6 for r in reqs]
+    heads = [len(r) - n_dec for r in reqs]
     out = eng.step([StepEntry(s, r[:h], [h - 1]) for s, r, h in zip(seqs, reqs, heads)]).cpu().double()
-    rows = [[out[i:i + 1]] for i in range(20)]
-    for t in range(6):
+    rows = [[out[i:i + 1]] for i in range(n)]
+    for t in range(n_dec):
         out = eng.step([StepEntry(s, [r[h + t]], [0]) for s, r, h in zip(seqs, reqs, heads)]).cpu().double()
-        for i in range(20):
+        for i in range(n):
             rows[i].append(out[i:i + 1])
-    for i, (w, h) in enumerate(zip(want, heads)):
-        assert rel_err(torch.cat(rows[i]), w[h - 1:]) < tol, f"request {i}"
+    for i, (r, h) in enumerate(zip(reqs, heads)):
+        check_logits(torch.cat(rows[i]), pm.logits(r)[h - 1:], pm16.logits(r)[h - 1:], dtype, f"request {i} of {n}")
     assert int(eng.err_flag) == 0
+    report(f"{n} rows {dtype}")

@@ -1,5 +1,6 @@
 """The decode-attention entry point that allocates nothing, called through its exported C symbol
-and compared with the ordinary entry point (which takes the caller's scratch).
+and compared with the ordinary entry point (which takes the caller's scratch) and with the plain
+implementation's attention.
 
 Some callers cannot allocate device memory while they run (a callback inside another library, a
 loop that must not hit cudaMalloc's synchronisation, a program whose own arena owns all device
@@ -15,6 +16,8 @@ from ctypes import c_float, c_int, c_void_p
 import numpy as np
 import pytest
 import torch
+
+import plain_llama as plain
 
 pytestmark = pytest.mark.gpu
 
@@ -45,6 +48,17 @@ def _case(seed, B, H, G, hd, lengths):
     return q, kp, vp, bt.cuda(), pos0
 
 
+def _plain(q, kp, vp, bt, lengths, H, G, hd):
+    """The plain implementation's attention for the one query of each sequence over its pages."""
+    rows = []
+    for b, n in enumerate(lengths):
+        pages = [int(p) for p in bt[b, :-(-n // 64)]]
+        k = torch.cat([kp[p].permute(1, 0, 2) for p in pages])[:n].double().cpu()       # [n, G, hd]
+        v = torch.cat([vp[p].permute(1, 0, 2) for p in pages])[:n].double().cpu()
+        rows.append(plain.attention(q[b].double().cpu().view(1, H, hd), k, v, torch.tensor([n - 1]), torch.arange(n)).reshape(1, -1))
+    return torch.cat(rows)
+
+
 def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     lib = _lib()
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -61,14 +75,20 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         rc = lib.sllm_attn_decode_bf16(*args, c_void_p(want.data_ptr()), *tail, c_void_p(scratch.data_ptr()), *dims)
         assert rc == 0
         got = torch.full((B, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-        before = torch.cuda.memory_allocated()
         rc = lib.sllm_attn_decode_bf16_noalloc(*args, c_void_p(got.data_ptr()), *tail, *dims)
         assert rc == 0, lib.sllm_attn_decode_noalloc_strerror(rc).decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
         assert torch.isfinite(got.float()).all()
         scale = float(want.float().abs().max())
         assert float((got.float() - want.float()).abs().max()) <= 6e-3 * scale      # the kernels tests' bfloat16 tolerance
+        ref = _plain(q, kp, vp, bt, lengths, H, G, hd)
+        assert float((got.double().cpu() - ref).abs().max()) <= 6e-3 * float(ref.abs().max())
+        # a warm call takes nothing from the device: the driver's count of free bytes (which sees any
+        # cudaMalloc, not only torch's allocator) is the same before and after
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = lib.sllm_attn_decode_bf16_noalloc(*args, c_void_p(got.data_ptr()), *tail, *dims)
+        torch.cuda.synchronize()
+        assert rc == 0 and torch.cuda.mem_get_info()[0] == free_before
 
 
 def test_no_alloc_entry_point_refuses_what_its_scratch_cannot_hold():
@@ -82,3 +102,4 @@ def test_no_alloc_entry_point_refuses_what_its_scratch_cannot_hold():
     assert rc == -10 and b"exceed the built-in scratch" in lib.sllm_attn_decode_noalloc_strerror(rc)
     torch.cuda.synchronize()
     assert float(out.float().abs().sum()) == 0.0                          # nothing ran
+    assert b"head width" in lib.sllm_attn_decode_noalloc_strerror(-1)
