@@ -114,14 +114,16 @@ def model_numbers(cfg, n_layers):
     per_layer = d * (H + 2 * G) * hd + H * hd * d + 3 * d * F          # matrix weights of one layer
     head = V * d
     norms = (2 * n_layers + 1) * d
-    return {"layer_params": per_layer, "head_params": head, "norm_params": norms, "kv_per_token": 2 * G * hd * n_layers}
+    return {"layer_params": per_layer, "head_params": head, "norm_params": norms}
 
 
-def decode_bytes(nums, n_layers, contexts, width):
-    """Bytes one decode step must read at `width` bytes an element: every matrix once (the output head
-    once, tied or not), the norm weights, and the cached keys and values of every live sequence."""
-    weights = width * (nums["layer_params"] * n_layers + nums["head_params"] + nums["norm_params"])
-    return weights + width * nums["kv_per_token"] * sum(contexts)
+def decode_bytes(eng, contexts, width):
+    """Bytes one decode step must read at `width` bytes an element, as the engine's own parts and
+    cache state them: every weight a step uses once (the output head once, tied or not; of the
+    embedding only rows), and the cached keys and values of every live sequence."""
+    weights = eng.model.elements_read_per_step()
+    kv_per_token = sum(2 * len(g.units) * g.need.kv_heads * g.need.head_dim for g in eng.cache.groups)
+    return width * (weights + kv_per_token * sum(contexts))
 
 
 def prefill_flops(cfg, n_layers, lengths, logit_rows=None):
@@ -276,8 +278,7 @@ class Bench:
 
     def decode_record(self, eng, sampler, cfg, n_layers, prompt_lens, steps, warmup, seed, dtype):
         ms, contexts, launches = self.time_decode(eng, sampler, prompt_lens, steps, warmup, seed)
-        nums = model_numbers(cfg, n_layers)
-        achieved = decode_bytes(nums, n_layers, contexts, WIDTH[dtype]) / (ms * 1e-3) / 1e9
+        achieved = decode_bytes(eng, contexts, WIDTH[dtype]) / (ms * 1e-3) / 1e9
         return {"value": round(len(prompt_lens) / ms * 1e3, 1), "ms": round(ms, 4), "gbs": round(achieved, 1),
                 "frac": round(achieved / self.pk["hbm_gbs"], 4)}, launches
 
@@ -298,7 +299,6 @@ def run(args):
     try:
         cfg, n_layers, spec = b.config(args.shape, args.layers)
         full_layers = (SHAPE if args.shape == "smollm2-1.7b" else OTHER_SHAPES[args.shape])["num_hidden_layers"]
-        nums = model_numbers(cfg, n_layers)
         want_points = not args.no_points and args.only == "all" and args.prompts is None
         biggest = max(64 if want_points else 1, args.batch)
         eng, sampler = b.load(spec, dtype, biggest * args.context, biggest)
@@ -353,9 +353,9 @@ def run(args):
             torch.cuda.synchronize()
             dt = time.perf_counter() - marks["t0"]
             assert all(len(o) == args.steps + 2 for o in out)
-            n_pages = -(-args.context // 64)
+            graph = llm.load(spec, dtype)[0].decode_graphs.last_graph      # the captured step the run ended on
             e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
-                   "h2d_bytes_per_step": 4 * (args.batch * (5 + n_pages) + 1), "d2h_bytes_per_step": 4 * args.batch,
+                   "h2d_bytes_per_step": graph.h2d_bytes, "d2h_bytes_per_step": 4 * args.batch,
                    "window": f"decode steps 2..{args.steps + 1} of a generation of {args.steps + 2} tokens: {args.steps} steps, "
                              "wall clock, from after the first decode step to the last token on the host"}
         c1 = clocks.mark()          # the clock samples cover the device-timed steps and the end-to-end run

@@ -19,6 +19,10 @@ import numpy as np
 import torch
 
 from .needs import PAGE, CacheNeed, StateNeed
+
+SEQ_STATE_WORDS = 8      # int32 words of a sequence's record (lib_sampling.cu has the same layout)
+SEQ_POS, SEQ_GENERATED, SEQ_LAST_TOKEN, SEQ_FLAGS, SEQ_KEY, SEQ_COUNTER = 0, 1, 2, 3, 4, 6
+SEQ_FLAG_FINISHED = 1
 from .pool import CacheFull, FreeList
 
 
@@ -48,10 +52,10 @@ class KVGroup:
             lst.append(self.pool.alloc())
 
     def release_unseen(self, slot: int, length: int) -> None:
-        """Window group: give back the pages no query at a position >= length can see."""
-        if self.need.kind != "window":
+        """Give back the pages no query at a position >= length can see (the need's kind says which)."""
+        first_seen = self.need.first_needed(length)
+        if first_seen <= 0:
             return
-        first_seen = length - self.need.window + 1
         lst = self.pages[slot]
         for i, pg in enumerate(lst):
             if pg >= 0 and (i + 1) * PAGE - 1 < first_seen:
@@ -88,6 +92,11 @@ class SequenceCache:
             for u in units:
                 self.group_of_unit[u] = len(self.groups)
             self.groups.append(g)
+        # the fixed-size record of every sequence, on the device: tokens held, tokens generated, last token,
+        # flags, sampling key (2 words), draw counter (2 words). The sampler's kernel reads key and counter
+        # from it and advances it; `length` above and the generation loop's bookkeeping are its host mirror.
+        # One spare row serves the padding rows of replayed decode steps.
+        self.seq_state = torch.zeros((n_slots + 1, SEQ_STATE_WORDS), dtype=torch.int32, device=device)
         self.state: dict[int, torch.Tensor] = {
             unit: torch.zeros((n_slots + 1, *need.shape), dtype=need.dtype, device=device)   # last: spare, for padding
             for unit, need in state_needs.items() if need is not None}
@@ -100,7 +109,17 @@ class SequenceCache:
             g.pages[slot] = []
         for st in self.state.values():
             st[slot].zero_()
+        self.seq_state[slot].zero_()
         return slot
+
+    def seed(self, slots: list[int], seeds: list[int]) -> None:
+        """Start the sampling streams of freshly opened sequences: key = the sequence's 64-bit seed,
+        draw counter 0 (one small copy for the batch)."""
+        rec = np.zeros((len(slots), SEQ_STATE_WORDS), dtype=np.int64)
+        for i, sd in enumerate(seeds):
+            rec[i, SEQ_KEY], rec[i, SEQ_KEY + 1] = sd & 0xFFFFFFFF, (sd >> 32) & 0xFFFFFFFF
+        rec = torch.from_numpy(rec.astype(np.uint32).view(np.int32))
+        self.seq_state.index_copy_(0, torch.as_tensor(slots, dtype=torch.long, device=self.device), rec.to(self.device))
 
     def close(self, slot: int) -> None:
         if not self.slots.is_held(slot):

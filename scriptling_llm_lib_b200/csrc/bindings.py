@@ -14,7 +14,7 @@ import torch
 
 from .build import load_library
 
-PAGE = 64  # tokens per cache page (SLLM_PAGE in common.cuh)
+from ..cache.needs import PAGE  # tokens per cache page; load_library checks that the objects were built with it
 
 
 class KernelError(RuntimeError):
@@ -250,6 +250,12 @@ class TensorCoreGemm:
 
     QKV_ROPE_HEAD_DIMS = (64, 128)
 
+    @classmethod
+    def rotation_fusable(cls, head_dim: int, rot: int, interleaved: bool) -> bool:
+        """Whether the q|k|v product's epilogue can rotate by a (cos, sin) table and fill the cache
+        itself: its 32-column chunks must hold whole pairs, or both halves of a fully rotated head."""
+        return head_dim in cls.QKV_ROPE_HEAD_DIMS and (interleaved or rot == head_dim)
+
     def gemm_qkv_rope(self, a, w, qkv, err_flag, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv,
                       head_dim, rot, interleaved):
         """qkv[:, :n_heads*head_dim] = rotated queries of a @ w^T (w rows: q | k | v heads); the rotated
@@ -291,11 +297,12 @@ class TensorCoreGemm:
             c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
             c_int(1 if swiglu else 0), c_int(ksplit), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_skinny")
 
-    def prefers_skinny(self, a, w, kind: str) -> bool:
+    def prefers_skinny(self, a, w, kind: str, sm_count: int) -> bool:
         """True where the few-rows kernel is the fastest of the three products for a [M,K] x [N,K]^T
         (measured on the layer shapes of 1-8 B models): 9..128 rows; always when the reader takes
         partial sums ("partials": K is split to fill the GPU); with the SiLU gate ("swiglu") up to 64
-        rows; a plain product ("plain") from 33 rows on and only while its N/128 blocks fit one wave."""
+        rows; a plain product ("plain") from 33 rows on and only while its N/128 blocks fit one wave
+        of the GPU's `sm_count` SMs."""
         M, N = a.shape[0], w.shape[0]
         if not (8 < M <= self.SKINNY_MAX_M and self.takes(a, w)):
             return False
@@ -303,7 +310,7 @@ class TensorCoreGemm:
             return True
         if kind == "swiglu":
             return M <= 64
-        return M > 32 and N <= 128 * 148
+        return M > 32 and N <= 128 * sm_count
 
     @staticmethod
     def skinny_split(n_out: int, k: int, sm_count: int) -> int:
@@ -351,10 +358,17 @@ class DecodeKernels:
                 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
     @staticmethod
-    def prefers(a, w) -> bool:
+    def prefers(a, w, sm_count: int) -> bool:
         """True when this kernel is the faster one for the shape: always up to 16 rows; beyond that
-        only while the output is too narrow to give the 128 x 256 tensor-core tiles enough blocks."""
-        return DecodeKernels.takes(a, w) and (a.shape[0] <= 16 or w.shape[0] < 12288)
+        only while the output is too narrow to give the 128 x 256 tensor-core tiles enough blocks
+        (fewer than a third of the SMs; measured at 148: 48 tiles)."""
+        return DecodeKernels.takes(a, w) and (a.shape[0] <= 16 or 3 * -(-w.shape[0] // 256) <= sm_count)
+
+    @staticmethod
+    def rotation_fusable(rot: int, interleaved: bool) -> bool:
+        """Whether the decode attention kernel can rotate queries and the new key by a (cos, sin)
+        table itself: its 16-byte vectors must not straddle the rotary width or its half."""
+        return rot >= 2 and rot % (8 if interleaved else 16) == 0
 
     MAX_SPLITS = 64      # beyond this the merging block falls back to a slow loop
 
@@ -518,6 +532,23 @@ class SamplingKernels:
             raise KernelError("logits must be float32 on a CUDA device")
         _check(fn(c_void_p(logits.data_ptr()), c_int(logits.stride(0)), c_int(n), c_int(V),
                   _ptr(params, torch.int32, "params"), _ptr(out, torch.int32, "out"), _stream()), "sample_rows")
+
+    STATE_WORDS = 8   # int32 words of a sequence's state record: pos, generated, last token, flags, key x2, counter x2
+
+    def sample_rows_state(self, logits, options, state, slots, pos_after, stop_ids, out):
+        """The same, every row's sampling key and draw counter read from (and advanced in) its
+        sequence's record state[slots[row]]; options int32 [4] on the device; stop_ids int32 [n] or None."""
+        if logits.dim() != 2 or logits.stride(1) != 1 or not logits.is_cuda or logits.dtype != torch.float32:
+            raise KernelError("logits must be float32 [rows, vocab] with unit column stride on a CUDA device")
+        n, V = logits.shape
+        if state.dim() != 2 or state.shape[1] != self.STATE_WORDS or slots.shape[0] < n or out.shape[0] < n:
+            raise KernelError("sample_rows_state: state must be [slots, 8] and slots/out must cover every row")
+        fn = self.lib.sllm_sample_rows_state
+        fn.restype = c_int
+        _check(fn(c_void_p(logits.data_ptr()), c_int(logits.stride(0)), c_int(n), c_int(V), _ptr(options, torch.int32, "options"),
+                  _ptr(state, torch.int32, "state"), _ptr(slots, torch.int32, "slots"), _ptr(pos_after, torch.int32, "pos_after"),
+                  _ptr(stop_ids, torch.int32, "stop_ids"), c_int(0 if stop_ids is None else stop_ids.numel()),
+                  _ptr(out, torch.int32, "out"), _stream()), "sample_rows_state")
 
     def repeat_penalty(self, logits, recent, counts, penalty, last_n):
         n, V = logits.shape

@@ -183,6 +183,11 @@ def load_library(name: str) -> ctypes.CDLL:
                 lib = ctypes.CDLL(str(path))
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from None
+            from ..cache.needs import PAGE
+            built_with = lib.sllm_page_tokens() if hasattr(lib, "sllm_page_tokens") else PAGE
+            if built_with != PAGE:
+                raise KernelBuildError(f"{path} was built for cache pages of {built_with} tokens; the cache uses {PAGE} "
+                                       "(SLLM_PAGE in csrc/common.cuh and PAGE in cache/needs.py must agree)")
             _loaded[name] = lib
         return lib
 

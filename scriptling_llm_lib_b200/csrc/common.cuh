@@ -9,6 +9,9 @@
 
 #define SLLM_EXPORT extern "C" __attribute__((visibility("default")))
 
+// every library says which page size it was built with; the loader compares it with the cache's
+SLLM_EXPORT int sllm_page_tokens(void) { return SLLM_PAGE; }
+
 // Every launcher returns the CUDA error code of its launch (0 = success); negative values are
 // argument errors detected on the host before anything is enqueued.
 #define SLLM_ERR_ARG (-1)

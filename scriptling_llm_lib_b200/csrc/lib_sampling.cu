@@ -77,16 +77,66 @@ __device__ double block_scan_excl_d(double v, double* red, double* total) {
   return wexcl + inc - v;
 }
 
+// The per-sequence state record, 8 int32 words per cache slot (csrc and cache/store.py agree on it):
+// tokens held, tokens generated, last token, flags, sampling key (two words), draw counter (two words).
+#define SEQ_STATE_WORDS 8
+#define SEQ_POS 0
+#define SEQ_GENERATED 1
+#define SEQ_LAST_TOKEN 2
+#define SEQ_FLAGS 3
+#define SEQ_KEY 4
+#define SEQ_COUNTER 6
+#define SEQ_FLAG_FINISHED 1
+
+struct SampleStateArgs {
+  const int* options;    // [4]: strategy, temperature bits, top_k, top_p bits -- the same for every row
+  int* state;            // [slots][SEQ_STATE_WORDS]
+  const int* slots;      // [rows] the slot of each row's sequence
+  const int* pos_after;  // [rows] tokens the sequence holds after the step that made these logits (may be null)
+  const int* stop_ids;   // [n_stop]
+  int n_stop;
+};
+
+// What the reference does after it has picked a token: count it, remember it, stop on a stop token
+// (model_f32.go:661-667) -- here as an update of the sequence's record by the thread that wrote the token.
+__device__ __forceinline__ void seq_state_update(const SampleStateArgs& sa, int row, int token) {
+  int* rec = sa.state + (size_t)sa.slots[row] * SEQ_STATE_WORDS;
+  if (sa.pos_after) rec[SEQ_POS] = sa.pos_after[row];
+  rec[SEQ_GENERATED] += 1;
+  rec[SEQ_LAST_TOKEN] = token;
+  unsigned lo = (unsigned)rec[SEQ_COUNTER] + 1u;
+  rec[SEQ_COUNTER] = (int)lo;
+  if (lo == 0u) rec[SEQ_COUNTER + 1] += 1;
+  bool stop = false;
+  for (int i = 0; i < sa.n_stop; i++) stop |= (sa.stop_ids[i] == token);
+  if (stop) rec[SEQ_FLAGS] |= SEQ_FLAG_FINISHED;
+}
+
+// STATE: the row's parameters come from the options record and from its sequence's state record
+// (key and draw counter), which the kernel then advances; else from params[row] and nothing is updated.
+template <bool STATE>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int ldl, int V, const SampleParams* __restrict__ params,
-                   int* __restrict__ out) {
+                   SampleStateArgs sa, int* __restrict__ out) {
   __shared__ double red[32];
   __shared__ float red_f[32];
   __shared__ int red_i[32];
   __shared__ int pick;
   int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const float* lg = logits + (size_t)row * ldl;
-  SampleParams p = params[row];
+  SampleParams p;
+  if (STATE) {
+    const int* rec = sa.state + (size_t)sa.slots[row] * SEQ_STATE_WORDS;
+    p.strategy = sa.options[0];
+    p.temperature = __int_as_float(sa.options[1]);
+    p.top_k = sa.options[2];
+    p.top_p = __int_as_float(sa.options[3]);
+    p.seed_lo = (unsigned)rec[SEQ_KEY]; p.seed_hi = (unsigned)rec[SEQ_KEY + 1];
+    p.draw_lo = (unsigned)rec[SEQ_COUNTER]; p.draw_hi = (unsigned)rec[SEQ_COUNTER + 1];
+    __syncthreads();                 // every thread has read the record before thread 0 advances it
+  } else {
+    p = params[row];
+  }
   int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
   int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
 
@@ -121,7 +171,10 @@ sample_rows_kernel(const float* __restrict__ logits, int ldl, int V, const Sampl
   best = red_f[0];
   best_i = red_i[0];
   if (p.strategy == 0 || !(p.temperature > 0.f)) {
-    if (tid == 0) out[row] = best_i;
+    if (tid == 0) {
+      out[row] = best_i;
+      if (STATE) seq_state_update(sa, row, best_i);
+    }
     return;
   }
   __syncthreads();
@@ -234,7 +287,10 @@ sample_rows_kernel(const float* __restrict__ logits, int ldl, int V, const Sampl
       __syncthreads();
     }
   }
-  if (tid == 0) out[row] = pick;
+  if (tid == 0) {
+    out[row] = pick;
+    if (STATE) seq_state_update(sa, row, pick);
+  }
 }
 
 // logits[row, t] /= penalty if positive else *= penalty, once for each distinct in-range token
@@ -264,7 +320,22 @@ SLLM_EXPORT int sllm_sample_rows(const float* logits, int ldl, int n_rows, int V
                                  cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return SLLM_ERR_ARG;
-  sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ldl, V, (const SampleParams*)params, out);
+  sample_rows_kernel<false><<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ldl, V, (const SampleParams*)params,
+                                                                     SampleStateArgs{}, out);
+  SLLM_RETURN_LAST();
+}
+
+// The same with every row's key and draw counter taken from its sequence's state record
+// (state[slots[row]]), which is advanced: generated count, last token, counter, finished flag when
+// the token is one of stop_ids, and the position if pos_after is given. `options`: 4 int32 on the
+// device (strategy, temperature bits, top_k, top_p bits). Nothing comes from the host per call.
+SLLM_EXPORT int sllm_sample_rows_state(const float* logits, int ldl, int n_rows, int V, const int* options, int* state,
+                                       const int* slots, const int* pos_after, const int* stop_ids, int n_stop, int* out,
+                                       cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (V <= 0 || n_stop < 0 || !options || !state || !slots) return SLLM_ERR_ARG;
+  SampleStateArgs sa{options, state, slots, pos_after, stop_ids, n_stop};
+  sample_rows_kernel<true><<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ldl, V, nullptr, sa, out);
   SLLM_RETURN_LAST();
 }
 

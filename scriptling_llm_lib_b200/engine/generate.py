@@ -125,15 +125,24 @@ class Generator:
         max_seqs = min(eng.cache.n_slots, max_batch or eng.cache.n_slots)
         batches = plan_batches([len(p) for p in prompts], max_tokens, max_seqs, eng.cache.n_pages, eng.max_positions)
         results: list[GenerationResult | None] = [None] * len(prompts)
+        # With an engine that keeps per-sequence state records on the device and a sampler that reads
+        # them, a step's sampling takes nothing from the host: options and stop set go up once per call,
+        # the sequences' seeds once per batch.
+        on_device_state = hasattr(self.sampler, "sample_state") and hasattr(getattr(eng, "cache", None), "seq_state")
+        if on_device_state:
+            self.sampler.begin(options, stop)
         for batch in batches:
             state = BatchState(batch, [prompts[i] for i in batch], max_tokens, stop, eng.max_positions)
             seqs = {i: eng.open() for i in range(len(batch))}
             seeds = [seed + r for r in batch]               # one sampling stream per request
+            if on_device_state:
+                eng.cache.seed([seqs[i].slot for i in range(len(batch))], seeds)
             t_ev = [eng.new_event() for _ in range(3)]
             try:
                 t_ev[0].record()
                 live = state.live()
                 logits = eng.step([StepEntry(seqs[i], state.seqs[i].prompt) for i in live])
+                index = eng.last_step if on_device_state else None
                 fed = [len(state.seqs[i].prompt) for i in live]
                 step_no = 0
                 # When the engine replays its decode step, the next step is launched with the sampled ids
@@ -143,8 +152,11 @@ class Generator:
                     and not options.penalises
                 while True:
                     recent = [state.seqs[i].prompt + state.seqs[i].out for i in live] if options.penalises else None
-                    toks_dev = self.sampler.sample(logits, options, [seeds[i] for i in live],
-                                                   [len(state.seqs[i].out) for i in live], recent)
+                    if on_device_state:
+                        toks_dev = self.sampler.sample_state(logits, eng.cache, index, options, recent)
+                    else:
+                        toks_dev = self.sampler.sample(logits, options, [seeds[i] for i in live],
+                                                       [len(state.seqs[i].out) for i in live], recent)
                     if step_no == 0:
                         t_ev[1].record()
                     ahead = None
@@ -154,7 +166,8 @@ class Generator:
                         cont = [j for j, i in enumerate(live) if not state.ends_by_count(i, fed[j])]
                         if cont:
                             rows = toks_dev if len(cont) == len(live) else toks_dev[torch.as_tensor(cont, device=toks_dev.device)]
-                            ahead = ([live[j] for j in cont], eng.decode_step_device([seqs[live[j]] for j in cont], rows))
+                            ahead = ([live[j] for j in cont], eng.decode_step_device([seqs[live[j]] for j in cont], rows),
+                                     eng.last_step if on_device_state else None)
                     toks = read()
                     for i in state.accept(live, fed, toks):
                         seqs.pop(i).close()
@@ -166,9 +179,14 @@ class Generator:
                         break
                     if ahead is not None:
                         keep = [j for j, i in enumerate(ahead[0]) if state.seqs[i].reason is None]
-                        logits = ahead[1] if len(keep) == len(ahead[0]) else ahead[1][torch.as_tensor(keep, device=ahead[1].device)]
+                        if len(keep) == len(ahead[0]):
+                            logits, index = ahead[1], ahead[2]
+                        else:
+                            rows = torch.as_tensor(keep, device=ahead[1].device)
+                            logits, index = ahead[1][rows], (ahead[2].rows(rows) if on_device_state else None)
                     else:
                         logits = eng.step([StepEntry(seqs[i], [state.seqs[i].out[-1]]) for i in live])
+                        index = eng.last_step if on_device_state else None
                     fed = [1] * len(live)
                     step_no += 1
                 t_ev[2].record()

@@ -27,8 +27,8 @@ class DecodeGraph:
         self.engine, self.batch, self.width = engine, batch, width
         n_groups = len(engine.cache.groups)
         B = batch
-        # layout of the index buffer (int32): ids, pos, seq, seq_start, pos0, slots, want_rows, block tables
-        self.sizes = [B, B, B, B + 1, B, B, B] + [B * width] * n_groups
+        # layout of the index buffer (int32): ids, pos, seq, seq_start, pos0, slots, want_rows, pos after, block tables
+        self.sizes = [B, B, B, B + 1, B, B, B, B] + [B * width] * n_groups
         total = sum(self.sizes)
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
@@ -40,8 +40,8 @@ class DecodeGraph:
         ctx = StepContext(engine)
         ctx.n_tokens = ctx.n_seqs = B
         ctx.max_new = 1
-        ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows = views[:7]
-        ctx.block_tables = [v.view(B, width) for v in views[7:]]
+        ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows, ctx.seq_pos_after = views[:8]
+        ctx.block_tables = [v.view(B, width) for v in views[8:]]
         ctx.is_decode = True
         ctx.max_pages = width
         self.ctx = ctx
@@ -84,6 +84,9 @@ class DecodeGraph:
         off += B
         h[off:off + B] = np.arange(B)
         off += B
+        h[off:off + B] = 1
+        h[off:off + n] = np.asarray(pos0, dtype=np.int64) + 1 if n else 0
+        off += B
         for g in range(len(eng.cache.groups)):
             tab = h[off:off + B * W].reshape(B, W)
             tab[:] = eng.cache.n_pages               # the spare page
@@ -113,6 +116,15 @@ class DecodeGraph:
         bindings.LAUNCHES[0] += self.kernels_per_replay
         return self.logits[:n]
 
+    def index(self, n: int):
+        from .step import StepIndex
+        return StepIndex(self.ctx.slots[:n], self.ctx.seq_pos_after[:n])
+
+    @property
+    def h2d_bytes(self) -> int:
+        """Bytes copied to the device before each replay when the token ids are there already."""
+        return 4 * (self.host.numel() - self.batch)
+
 
 class DecodeGraphs:
     """The graphs of one engine, captured on first use."""
@@ -120,6 +132,8 @@ class DecodeGraphs:
     def __init__(self, engine):
         self.engine = engine
         self.graphs: dict[tuple[int, int], DecodeGraph] = {}
+        self.last_index = None
+        self.last_graph: DecodeGraph | None = None
 
     def clear(self):
         self.graphs.clear()
@@ -133,4 +147,6 @@ class DecodeGraphs:
         g = self.graphs.get(key)
         if g is None:
             g = self.graphs[key] = DecodeGraph(self.engine, batch, width)
-        return g.run(ids, pos0, slots, tables)
+        out = g.run(ids, pos0, slots, tables)
+        self.last_graph, self.last_index = g, g.index(out.shape[0])
+        return out

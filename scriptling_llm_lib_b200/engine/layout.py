@@ -25,11 +25,11 @@ class ModelLayout:
     vocab_size: int
     hidden_size: int
     max_positions: int
-    embedding_name: str
+    embedding: PartSpec                 # resolved through the EMBEDDINGS registry
     layers: tuple[LayerSpec, ...]
     schedule: tuple[ScheduleEntry, ...]
-    final_norm: PartSpec
-    head_name: str | None               # None: the head is tied to the embedding
+    final_norm: PartSpec                # NORMS; adds the last pending addend and norms the wanted rows
+    head: PartSpec                      # HEADS
     stop_ids: tuple[int, ...] = ()
     ignorable_tensors: tuple[str, ...] = field(default=())   # may be in the file without being used
 

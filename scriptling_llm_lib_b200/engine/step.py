@@ -61,6 +61,17 @@ class StepEntry:
     want: list[int] | None = None      # places among `tokens` whose logits are wanted; None: the last
 
 
+@dataclass
+class StepIndex:
+    """Device views of the last step's sequences, in entry order: their cache slots and the tokens each
+    holds after the step. The sampler finds every row's state record through them without a copy."""
+    slots: torch.Tensor
+    pos_after: torch.Tensor
+
+    def rows(self, keep: torch.Tensor) -> "StepIndex":
+        return StepIndex(self.slots[keep].contiguous(), self.pos_after[keep].contiguous())
+
+
 class StepContext:
     """What the parts see of a step: the kernels, the packed batch's index arrays, the cache."""
 
@@ -72,6 +83,7 @@ class StepContext:
         self.err_flag = engine.err_flag
         self.n_tokens = self.n_seqs = self.max_new = 0
         self.token_ids = self.tok_pos = self.tok_seq = self.seq_start = self.seq_pos0 = self.slots = None
+        self.seq_pos_after = None
         self.block_tables: list[torch.Tensor] = []
 
     @property
@@ -118,6 +130,7 @@ class Engine:
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._tickets = None
+        self.last_step: StepIndex | None = None
         self.cache = None
         self.resize_cache(max_tokens, max_seqs)
 
@@ -256,10 +269,12 @@ class Engine:
             slots = [e.sequence.slot for e in entries]
             tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
             logits = self.decode_graphs.run(ids, pos0, slots, tables)
+            self.last_step = self.decode_graphs.last_index
             if want_rows != list(range(B)):
                 logits = logits[torch.as_tensor(want_rows, dtype=torch.long, device=self.device)] if want_rows else None
         else:
             ctx = self._context(entries, ids, lens, pos0, want_rows)
+            self.last_step = StepIndex(ctx.slots, ctx.seq_pos_after)
             logits = self._forward(ctx, want=bool(want_rows))
             if T > B:                                   # a prompt step is long enough to afford the read
                 self.check_errors()
@@ -296,6 +311,7 @@ class Engine:
         slots = [s.slot for s in sequences]
         tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
         logits = self.decode_graphs.run(ids.contiguous(), [s.length for s in sequences], slots, tables)
+        self.last_step = self.decode_graphs.last_index
         self.cache.advance(growth)
         return logits
 
@@ -322,7 +338,7 @@ class Engine:
         slots = [e.sequence.slot for e in entries]
         tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
         pieces = [ids.astype(np.int32), tok_pos, tok_seq, seq_start, pos0_a, np.asarray(slots, dtype=np.int32),
-                  np.asarray(want_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
+                  np.asarray(want_rows, dtype=np.int32), pos0_a + lens_a] + [t.reshape(-1) for t in tables]
         sizes = [p.shape[0] for p in pieces]
         host = torch.from_numpy(np.concatenate(pieces)).pin_memory()
         dev = host.to(self.device, non_blocking=True)
@@ -332,8 +348,8 @@ class Engine:
             off += n
         ctx = StepContext(self)
         ctx.n_tokens, ctx.n_seqs, ctx.max_new = T, B, int(lens_a.max())
-        ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows = views[:7]
-        ctx.block_tables = [v.view(B, t.shape[1]) for v, t in zip(views[7:], tables)]
+        ctx.token_ids, ctx.tok_pos, ctx.tok_seq, ctx.seq_start, ctx.seq_pos0, ctx.slots, ctx.want_rows, ctx.seq_pos_after = views[:8]
+        ctx.block_tables = [v.view(B, t.shape[1]) for v, t in zip(views[8:], tables)]
         ctx.is_decode = bool((lens_a == 1).all())
         ctx.max_pages = int(-(-(int((pos0_a + lens_a).max())) // PAGE))
         ctx._host_keepalive = host

@@ -13,7 +13,8 @@ from ..config.llama import LlamaConfig
 from ..config.registry import register_architecture
 from ..engine.layout import ModelLayout, sequential_schedule
 from ..parts.base import PartSpec
-from ..parts.block import LayerSpec
+from ..parts.block import pre_norm_layer
+from ..parts.embedding import linear_head, token_embedding
 
 
 def llama_layout(cfg: LlamaConfig) -> ModelLayout:
@@ -34,13 +35,14 @@ def llama_layout(cfg: LlamaConfig) -> ModelLayout:
                                          weight_name=p + "input_layernorm.weight"))
         norm2 = PartSpec("rmsnorm", dict(width=cfg.hidden_size, eps=cfg.rms_norm_eps,
                                          weight_name=p + "post_attention_layernorm.weight"))
-        layers.append(LayerSpec(mixer, ffn, norm1, norm2, "pre_norm"))
+        layers.append(pre_norm_layer(mixer, ffn, norm1, norm2))
     return ModelLayout(
         vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, max_positions=cfg.max_position_embeddings,
-        embedding_name="model.embed_tokens.weight", layers=tuple(layers),
+        embedding=token_embedding(cfg.vocab_size, cfg.hidden_size, "model.embed_tokens.weight"), layers=tuple(layers),
         schedule=sequential_schedule(cfg.num_hidden_layers),
         final_norm=PartSpec("rmsnorm", dict(width=cfg.hidden_size, eps=cfg.rms_norm_eps, weight_name="model.norm.weight")),
-        head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
+        head=linear_head(cfg.vocab_size, cfg.hidden_size, "model.embed_tokens.weight", tied=True) if cfg.tie_word_embeddings
+        else linear_head(cfg.vocab_size, cfg.hidden_size, "lm_head.weight"),
         stop_ids=cfg.eos_token_ids,
         ignorable_tensors=("lm_head.weight",) if cfg.tie_word_embeddings else ())
 

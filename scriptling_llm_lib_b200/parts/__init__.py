@@ -1,9 +1,10 @@
-from . import attention, block, feedforward, norm, rotary  # noqa: F401  (registers the built-in parts)
-from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FeedForward, Mixer, Norm, Part,
-                   PartSpec, PositionEncoding)
-from .block import LayerSpec, build_block
-from .embedding import OutputHead, TokenEmbedding
+from . import attention, block, embedding, feedforward, norm, rotary  # noqa: F401  (registers the built-in parts)
+from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Embedding, FeedForward,
+                   Head, Mixer, Norm, Part, PartSpec, PositionEncoding)
+from .block import Block, LayerSpec, build_block, pre_norm_layer
+from .embedding import OutputHead, TokenEmbedding, linear_head, token_embedding
 from .linear import Linear
 
-__all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "FeedForward", "Mixer", "Norm",
-           "Part", "PartSpec", "PositionEncoding", "LayerSpec", "build_block", "OutputHead", "TokenEmbedding", "Linear"]
+__all__ = ["ARRANGEMENTS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Embedding",
+           "FeedForward", "Head", "Mixer", "Norm", "Part", "PartSpec", "PositionEncoding", "Block", "LayerSpec", "build_block",
+           "pre_norm_layer", "OutputHead", "TokenEmbedding", "linear_head", "token_embedding", "Linear"]

@@ -6,6 +6,12 @@ after the query are masked; max-subtracted softmax; out = sum p v; y = out Wo^T
 (model_f32.go:391-470, float32_ops.go:190-235, :252-260). A `window` (absent in the reference)
 also masks keys `window` or more positions behind the query and lets the cache give old pages
 back. With `writes=False` the layer projects queries only and reads the unit another layer wrote.
+
+The position encoding is optional (`position=None`: queries and keys as projected). Storing keys
+and values in the cache is this mixer's own step, whatever the encoding: for an encoding that is a
+rotation by a table the store and the rotation are one kernel (or part of the q|k|v product's
+epilogue, or of the decode attention kernel, where the widths allow); any other encoding rewrites
+the step's query and key rows in place first (`transform`) and the store copies.
 """
 from __future__ import annotations
 
@@ -20,9 +26,13 @@ from .linear import Linear
 
 
 class Attention(Mixer):
-    graph_safe = True
+    @property
+    def graph_safe(self) -> bool:
+        """The decode step launches the same work whatever the values; an encoding that rewrites rows
+        itself (`transform`) has to say the same of its own work."""
+        return self.position is None or self.position.rotation() is not None or bool(getattr(self.position, "graph_safe", False))
 
-    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec,
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec | None,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
                  scale: float | None = None):
         if n_heads % n_kv_heads:
@@ -31,7 +41,7 @@ class Attention(Mixer):
             raise ValueError(f"head_dim {head_dim}: the attention kernels take head widths in steps of 16")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim, self.window = hidden, n_heads, n_kv_heads, head_dim, window
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
-        self.position = POSITION_ENCODINGS.build(position)
+        self.position = POSITION_ENCODINGS.build(position) if position is not None else None
         qw, kw = n_heads * head_dim, n_kv_heads * head_dim
         self.qkv = Linear([q_name, k_name, v_name], [qw, kw, kw], hidden)
         self.out = Linear([o_name], [hidden], qw)
@@ -46,7 +56,19 @@ class Attention(Mixer):
         self.q_only = self.qkv.rows(0, self.n_heads * self.head_dim)
 
     def prepare(self, max_positions, device):
-        self.position.prepare(max_positions, device)
+        if self.position is not None:
+            self.position.prepare(max_positions, device)
+
+    def _store(self, qkv, ctx, rotation, n_kv, kpages, vpages, block_table) -> None:
+        """Give the step's queries and keys their positions and append keys and values to the cache
+        (n_kv == 0: queries only). `rotation`: the encoding's table, or None."""
+        if self.position is not None and rotation is None:
+            self.position.transform(qkv, ctx, self.n_heads, n_kv, self.head_dim)
+        if rotation is None and n_kv == 0:
+            return
+        table, rot, interleaved = rotation if rotation is not None else (None, 0, False)
+        ctx.kernels.rope_kv_write(qkv, ctx.tok_pos, ctx.tok_seq, block_table, table, kpages, vpages, self.n_heads, n_kv,
+                                  self.head_dim, rot, interleaved)
 
     def cache_need(self):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
@@ -54,12 +76,15 @@ class Attention(Mixer):
     def forward(self, x, ctx, unit, writes):
         kpages, vpages, block_table = ctx.unit_kv(unit)
         fast_decode = ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
-        fusion = getattr(self.position, "decode_fusion", lambda: None)() if fast_decode else None
+        rotation = self.position.rotation() if self.position is not None else None
         tc = ctx.kernels.tensor_core if x.dtype == torch.bfloat16 else None
+        # a rotation can ride in the decode attention kernel, or in the q|k|v product of a long prompt step
+        fusion = rotation if (fast_decode and rotation is not None and DecodeKernels.rotation_fusable(*rotation[1:])) else None
         fused_product = None
-        if (tc is not None and writes and not fast_decode and x.shape[0] > tc.SKINNY_MAX_M and self.head_dim in tc.QKV_ROPE_HEAD_DIMS
-                and self.qkv.weight.dtype == torch.bfloat16 and tc.takes(x, self.qkv.weight)):
-            fused_product = getattr(self.position, "product_fusion", lambda: None)()
+        if (tc is not None and writes and not fast_decode and rotation is not None and x.shape[0] > tc.SKINNY_MAX_M
+                and tc.rotation_fusable(self.head_dim, *rotation[1:]) and self.qkv.weight.dtype == torch.bfloat16
+                and tc.takes(x, self.qkv.weight)):
+            fused_product = rotation
         if fused_product is not None:
             # a long prompt step: the q|k|v product rotates and fills the cache in its own epilogue
             qkv = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
@@ -67,10 +92,9 @@ class Attention(Mixer):
                              kpages, vpages, self.n_heads, self.n_kv_heads, self.head_dim, fused_product[1], fused_product[2])
         else:
             qkv = (self.qkv if writes else self.q_only).forward(x, ctx)
-            if fusion is None and writes:
-                self.position.apply(qkv, ctx, self.n_heads, self.n_kv_heads, kpages, vpages, block_table)
-            elif fusion is None:
-                self.position.apply(qkv, ctx, self.n_heads, 0, None, None, block_table)
+            if fusion is None:
+                self._store(qkv, ctx, rotation, self.n_kv_heads if writes else 0, kpages if writes else None,
+                            vpages if writes else None, block_table)
         attn = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
         if fast_decode:
             n_split = ctx.decode_splits(self.n_heads, self.n_kv_heads, self.head_dim)

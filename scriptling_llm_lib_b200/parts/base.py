@@ -1,13 +1,20 @@
-"""The parts a layer is put together from, and the registries that name them.
+"""The parts a model is put together from, and the registries that name them.
 
-A layer is {norm, mixer, norm, feed-forward} in some arrangement. Each part takes its sizes and
-constants as parameters, publishes the tensors it wants (`tensor_specs`), takes them (`bind`) and
-runs on the rows it is given (`forward`). No part knows which model it is in: tensor names, widths,
-eps, theta and head counts all arrive through the constructor. A model's layout names a part by
-its registered kind, layer by layer, so different layers can have different mixers and
-feed-forwards.
+A layer is an arrangement (a block) of named parts: norms, a mixer, a feed-forward, or whatever
+the arrangement asks for. Around the layers stand an embedding, a final norm and an output head,
+parts like the others. Each part takes its sizes and constants as parameters, publishes the
+tensors it wants (`tensor_specs`), takes them (`bind`) and runs on the rows it is given
+(`forward`). No part knows which model it is in: tensor names, widths, eps, theta and head counts
+all arrive through the constructor. A model's layout names a part by its registered kind, layer
+by layer, so different layers can have different mixers and feed-forwards.
 
 Interfaces (duck-typed; the base classes document them):
+
+  Embedding.forward(ids, ctx) -> x            the float32 residual stream [T, hidden] of the step's tokens
+  Head.forward(normed, ctx) -> logits         float32 [n, vocab] for the rows it is given
+  Block.forward(residual, delta, ctx, unit, writes) -> delta
+                                              an arrangement: runs its parts on the stream; also parts(),
+                                              graph_safe(), cache_need(), state_need() (see block.py)
 
   Mixer.cache_need() -> CacheNeed | None      keys/values the layer keeps per position
   Mixer.state_need() -> StateNeed | None      per-sequence state of fixed size
@@ -20,7 +27,7 @@ Interfaces (duck-typed; the base classes document them):
                                               residual float32 [T, hidden], updated in place by
                                               += delta when rows is None; rows picks rows to norm;
                                               delta: None or either form of y
-  PositionEncoding.prepare(max_positions, device); .apply(...)   see rotary.py
+  PositionEncoding.prepare(max_positions, device); .rotation() or .transform(...)   see below
 """
 from __future__ import annotations
 
@@ -41,6 +48,17 @@ class PartSpec:
 class Part:
     def tensor_specs(self) -> list[TensorSpec]:
         return []
+
+    def elements_read_per_step(self) -> int:
+        """Weight elements a decode step has to read for this part whatever the batch (a roofline's
+        numerator): by default every tensor it owns, once."""
+        n = 0
+        for s in self.tensor_specs():
+            k = 1
+            for d in s.shape:
+                k *= d
+            n += k
+        return n
 
     def bind(self, tensors: dict, dtype, device) -> None:
         """Take this part's tensors (by the names it published) for an engine of `dtype`."""
@@ -71,7 +89,35 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    pass
+    """How a mixer's queries and keys learn their positions. A mixer without one (None in its
+    parameters) uses queries and keys as projected. An encoding is one of two kinds:
+
+      rotation() -> (table, rotary_width, interleaved)
+          a rotation of pairs by an angle per position and pair: table float32
+          [positions, rotary_width / 2, 2] of (cos, sin). The mixer's kernels do the rotating, fused
+          into the products and the decode attention where the widths allow.
+      transform(qkv, ctx, n_heads, n_kv_heads, head_dim) -> None
+          anything else: rewrite the query heads (columns [0, n_heads * head_dim)) and the key heads
+          (the next n_kv_heads * head_dim columns) of the step's rows in place, using ctx.tok_pos.
+          `rotation()` then returns None.
+
+    Neither writes the cache: storing keys and values is the mixer's own step."""
+
+    def rotation(self):
+        return None
+
+    def transform(self, qkv, ctx, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ids, ctx):
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, normed, ctx):
+        raise NotImplementedError
 
 
 class Registry:
@@ -101,3 +147,5 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 ARRANGEMENTS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")

@@ -1,32 +1,78 @@
 """How a layer's parts are arranged around the residual stream.
 
-"pre_norm": x += mixer(norm(x)); x += feed_forward(norm(x)) (model_f32.go:382-500). The residual
-stream is float32; a block hands its last sublayer's output on as a pending `delta`, which the next
-norm adds while it reads the row, so no separate pass over the stream is needed.
+A layer is data: the name of an arrangement and the parts it is made of, by role. An arrangement
+(a block class) builds its parts from their registries, runs them in its order, and answers for
+the layer: which parts it has, whether its decode step can be captured, what it needs of the cache.
+The engine asks the block, never a part by name, so an arrangement with other roles (no
+feed-forward, two mixers, four norms) is a class of its own and nothing else changes.
+
+"pre_norm": x += mixer(norm(x)); x += feed_forward(norm(x)) (model_f32.go:382-500), roles
+`mixer_norm`, `mixer`, `feed_forward_norm`, `feed_forward`. The residual stream is float32; a block
+hands its last sublayer's output on as a pending `delta`, which the next norm adds while it reads
+the row, so no separate pass over the stream is needed.
+
+A block's interface:
+  parts() -> list of its parts                  for tensor specs, bind, prepare
+  forward(residual, delta, ctx, unit, writes) -> delta
+  graph_safe() -> bool                          its decode step launches the same work whatever the values
+  cache_need() -> CacheNeed | None              what the cache unit it writes must hold
+  state_need() -> StateNeed | None              per-sequence state of fixed size
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
+from typing import Mapping
 
 from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, PartSpec
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer as data: which parts, with which parameters, in which arrangement."""
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    arrangement: str = "pre_norm"
+    """One layer as data: the arrangement and its parts by role."""
+    arrangement: str
+    parts: Mapping[str, PartSpec] = field(default_factory=dict)
 
 
-class PreNormBlock:
+def pre_norm_layer(mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, feed_forward_norm: PartSpec) -> LayerSpec:
+    return LayerSpec("pre_norm", dict(mixer=mixer, feed_forward=feed_forward, mixer_norm=mixer_norm,
+                                      feed_forward_norm=feed_forward_norm))
+
+
+class Block:
+    """Base of the arrangements: answers for the layer out of `parts()`; an arrangement with one
+    mixer need only name it `self.mixer`."""
+    mixer = None
+
+    def parts(self) -> list:
+        raise NotImplementedError
+
+    def forward(self, residual, delta, ctx, unit, writes):
+        raise NotImplementedError
+
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts())
+
+    def cache_need(self):
+        return self.mixer.cache_need() if self.mixer is not None else None
+
+    def state_need(self):
+        return self.mixer.state_need() if self.mixer is not None else None
+
+
+def _role(spec: LayerSpec, role: str) -> PartSpec:
+    try:
+        return spec.parts[role]
+    except KeyError:
+        raise ValueError(f"the {spec.arrangement!r} arrangement needs a part in the role {role!r}; "
+                         f"the layer has {', '.join(sorted(spec.parts)) or 'none'}") from None
+
+
+class PreNormBlock(Block):
     def __init__(self, spec: LayerSpec):
-        self.mixer_norm = NORMS.build(spec.mixer_norm)
-        self.mixer = MIXERS.build(spec.mixer)
-        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm)
-        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward)
+        self.mixer_norm = NORMS.build(_role(spec, "mixer_norm"))
+        self.mixer = MIXERS.build(_role(spec, "mixer"))
+        self.feed_forward_norm = NORMS.build(_role(spec, "feed_forward_norm"))
+        self.feed_forward = FEED_FORWARDS.build(_role(spec, "feed_forward"))
 
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]

@@ -35,9 +35,9 @@ class SwiGLU(FeedForward):
         h = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
         w = self.gate_up.weight
         fast = self.tiled and x.dtype == torch.bfloat16 and w.dtype == x.dtype
-        if fast and ctx.kernels.tensor_core.prefers_skinny(x, w, "swiglu"):
+        if fast and ctx.kernels.tensor_core.prefers_skinny(x, w, "swiglu", ctx.engine.sm_count):
             ctx.kernels.tensor_core.gemm_skinny(x, w, h, ctx.err_flag, swiglu=True)
-        elif fast and ctx.kernels.decode.prefers(x, w):
+        elif fast and ctx.kernels.decode.prefers(x, w, ctx.engine.sm_count):
             ctx.kernels.decode.gemm_small_m(x, w, h, swiglu=True)
         elif fast and ctx.kernels.tensor_core.takes(x, w):
             ctx.kernels.tensor_core.gemm(x, w, h, ctx.err_flag, swiglu=True)

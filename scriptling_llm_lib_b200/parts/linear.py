@@ -38,14 +38,14 @@ class Linear:
         w = self.weight
         out_dtype = out_dtype or x.dtype
         if w.dtype == x.dtype:
-            if x.dtype == torch.bfloat16 and ctx.kernels.tensor_core.prefers_skinny(x, w, "partials" if partials_ok else "plain"):
+            if x.dtype == torch.bfloat16 and ctx.kernels.tensor_core.prefers_skinny(x, w, "partials" if partials_ok else "plain", ctx.engine.sm_count):
                 tc = ctx.kernels.tensor_core
                 split = tc.skinny_split(w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
                 shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
                 out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)
                 tc.gemm_skinny(x, w, out, ctx.err_flag)
                 return out
-            if x.dtype == torch.bfloat16 and ctx.kernels.decode.prefers(x, w):
+            if x.dtype == torch.bfloat16 and ctx.kernels.decode.prefers(x, w, ctx.engine.sm_count):
                 split = ctx.kernels.decode.split_for(w.shape[0], w.shape[1], ctx.engine.sm_count) if partials_ok else 1
                 shape = (split, x.shape[0], w.shape[0]) if split > 1 else (x.shape[0], w.shape[0])
                 out = torch.empty(shape, dtype=torch.float32 if split > 1 else out_dtype, device=x.device)

@@ -13,6 +13,8 @@ from .base import NORMS, Norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, width: int, eps: float, weight_name: str):
         self.width, self.eps, self.weight_name = width, float(eps), weight_name
         self.weight = None

@@ -5,9 +5,9 @@ f_i * position; dimensions past rotary_dim are left alone (model_f32.go:252-260,
 float32_ops.go:174-188). The reference pairs adjacent dimensions (2i, 2i+1) ("interleaved"); the
 half-split pairing (i, i + rotary_dim/2) is what safetensors checkpoints of the family expect.
 The reference knows no frequency rescaling; `llama3` and `linear` rewrite the table on the host.
-Angles, cosines and sines are computed on the host in float64 and stored as float32 pairs.
-Rotated K and raw V are written into the paged cache by the same kernel (V is never rotated,
-model_f32.go:445-448).
+Angles, cosines and sines are computed on the host in float64 and stored as float32 pairs. The
+encoding only owns the table: the mixer's kernels rotate by it (and store keys and values, which
+is the mixer's business: V is never rotated, model_f32.go:445-448).
 """
 from __future__ import annotations
 
@@ -58,27 +58,9 @@ class RotaryEncoding(PositionEncoding):
     def max_positions(self) -> int:
         return 0 if self.cos_sin is None else self.cos_sin.shape[0]
 
-    def decode_fusion(self):
-        """(table, rotary width, interleaved) when the decode attention kernel can rotate by itself
-        (its 16-byte vectors must not straddle the rotary width or its half), else None."""
-        interleaved = self.pairing == "interleaved"
-        if self.cos_sin is None or self.rotary_dim % (8 if interleaved else 16):
-            return None
-        return self.cos_sin, self.rotary_dim, interleaved
-
-    def product_fusion(self):
-        """(table, rotary width, interleaved) when the q|k|v product's own epilogue can rotate and fill
-        the cache (its 32-column chunks must hold whole pairs, or both halves of a fully rotated head)."""
-        interleaved = self.pairing == "interleaved"
-        if self.cos_sin is None or (not interleaved and self.rotary_dim != self.head_dim):
-            return None
-        return self.cos_sin, self.rotary_dim, interleaved
-
-    def apply(self, qkv, ctx, n_heads: int, n_kv: int, kpages, vpages, block_table) -> None:
-        """Rotate the q heads of `qkv` in place; rotate its k heads and store them with the v heads at
-        each token's place in the cache (n_kv == 0: queries only)."""
-        ctx.kernels.rope_kv_write(qkv, ctx.tok_pos, ctx.tok_seq, block_table, self.cos_sin, kpages, vpages, n_heads,
-                                  n_kv, self.head_dim, self.rotary_dim, self.pairing == "interleaved")
+    def rotation(self):
+        """(table [positions, rotary_dim / 2, 2] of (cos, sin), rotary width, interleaved pairing)."""
+        return self.cos_sin, self.rotary_dim, self.pairing == "interleaved"
 
 
 POSITION_ENCODINGS.register("rotary", RotaryEncoding)

@@ -4,8 +4,11 @@ Strategies and option names are the reference's (model.go:701-851; `llm.generate
 model.go:868-946): "greedy", "temperature", "top_k", "top_p", with `temperature`, `top_k`, `top_p`,
 `repeat_penalty`, `repeat_last_n`. Greedy ignores temperature and penalty (model_f32.go:610-615);
 a temperature of 0 means greedy. The reference draws from one clock-seeded generator
-(sampling.go:14-18); here each sequence has its own seed and a draw counter (its fixed-size
-sampling state), so a sequence's tokens do not depend on its batch mates.
+(sampling.go:14-18); here each sequence has its own seed and a draw counter, kept in its
+fixed-size state record on the device (cache.seq_state) and advanced by the sampling kernel, so a
+sequence's tokens do not depend on its batch mates and a sampled decode step takes nothing from
+the host. `sample` (parameters packed on the host for every call) remains for callers without
+sequences: kernel tests and measurements.
 """
 from __future__ import annotations
 
@@ -83,6 +86,47 @@ class Sampler:
         self._copied.record()
         return dev
 
+    def begin(self, options: SamplingOptions, stop_ids=()) -> None:
+        """Put the options and the stop set of a generation call on the device (once per call, and
+        only when they differ from the last call's); `sample_state` then takes nothing from the host."""
+        key = (options.strategy if not options.is_greedy else "greedy", options.temperature, options.top_k, options.top_p,
+               tuple(sorted(set(int(t) for t in stop_ids or ()))))
+        if getattr(self, "_begun", None) == key:
+            return
+        words = pack_params(options, [0], [0])[0, :4].copy()
+        self._options_dev = torch.from_numpy(words).to(self.device)
+        self._stop_dev = torch.tensor(key[4], dtype=torch.int32, device=self.device) if key[4] else None
+        self._begun = key
+
+    def sample_state(self, logits: torch.Tensor, cache, index, options: SamplingOptions,
+                     recent: list[list[int]] | None = None) -> torch.Tensor:
+        """logits float32 [n, V] -> int32 token ids [n] on the device, every row's sampling key and draw
+        counter taken from its sequence's state record on the device (`cache.seq_state` at
+        `index.slots`), which the kernel advances (tokens held, generated count, last token, counter,
+        finished flag on a stop token). Call `begin` first."""
+        n = logits.shape[0]
+        if options.penalises and recent is not None:
+            logits = self._penalised(logits, options, recent)
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        self.kernels.sample_rows_state(logits, self._options_dev, cache.seq_state, index.slots, index.pos_after,
+                                       self._stop_dev, out)
+        return out
+
+    def _penalised(self, logits, options, recent):
+        n = logits.shape[0]
+        last_n = max(1, options.repeat_last_n)
+        win = np.full((n, last_n), -1, dtype=np.int32)
+        counts = np.zeros(n, dtype=np.int32)
+        for i, r in enumerate(recent):
+            tail = r[-last_n:]
+            win[i, :len(tail)] = tail
+            counts[i] = len(tail)
+        logits = logits.clone()
+        self.kernels.repeat_penalty(
+            logits, torch.from_numpy(win).to(self.device), torch.from_numpy(counts).to(self.device),
+            torch.full((n,), float(options.repeat_penalty), dtype=torch.float32, device=self.device), last_n)
+        return logits
+
     def begin_read(self, tokens: torch.Tensor):
         """Start copying sampled ids to the host; returns a function that waits for that copy alone and
         gives the ids as a list. Called before later work is put on the stream, it lets the host read a
@@ -113,17 +157,7 @@ class Sampler:
         `recent`: each sequence's prompt and generated tokens so far (for the repeat penalty)."""
         n = logits.shape[0]
         if options.penalises and recent is not None:
-            last_n = max(1, options.repeat_last_n)
-            win = np.full((n, last_n), -1, dtype=np.int32)
-            counts = np.zeros(n, dtype=np.int32)
-            for i, r in enumerate(recent):
-                tail = r[-last_n:]
-                win[i, :len(tail)] = tail
-                counts[i] = len(tail)
-            logits = logits.clone()
-            self.kernels.repeat_penalty(
-                logits, torch.from_numpy(win).to(self.device), torch.from_numpy(counts).to(self.device),
-                torch.full((n,), float(options.repeat_penalty), dtype=torch.float32, device=self.device), last_n)
+            logits = self._penalised(logits, options, recent)
         params = self._params(options, seeds, draws)
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         self.kernels.sample_rows(logits, params, out)

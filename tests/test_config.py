@@ -71,8 +71,10 @@ def test_registry(tmp_path):
     arch, cfg = load_config(tmp_path)
     assert arch.name == "LlamaForCausalLM" and isinstance(cfg, LlamaConfig)
     layout = arch.layout(cfg)
-    assert len(layout.layers) == 3 and layout.head_name == "lm_head.weight" and layout.stop_ids == (11, 12)
-    assert layout.layers[0].mixer.kind == "attention" and layout.layers[0].feed_forward.kind == "swiglu"
+    assert len(layout.layers) == 3 and layout.stop_ids == (11, 12)
+    assert layout.head.kind == "linear_head" and layout.head.params["weight_name"] == "lm_head.weight" and not layout.head.params["tied"]
+    assert layout.embedding.kind == "token_embedding" and layout.layers[0].arrangement == "pre_norm"
+    assert layout.layers[0].parts["mixer"].kind == "attention" and layout.layers[0].parts["feed_forward"].kind == "swiglu"
     (tmp_path / "config.json").write_text(json.dumps(dict(TINY_B, architectures=["NopeForCausalLM"])))
     with pytest.raises(ConfigError) as e:
         load_config(tmp_path)

@@ -292,3 +292,41 @@ def test_random_model_spec_runs_like_its_folder(tmp_path):
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert [int(t) for t in r.stdout.split()] == llm.generate(d, prompts[0], 10, "greedy", stop_ids=[], dtype="float32")
+
+
+def test_state_record_on_the_device_follows_the_generation(tmp_path, monkeypatch):
+    """Every sequence has a fixed-size record on the device (tokens held, tokens generated, last
+    token, finished flag, sampling key and draw counter) that the sampling kernel reads and
+    advances: a sampled run packs and uploads no parameters per step, and after the run the records
+    hold what the host's bookkeeping says."""
+    from scriptling_llm_lib_b200 import llm
+    from scriptling_llm_lib_b200.cache.store import (SEQ_COUNTER, SEQ_FLAG_FINISHED, SEQ_FLAGS, SEQ_GENERATED, SEQ_KEY,
+                                                     SEQ_LAST_TOKEN, SEQ_POS)
+    from scriptling_llm_lib_b200.sampling.sampler import Sampler
+    raw, seed = TINY["B"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm = plain_model(d)
+    prompts = [random_ids(n, 384, 60 + n) for n in (8, 40, 3)]
+    kw = dict(strategy="top_k", temperature=0.9, top_k=30, repeat_penalty=0.0)
+    free = [plain.generate(pm, p, 14, stop_ids=(), seed=2 ** 33 + 5 + i, **kw) for i, p in enumerate(prompts)]
+    stop = free[1][6]
+    want = [plain.generate(pm, p, 14, stop_ids=(stop,), seed=2 ** 33 + 5 + i, **kw) for i, p in enumerate(prompts)]
+
+    def no_upload(self, options, seeds, draws):
+        raise AssertionError("sampling parameters were packed on the host for a step")
+    monkeypatch.setattr(Sampler, "_params", no_upload)
+    got = llm.generate(d, prompts, 14, "top_k", temperature=0.9, top_k=30, repeat_penalty=0.0, seed=2 ** 33 + 5, stop_ids=[stop],
+                       dtype="float32")
+    assert got == want
+    eng, _ = llm.load(d, "float32")
+    rec = eng.cache.seq_state.cpu().numpy().astype("int64") & 0xFFFFFFFF
+    for slot, (p, out) in enumerate(zip(prompts, got)):                  # one batch: request i ran in slot i
+        r = rec[slot]
+        assert r[SEQ_GENERATED] == len(out) and r[SEQ_LAST_TOKEN] == out[-1]
+        assert r[SEQ_POS] == len(p) + len(out) - 1                       # the last sampled token is not fed back
+        assert bool(r[SEQ_FLAGS] & SEQ_FLAG_FINISHED) == (out[-1] == stop)
+        assert r[SEQ_KEY] == 5 + slot and r[SEQ_KEY + 1] == 2 and r[SEQ_COUNTER] == len(out) and r[SEQ_COUNTER + 1] == 0
+    # a slot that is opened again starts from a zeroed record
+    s = eng.open()
+    assert int(eng.cache.seq_state[s.slot].abs().sum()) == 0
+    s.close()

@@ -219,7 +219,7 @@ def test_gemm_qkv_with_rotation_and_cache_write(kernel_sets, H, G, hd, rot, pair
     tc = kernel_sets[torch.bfloat16].tensor_core
     enc = RotaryEncoding(hd, rot, 54321.0, None, pairing)
     enc.prepare(1024, "cuda")
-    table, r, inter = enc.product_fusion()
+    table, r, inter = enc.rotation()
     lens, pos0 = [150, 70], [60, 300]
     T, K, N = sum(lens), 136, (H + 2 * G) * hd
     a, w = dev(rand(T, K, seed=41), torch.bfloat16), dev(rand(N, K, seed=42, scale=0.1), torch.bfloat16)
@@ -461,7 +461,7 @@ def test_attn_decode_with_rotation_and_cache_write_fused(kernel_sets, H, G, hd, 
     dk = kernel_sets[torch.bfloat16].decode
     enc = RotaryEncoding(hd, rot, 54321.0, None, pairing)
     enc.prepare(1024, "cuda")
-    assert enc.decode_fusion() is not None
+    assert dk.rotation_fusable(rot, pairing == "interleaved")
     pos0 = [0, 63, 64, 700, 257]
     B = len(pos0)
     rnd = lambda t: t.bfloat16().float()

@@ -125,7 +125,7 @@ def register_toy():
     from scriptling_llm_lib_b200.cache import StateNeed
     from scriptling_llm_lib_b200.config import ConfigError, register_architecture
     from scriptling_llm_lib_b200.engine.layout import ModelLayout, sequential_schedule
-    from scriptling_llm_lib_b200.parts import MIXERS, LayerSpec, Linear, Mixer, PartSpec
+    from scriptling_llm_lib_b200.parts import MIXERS, Linear, Mixer, PartSpec, linear_head, pre_norm_layer, token_embedding
 
     class RunningMean(Mixer):
         def __init__(self, hidden, w_name):
@@ -183,10 +183,11 @@ def register_toy():
                                           q_name="l1.q", k_name="l1.k", v_name="l1.v", o_name="l1.o"))
         ffn = lambda i: PartSpec("swiglu", dict(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size,
                                                 gate_name=f"l{i}.gate", up_name=f"l{i}.up", down_name=f"l{i}.down"))
-        layers = (LayerSpec(PartSpec("running_mean", dict(hidden=cfg.hidden_size, w_name="l0.mean")), ffn(0), norm("l0.n1"), norm("l0.n2")),
-                  LayerSpec(attn, ffn(1), norm("l1.n1"), norm("l1.n2")))       # different mixers in different layers
-        return ModelLayout(cfg.vocab_size, cfg.hidden_size, cfg.max_position_embeddings, "embed", layers,
-                           sequential_schedule(2), norm("final"), "head")
+        layers = (pre_norm_layer(PartSpec("running_mean", dict(hidden=cfg.hidden_size, w_name="l0.mean")), ffn(0), norm("l0.n1"), norm("l0.n2")),
+                  pre_norm_layer(attn, ffn(1), norm("l1.n1"), norm("l1.n2")))       # different mixers in different layers
+        return ModelLayout(cfg.vocab_size, cfg.hidden_size, cfg.max_position_embeddings,
+                           token_embedding(cfg.vocab_size, cfg.hidden_size, "embed"), layers, sequential_schedule(2), norm("final"),
+                           linear_head(cfg.vocab_size, cfg.hidden_size, "head"))
 
     register_architecture("ToyMeanForCausalLM", ToyConfig, layout, replace=True)
     return ToyConfig, layout
@@ -303,7 +304,8 @@ def register_routed_toy():
     f_i * log(1 + position) instead of f_i * position (its own table, the library's kernels)."""
     from scriptling_llm_lib_b200.config import ConfigError, register_architecture
     from scriptling_llm_lib_b200.engine.layout import ModelLayout, sequential_schedule
-    from scriptling_llm_lib_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, LayerSpec, Linear, PartSpec, PositionEncoding
+    from scriptling_llm_lib_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, Linear, PartSpec, PositionEncoding,
+                                               linear_head, pre_norm_layer, token_embedding)
     from scriptling_llm_lib_b200.parts.feedforward import SwiGLU
 
     class TopOneExperts(FeedForward):
@@ -346,12 +348,8 @@ def register_routed_toy():
             ang = np.log1p(np.arange(max_positions, dtype=np.float64))[:, None] * inv[None, :]
             self.cos_sin = torch.from_numpy(np.stack([np.cos(ang), np.sin(ang)], -1).astype(np.float32)).to(device)
 
-        def decode_fusion(self):
+        def rotation(self):                      # a rotation by a table of its own: the library's kernels do the rest
             return self.cos_sin, self.head_dim, False
-
-        def apply(self, qkv, ctx, n_heads, n_kv, kpages, vpages, block_table):
-            ctx.kernels.rope_kv_write(qkv, ctx.tok_pos, ctx.tok_seq, block_table, self.cos_sin, kpages, vpages, n_heads, n_kv,
-                                      self.head_dim, self.head_dim, False)
 
     FEED_FORWARDS.register("top_one_experts", TopOneExperts, replace=True)
     POSITION_ENCODINGS.register("log_rotary", LogRotary, replace=True)
@@ -383,10 +381,11 @@ def register_routed_toy():
         dense = PartSpec("swiglu", dict(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size,
                                         gate_name="l0.gate", up_name="l0.up", down_name="l0.down"))
         routed = PartSpec("top_one_experts", dict(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size, n_experts=3, prefix="l1."))
-        layers = (LayerSpec(attn(0), dense, norm("l0.n1"), norm("l0.n2")),
-                  LayerSpec(attn(1), routed, norm("l1.n1"), norm("l1.n2")))      # different feed-forwards in different layers
-        return ModelLayout(cfg.vocab_size, cfg.hidden_size, cfg.max_position_embeddings, "embed", layers,
-                           sequential_schedule(2), norm("final"), "head")
+        layers = (pre_norm_layer(attn(0), dense, norm("l0.n1"), norm("l0.n2")),
+                  pre_norm_layer(attn(1), routed, norm("l1.n1"), norm("l1.n2")))      # different feed-forwards in different layers
+        return ModelLayout(cfg.vocab_size, cfg.hidden_size, cfg.max_position_embeddings,
+                           token_embedding(cfg.vocab_size, cfg.hidden_size, "embed"), layers, sequential_schedule(2), norm("final"),
+                           linear_head(cfg.vocab_size, cfg.hidden_size, "head"))
 
     register_architecture("ToyRoutedForCausalLM", RoutedConfig, layout, replace=True)
     return RoutedConfig, layout
@@ -472,3 +471,161 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
     for i in range(3):
         assert rel_err(torch.cat(got[i]), want[i]) < tol, f"request {i}"
     assert min(margins) > 0.05                                       # no routing decision hung on rounding
+
+
+# --------------------------------------------------------------------------- another architecture's surroundings
+def register_capped_toy():
+    """What another architecture could bring without a change to the library, all defined here: an
+    embedding scaled by sqrt(hidden), a head whose logits are capped (cap * tanh(logit / cap)) and
+    that is tied to the embedding, a block of one mixer and no feed-forward ("mixer_only"), a layer
+    whose attention has no position encoding at all, and a position encoding that is no rotation
+    (it adds position * slope to the first dimension of every query and key head, in place)."""
+    import math
+    from scriptling_llm_lib_b200.config import ConfigError, register_architecture
+    from scriptling_llm_lib_b200.engine.layout import ModelLayout, sequential_schedule
+    from scriptling_llm_lib_b200.parts import (ARRANGEMENTS, EMBEDDINGS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, LayerSpec,
+                                               OutputHead, PartSpec, PositionEncoding, TokenEmbedding, pre_norm_layer)
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, ids, ctx):
+            return super().forward(ids, ctx) * math.sqrt(self.width)
+
+    class CappedHead(OutputHead):
+        def __init__(self, cap, **kw):
+            super().__init__(**kw)
+            self.cap = cap
+
+        def forward(self, normed, ctx):
+            return self.cap * torch.tanh(super().forward(normed, ctx) / self.cap)
+
+    class MixerOnlyBlock(Block):
+        """x += mixer(norm(x)); nothing else."""
+
+        def __init__(self, spec):
+            self.norm = NORMS.build(spec.parts["norm"])
+            self.mixer = MIXERS.build(spec.parts["mixer"])
+
+        def parts(self):
+            return [self.norm, self.mixer]
+
+        def forward(self, residual, delta, ctx, unit, writes):
+            return self.mixer.forward(self.norm.forward(residual, delta, ctx), ctx, unit, writes)
+
+    class FirstDimRamp(PositionEncoding):
+        graph_safe = True
+
+        def __init__(self, slope):
+            self.slope = slope
+
+        def transform(self, qkv, ctx, n_heads, n_kv_heads, head_dim):
+            ramp = (ctx.tok_pos.to(torch.float32) * self.slope).to(qkv.dtype)
+            cols = torch.arange(n_heads + n_kv_heads, device=qkv.device) * head_dim
+            qkv[:, cols] = (qkv[:, cols].float() + ramp.float()[:, None]).to(qkv.dtype)
+
+    EMBEDDINGS.register("scaled_embedding", ScaledEmbedding, replace=True)
+    HEADS.register("capped_head", CappedHead, replace=True)
+    ARRANGEMENTS.register("mixer_only", MixerOnlyBlock, replace=True)
+    POSITION_ENCODINGS.register("first_dim_ramp", FirstDimRamp, replace=True)
+
+    @dataclass(frozen=True)
+    class CappedConfig:
+        hidden_size: int
+        vocab_size: int
+        intermediate_size: int
+        max_position_embeddings: int
+
+        @classmethod
+        def from_dict(cls, raw, where="config.json"):
+            try:
+                return cls(raw["hidden_size"], raw["vocab_size"], raw["intermediate_size"], raw["max_position_embeddings"])
+            except KeyError as e:
+                raise ConfigError(f"{where}: required key {e} is missing") from None
+
+        def to_json_dict(self):
+            return {"architectures": ["ToyCappedForCausalLM"], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                    "intermediate_size": self.intermediate_size, "max_position_embeddings": self.max_position_embeddings}
+
+    def layout(cfg):
+        def norm(name):
+            return PartSpec("rmsnorm", dict(width=cfg.hidden_size, eps=1e-5, weight_name=name))
+        attn = lambda i, pos: PartSpec("attention", dict(hidden=cfg.hidden_size, n_heads=4, n_kv_heads=2, head_dim=16, position=pos,
+                                                         q_name=f"l{i}.q", k_name=f"l{i}.k", v_name=f"l{i}.v", o_name=f"l{i}.o"))
+        ffn = PartSpec("swiglu", dict(hidden=cfg.hidden_size, intermediate=cfg.intermediate_size,
+                                      gate_name="l1.gate", up_name="l1.up", down_name="l1.down"))
+        layers = (LayerSpec("mixer_only", dict(norm=norm("l0.n"), mixer=attn(0, None))),                   # no positions, no feed-forward
+                  pre_norm_layer(attn(1, PartSpec("first_dim_ramp", dict(slope=0.05))), ffn, norm("l1.n1"), norm("l1.n2")))
+        return ModelLayout(cfg.vocab_size, cfg.hidden_size, cfg.max_position_embeddings,
+                           PartSpec("scaled_embedding", dict(vocab=cfg.vocab_size, width=cfg.hidden_size, name="embed")), layers,
+                           sequential_schedule(2), norm("final"),
+                           PartSpec("capped_head", dict(cap=3.0, vocab=cfg.vocab_size, width=cfg.hidden_size, weight_name="embed", tied=True)))
+
+    register_architecture("ToyCappedForCausalLM", CappedConfig, layout, replace=True)
+    return CappedConfig, layout
+
+
+def capped_plain_logits(w, ids, hidden, act_round):
+    S = len(ids)
+    pos = torch.arange(S)
+    x = w["embed"][torch.as_tensor(ids)] * (hidden ** 0.5)
+
+    def attn(i, n, ramp):
+        q = act_round(plain.linear(n, w[f"l{i}.q"])).view(S, 4, 16).clone()
+        k = act_round(plain.linear(n, w[f"l{i}.k"])).view(S, 2, 16).clone()
+        v = act_round(plain.linear(n, w[f"l{i}.v"])).view(S, 2, 16)
+        if ramp:
+            r = act_round((pos.to(torch.float32) * 0.05).to(torch.float64))
+            q[:, :, 0] = act_round(q[:, :, 0] + r[:, None])
+            k[:, :, 0] = act_round(k[:, :, 0] + r[:, None])
+        return plain.linear(act_round(plain.attention(q, k, v, pos, pos).reshape(S, 64)), w[f"l{i}.o"])
+
+    x = x + attn(0, act_round(plain.rms_norm(x, w["l0.n"], 1e-5)), False)
+    x = x + attn(1, act_round(plain.rms_norm(x, w["l1.n1"], 1e-5)), True)
+    n = act_round(plain.rms_norm(x, w["l1.n2"], 1e-5))
+    x = x + plain.linear(act_round(plain.swiglu(plain.linear(n, w["l1.gate"]), plain.linear(n, w["l1.up"]))), w["l1.down"])
+    return 3.0 * torch.tanh(plain.linear(act_round(plain.rms_norm(x, w["final"], 1e-5)), w["embed"]) / 3.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_its_own_embedding_head_block_and_positions(tmp_path, dtype):
+    from scriptling_llm_lib_b200.engine.model import DecoderModel
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    from scriptling_llm_lib_b200.weights import write_random_model
+    CappedConfig, layout = register_capped_toy()
+    cfg = CappedConfig(hidden_size=48, vocab_size=83, intermediate_size=56, max_position_embeddings=256)
+    model = DecoderModel(layout(cfg))
+    names = [s.name for s in model.tensor_specs()]
+    assert names.count("embed") == 1 and "head" not in names           # the tied head asks for nothing of its own
+    assert model.elements_read_per_step() == sum(int(np.prod(s.shape)) for s in model.tensor_specs())   # table counted once, as the head
+    d = write_random_model(cfg, model.tensor_specs(), 5, tmp_path / "capped")
+    eng = Engine.from_folder(d, dtype, max_tokens=1024, max_seqs=3)
+    assert eng.use_graphs and len(eng.cache.groups) == 1 and eng.cache.groups[0].units == [0, 1]
+    w = plain.read_safetensors(d / "model.safetensors")
+    act_round = (lambda t: t) if dtype == "float32" else (lambda t: t.to(torch.float32).to(torch.bfloat16).to(torch.float64))
+    reqs = [random_ids(n, 83, 830 + n) for n in (70, 9, 33)]
+    want = [capped_plain_logits(w, r, 48, act_round) for r in reqs]
+    tol = TOL[dtype]
+    for r, wl in zip(reqs, want):                                       # whole
+        s = eng.open()
+        assert rel_err(f64(eng.step([StepEntry(s, r, list(range(len(r))))])), wl) < tol
+        s.close()
+    seqs = [eng.open() for _ in reqs]                                   # unequal prompts, then one by one (captured steps)
+    plens = [40, 9, 1]
+    got = {i: [] for i in range(3)}
+    out = eng.step([StepEntry(s, reqs[i][:plens[i]], list(range(plens[i]))) for i, s in enumerate(seqs)])
+    off = 0
+    for i in range(3):
+        got[i].append(f64(out[off:off + plens[i]]))
+        off += plens[i]
+    pos = dict(enumerate(plens))
+    live = {i: s for i, s in enumerate(seqs) if pos[i] < len(reqs[i])}
+    while live:
+        order = sorted(live)
+        out = eng.step([StepEntry(live[i], [reqs[i][pos[i]]], [0]) for i in order])
+        for j, i in enumerate(order):
+            got[i].append(f64(out[j:j + 1]))
+            pos[i] += 1
+            if pos[i] == len(reqs[i]):
+                live.pop(i).close()
+    for i in range(3):
+        assert rel_err(torch.cat(got[i]), want[i]) < tol, f"request {i}"
+    assert float(torch.cat(got[0]).abs().max()) <= 3.0                  # the cap holds
