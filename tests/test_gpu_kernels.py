@@ -374,7 +374,7 @@ def test_attn_paged(kernel_sets, dtype, H, G, hd, window):
     # like sqrt(head_dim) (2e-6 holds up to a width of 64)
     assert rel_err(out.cpu().float(), want) < TOL[dtype] * (max(1.0, math.sqrt(hd / 64)) if dtype == torch.float32 else 1.0)
     # few new rows per sequence: the one-query-at-a-time form of the kernel
-    lens2 = [1, 3, 2, 4]
+    lens2 = [3, 1, 2, 4]
     qs2 = [t[:n] for t, n in zip(qs, lens2)]
     kp2, vp2, bt2 = paged([k[:p + n] for k, p, n in zip(kk, pos0, lens2)], [v[:p + n] for v, p, n in zip(vv, pos0, lens2)],
                           [p + n for p, n in zip(pos0, lens2)], dtype=dtype, seed=5)
