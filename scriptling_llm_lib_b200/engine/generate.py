@@ -141,8 +141,11 @@ class Generator:
             try:
                 t_ev[0].record()
                 live = state.live()
-                logits = eng.step([StepEntry(seqs[i], state.seqs[i].prompt) for i in live])
-                index = eng.last_step if on_device_state else None
+                if hasattr(eng, "prompt_step"):          # long batches of prompts go through in portions
+                    logits, index = eng.prompt_step([StepEntry(seqs[i], state.seqs[i].prompt) for i in live])
+                else:
+                    logits = eng.step([StepEntry(seqs[i], state.seqs[i].prompt) for i in live])
+                    index = eng.last_step if on_device_state else None
                 fed = [len(state.seqs[i].prompt) for i in live]
                 step_no = 0
                 # When the engine replays its decode step, the next step is launched with the sampled ids

@@ -57,7 +57,7 @@ class DecodeGraph:
         from ..csrc import bindings
         before = bindings.LAUNCHES[0]
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, pool=engine.decode_graphs.pool):
             self.logits = engine._forward(ctx, want=True)
         self.kernels_per_replay = bindings.LAUNCHES[0] - before
 
@@ -127,11 +127,16 @@ class DecodeGraph:
 
 
 class DecodeGraphs:
-    """The graphs of one engine, captured on first use."""
+    """The graphs of one engine, captured on first use. They share one memory pool (their replays
+    never overlap: one stream, one step after another), so a graph's buffers, its logits included,
+    hold a step's values only until the next replay of any of them. At most MAX_GRAPHS are kept;
+    the one replayed longest ago goes first."""
+    MAX_GRAPHS = 48
 
     def __init__(self, engine):
         self.engine = engine
         self.graphs: dict[tuple[int, int], DecodeGraph] = {}
+        self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
         self.last_index = None
         self.last_graph: DecodeGraph | None = None
 
@@ -144,9 +149,12 @@ class DecodeGraphs:
         width = min(max(8, _next_pow2(need)), max(cap, need))
         batch = _next_pow2(ids.shape[0] if isinstance(ids, torch.Tensor) else len(ids))
         key = (batch, width)
-        g = self.graphs.get(key)
+        g = self.graphs.pop(key, None)
         if g is None:
-            g = self.graphs[key] = DecodeGraph(self.engine, batch, width)
+            while len(self.graphs) >= self.MAX_GRAPHS:
+                self.graphs.pop(next(iter(self.graphs)))          # the dict is kept in order of last use
+            g = DecodeGraph(self.engine, batch, width)
+        self.graphs[key] = g
         out = g.run(ids, pos0, slots, tables)
         self.last_graph, self.last_index = g, g.index(out.shape[0])
         return out

@@ -270,8 +270,11 @@ class Engine:
             tables = [self.cache.block_table(g, slots) for g in range(len(self.cache.groups))]
             logits = self.decode_graphs.run(ids, pos0, slots, tables)
             self.last_step = self.decode_graphs.last_index
+            # the captured step's own buffer is overwritten by the next replay: the caller gets a copy
             if want_rows != list(range(B)):
                 logits = logits[torch.as_tensor(want_rows, dtype=torch.long, device=self.device)] if want_rows else None
+            else:
+                logits = logits.clone()
         else:
             ctx = self._context(entries, ids, lens, pos0, want_rows)
             self.last_step = StepIndex(ctx.slots, ctx.seq_pos_after)
@@ -280,6 +283,55 @@ class Engine:
                 self.check_errors()
         self.cache.advance(growth)
         return logits if logits is not None else torch.empty((0, V), dtype=torch.float32, device=self.device)
+
+    PROMPT_TOKENS_PER_STEP = 16384     # a prompt step's activations grow with its rows: longer batches go in portions
+
+    def prompt_step(self, entries: list[StepEntry], max_tokens_per_step: int | None = None):
+        """Whole prompts (or any token runs) of several sequences, in as many steps as it takes to keep
+        each step at `max_tokens_per_step` rows or fewer: a sequence's run is cut into portions, each
+        landing on what the portions before left in the cache. Returns the float32 logits of every
+        entry's last token, [entries, vocab], and the StepIndex of those rows (for the sampler). The
+        numbers are those of one big step, beyond rounding: a row sees its own sequence's keys only."""
+        budget = max_tokens_per_step or self.PROMPT_TOKENS_PER_STEP
+        if budget < 1:
+            raise StepError("a step needs room for at least one token")
+        if sum(len(e.tokens) for e in entries) <= budget:
+            logits = self.step([StepEntry(e.sequence, e.tokens) for e in entries])
+            return logits, self.last_step
+        rows: list[torch.Tensor | None] = [None] * len(entries)
+        done = [0] * len(entries)
+        nxt = 0
+        while nxt < len(entries):
+            step, room, finishing = [], budget, []
+            i = nxt
+            while i < len(entries) and room > 0:
+                toks = entries[i].tokens
+                take = min(room, len(toks) - done[i])
+                last = done[i] + take == len(toks)
+                step.append(StepEntry(entries[i].sequence, toks[done[i]:done[i] + take], [take - 1] if last else []))
+                done[i] += take
+                room -= take
+                if last:
+                    finishing.append(i)
+                    i += 1
+                else:
+                    break
+            out = self.step(step)
+            for j, k in enumerate(finishing):
+                rows[k] = out[j:j + 1]
+            nxt = i
+        slots = torch.tensor([e.sequence.slot for e in entries], dtype=torch.int32)
+        held = torch.tensor([e.sequence.length for e in entries], dtype=torch.int32)
+        both = torch.stack([slots, held]).pin_memory().to(self.device, non_blocking=True)
+        self.last_step = StepIndex(both[0], both[1])
+        return torch.cat(rows), self.last_step
+
+    def activation_reserve_bytes(self) -> int:
+        """A generous bound on what a prompt step of PROMPT_TOKENS_PER_STEP rows allocates beside
+        weights and cache (residual, products' outputs), plus the logits of the captured decode steps:
+        what the cache must leave free."""
+        width = 64 * self.layout.hidden_size                        # bytes a row, all buffers of a layer alive at once
+        return self.PROMPT_TOKENS_PER_STEP * width + 4 * self.layout.vocab_size * 4 * 1024
 
     def check_errors(self) -> None:
         """Raises if a kernel of an earlier step reported an error (a wait on the device that ran out
@@ -294,7 +346,9 @@ class Engine:
     def decode_step_device(self, sequences: list[Sequence], ids: torch.Tensor) -> torch.Tensor:
         """One token for each of `sequences`, the ids taken from an int32 device tensor (what the
         sampler just wrote), logits of every row back. Lets a caller launch the next step before it
-        has read the last step's tokens. Only for engines that replay their decode step."""
+        has read the last step's tokens. Only for engines that replay their decode step. The logits
+        are the captured step's own buffer: they hold until the next decode step is launched (sample
+        from them first, as the generation loop does, or copy them)."""
         if not self.use_graphs:
             raise StepError("this engine does not replay its decode step; feed token ids from the host")
         if ids.dtype != torch.int32 or ids.device != self.device or ids.shape[0] != len(sequences):

@@ -59,7 +59,8 @@ def _fit_cache(eng: Engine, prompts, max_tokens, max_batch):
         return
     free, _ = torch.cuda.mem_get_info(eng.device)
     have = eng.cache.n_pages * eng.bytes_per_page()
-    afford = int((free + have) * 0.85) // max(1, eng.bytes_per_page())
+    # what a prompt step's activations and the captured decode steps need stays free
+    afford = max(0, int((free + have - eng.activation_reserve_bytes()) * 0.9)) // max(1, eng.bytes_per_page())
     n_pages = max(max(pages), min(want_pages, afford), eng.cache.n_pages)
     eng.resize_cache(n_pages * PAGE, max(want_seqs, eng.cache.n_slots))
 

@@ -330,3 +330,34 @@ def test_state_record_on_the_device_follows_the_generation(tmp_path, monkeypatch
     s = eng.open()
     assert int(eng.cache.seq_state[s.slot].abs().sum()) == 0
     s.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_batches_of_prompts_go_through_in_portions(tmp_path, dtype):
+    """The generation loop keeps a prompt step under a number of rows: with room for 64 rows a step,
+    prompts of 120, 30, 75 and 200 tokens take seven steps, each portion landing on what the ones
+    before left in the cache; logits of the last places and generated tokens are those of one step."""
+    from scriptling_llm_lib_b200 import llm
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    raw, seed = TINY["D"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    pm, pm16 = plain_model(d), plain_model_bf16(d)
+    prompts = [random_ids(n, raw["vocab_size"], 640 + n) for n in (120, 30, 75, 200)]
+    eng = Engine.from_folder(d, dtype, max_tokens=1024, max_seqs=4)
+    seqs = [eng.open() for _ in prompts]
+    steps_before = []
+    orig_step = eng.step
+    eng.step = lambda entries: (steps_before.append(sum(len(e.tokens) for e in entries)), orig_step(entries))[1]
+    logits, index = eng.prompt_step([StepEntry(s, p) for s, p in zip(seqs, prompts)], max_tokens_per_step=64)
+    assert steps_before == [64, 64, 64, 64, 64, 64, 41] and index.slots.tolist() == [s.slot for s in seqs]
+    assert index.pos_after.tolist() == [len(p) for p in prompts] == [s.length for s in seqs]
+    for i, p in enumerate(prompts):
+        check_logits(logits[i:i + 1].cpu().double(), pm.logits(p)[-1:], pm16.logits(p)[-1:], dtype, f"prompt {i} in portions")
+    MEASURED.clear()
+    for s in seqs:
+        s.close()
+    if dtype == "float32":
+        gen_eng, _ = llm.load(d, "float32")
+        gen_eng.PROMPT_TOKENS_PER_STEP = 64
+        got = llm.generate(d, prompts, 6, "greedy", stop_ids=[], dtype="float32")
+        assert got == [plain.generate(pm, p, 6, stop_ids=()) for p in prompts]
