@@ -2,7 +2,12 @@
 // (bfloat16, head width 64 or 128; a head of 128 is two 64-wide swizzled blocks side by side in
 // shared memory for Q, K and V alike, and O takes 128 columns of tensor memory).
 //
-// One block: 128 consecutive queries of one sequence and one query head. Warp 0 fetches the query
+// One work item: 128 consecutive queries of one sequence and one query head. The grid is two blocks
+// per SM that stay; items are numbered longest first (heads fastest, a sequence's query tiles from
+// the last to the first) and dealt to the blocks in rows that run forth and back (block k takes
+// items k, 2G-1-k, 2G+k, ... of G blocks), so that a block's long items are paired with short ones
+// and every block ends at about the same time; barriers, tensor memory and the key/value ring live
+// across a block's items. Warp 0 fetches the query
 // tile and, page by page, the keys and values of the sequence with TMA (128-byte swizzle, no
 // multicast) -- the pages are found through the block table, this step's own keys were written
 // to the cache before. Warp 1 issues the products from one thread: S = Q K^T (128 x 64, float, in
@@ -33,7 +38,37 @@ struct FtArgs {
   int H, G, window;
   float scale;
   int* err;
+  int n_qt, n_items;    // query tiles per sequence (of the longest), work items = H * n_qt * sequences
 };
+
+// What a block works on in its r-th round.
+struct FtItem {
+  int b, h, g, row0, r0, nq, pos0, t_lo, t_hi, n_tiles, q_hi;
+  bool valid;           // false: past the end of a shorter sequence -- nothing to do
+};
+__device__ __forceinline__ bool ft_item(const FtArgs& p, int round, FtItem& it) {
+  int G = gridDim.x;
+  int idx = round * G + ((round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  if (idx >= p.n_items) return false;
+  it.h = idx % p.H;
+  int rest = idx / p.H;
+  int qt = p.n_qt - 1 - rest % p.n_qt;
+  it.b = rest / p.n_qt;
+  it.row0 = p.seq_start[it.b];
+  int S = p.seq_start[it.b + 1] - it.row0;
+  it.r0 = qt * FT_BQ;
+  it.valid = it.r0 < S;
+  it.nq = min(FT_BQ, S - it.r0);
+  it.pos0 = p.seq_pos0[it.b];
+  it.g = it.h / (p.H / p.G);
+  int q_lo = it.pos0 + it.r0;
+  it.q_hi = it.pos0 + it.r0 + it.nq - 1;
+  int k_first = p.window > 0 ? max(0, q_lo - p.window + 1) : 0;
+  it.t_lo = k_first / FT_BK;
+  it.t_hi = it.q_hi / FT_BK;
+  it.n_tiles = it.t_hi - it.t_lo + 1;
+  return true;
+}
 
 __device__ __forceinline__ float ft_ex2(float x) {
   float y;
@@ -56,31 +91,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // [Q][P][K stages][V stages][barriers]
   const uint32_t sQ = smem_u32(smem), sP = sQ + Q_BYTES, sK = sP + P_BYTES, sV = sK + FT_STAGES * KV_BYTES;
   uint64_t* bars = (uint64_t*)(smem + Q_BYTES + P_BYTES + 2 * FT_STAGES * KV_BYTES);
-  // q_full, kv_full[ST], kv_empty[ST], s_full[2], s_empty[2], p_full, p_empty, o_full
+  // q_full, kv_full[ST], kv_empty[ST], s_full[2], s_empty[2], p_full, p_empty, o_full, q_empty
   const uint32_t b_qfull = smem_u32(bars), b_kvfull = b_qfull + 8, b_kvempty = b_kvfull + 8 * FT_STAGES,
                  b_sfull = b_kvempty + 8 * FT_STAGES, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16, b_pempty = b_pfull + 8,
-                 b_ofull = b_pempty + 8;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 1 + 1 + 1);
+                 b_ofull = b_pempty + 8, b_qempty = b_ofull + 8;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 1 + 1 + 1 + 1);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
   if ((uint8_t*)(abort + 1) > smem_raw + smem_bytes) {      // the 1 KB alignment took more than the launch left room for
     if (threadIdx.x == 0) atomicExch(p.err, 3);
     return;
   }
 
-  // heads vary fastest, query tiles from the last (most keys) to the first: blocks start in the order
-  // of their length over the whole grid, so the long ones are not left for the end
-  int b = blockIdx.z, h = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
-  int row0 = p.seq_start[b], S = p.seq_start[b + 1] - row0;
-  int r0 = qt * FT_BQ;
-  if (r0 >= S) return;
-  int nq = min(FT_BQ, S - r0);
-  int pos0 = p.seq_pos0[b];
-  int g = h / (p.H / p.G);
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int* bt = p.block_table + (size_t)b * p.max_pages;
-  int q_lo = pos0 + r0, q_hi = pos0 + r0 + nq - 1;
-  int k_first = p.window > 0 ? max(0, q_lo - p.window + 1) : 0;
-  int t_lo = k_first / FT_BK, t_hi = q_hi / FT_BK, n_tiles = t_hi - t_lo + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
@@ -89,6 +111,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(b_pfull, 4);
     mbar_init(b_pempty, 1);
     mbar_init(b_ofull, 1);
+    mbar_init(b_qempty, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -102,75 +125,102 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;          // columns: S0 0-63, S1 64-127, O from 128 (one column per dim)
 
+  // Every role walks the same items in the same order and counts tiles (J) and items (I) by itself; a
+  // barrier's phase follows from those counts, so nothing is set up again between items.
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(b_qfull, Q_BYTES);
+      int J = 0, I = 0;
+      FtItem it;
+      bool ok = true;
+      for (int round = 0; ok && ft_item(p, round, it); round++) {
+        if (!it.valid) continue;
+        const int* bt = p.block_table + (size_t)it.b * p.max_pages;
+        // the products of the last item that read Q are done
+        if (!mbar_wait(b_qempty, (I & 1) ^ 1, abort)) break;
+        mbar_expect_tx(b_qfull, Q_BYTES);
 #pragma unroll
-      for (int a = 0; a < NA; a++) tma_load_2d(sQ + a * QA, &map_q, h * FT_HD + 64 * a, row0 + r0, b_qfull);
-      int issued = 0;
-      for (int j = 0; j < n_tiles; j++) {
-        int s = j % FT_STAGES;
-        if (!mbar_wait(b_kvempty + 8 * s, ((j / FT_STAGES) & 1) ^ 1, abort)) break;
-        int page = bt[t_lo + j];
-        int krow = (page * p.G + g) * FT_BK;
-        mbar_expect_tx(b_kvfull + 8 * s, 2 * KV_BYTES);
+        for (int a = 0; a < NA; a++) tma_load_2d(sQ + a * QA, &map_q, it.h * FT_HD + 64 * a, it.row0 + it.r0, b_qfull);
+        I++;
+        for (int j = 0; j < it.n_tiles; j++) {
+          int s = J % FT_STAGES;
+          if (!mbar_wait(b_kvempty + 8 * s, ((J / FT_STAGES) & 1) ^ 1, abort)) { ok = false; break; }
+          int page = bt[it.t_lo + j];
+          int krow = (page * p.G + it.g) * FT_BK;
+          mbar_expect_tx(b_kvfull + 8 * s, 2 * KV_BYTES);
 #pragma unroll
-        for (int a = 0; a < NA; a++) {
-          tma_load_2d(sK + s * KV_BYTES + a * KA, &map_k, 64 * a, krow, b_kvfull + 8 * s);
-          tma_load_2d(sV + s * KV_BYTES + a * KA, &map_v, 64 * a, krow, b_kvfull + 8 * s);
+          for (int a = 0; a < NA; a++) {
+            tma_load_2d(sK + s * KV_BYTES + a * KA, &map_k, 64 * a, krow, b_kvfull + 8 * s);
+            tma_load_2d(sV + s * KV_BYTES + a * KA, &map_v, 64 * a, krow, b_kvfull + 8 * s);
+          }
+          J++;
         }
-        issued = j + 1;
       }
-      if (*abort) {
+      if (*abort) {            // let the copies that are under way land before the block leaves
         volatile int never = 0;
-        mbar_wait(b_qfull, 0, &never);
-        for (int j = max(0, issued - FT_STAGES); j < issued; j++) mbar_wait(b_kvfull + 8 * (j % FT_STAGES), (j / FT_STAGES) & 1, &never);
+        if (I > 0) mbar_wait(b_qfull, (I - 1) & 1, &never);
+        for (int j = max(0, J - FT_STAGES); j < J; j++) mbar_wait(b_kvfull + 8 * (j % FT_STAGES), (j / FT_STAGES) & 1, &never);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(FT_BQ, FT_BK);          // S = Q K^T: both K-major
       constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(FT_BQ, FT_HD);      // O = P V: V is MN-major (dims contiguous)
-      bool ok = mbar_wait(b_qfull, 0, abort);
-      auto issue_s = [&](int j) -> bool {
-        int s = j % FT_STAGES, a = j & 1;
-        if (!mbar_wait(b_kvfull + 8 * s, (j / FT_STAGES) & 1, abort)) return false;
-        if (!mbar_wait(b_sempty + 8 * a, ((j >> 1) & 1) ^ 1, abort)) return false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      int J0 = 0, I = 0;
+      FtItem it;
+      bool ok = true;
+      for (int round = 0; ok && ft_item(p, round, it); round++) {
+        if (!it.valid) continue;
+        const int n_tiles = it.n_tiles;
+        ok = mbar_wait(b_qfull, I & 1, abort);
+        I++;
+        auto issue_s = [&](int j) -> bool {
+          int Jg = J0 + j, s = Jg % FT_STAGES, a = Jg & 1;
+          if (!mbar_wait(b_kvfull + 8 * s, (Jg / FT_STAGES) & 1, abort)) return false;
+          if (!mbar_wait(b_sempty + 8 * a, ((Jg >> 1) & 1) ^ 1, abort)) return false;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int k = 0; k < FT_HD / 16; k++)      // 16 dims a step: four steps in each 64-wide block
-          umma_bf16(tmem_base + a * 64, umma_desc_sw128(sQ + (k >> 2) * QA + (k & 3) * 32),
-                    umma_desc_sw128(sK + s * KV_BYTES + (k >> 2) * KA + (k & 3) * 32), idesc_s, k ? 1u : 0u);
-        umma_commit(b_sfull + 8 * a);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_tiles && ok; j++) {
-        if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
-        int s = j % FT_STAGES;
-        ok = mbar_wait(b_pfull, j & 1, abort);        // P of tile j is written, and O has been rescaled if it had to be
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          for (int k = 0; k < FT_HD / 16; k++)      // 16 dims a step: four steps in each 64-wide block
+            umma_bf16(tmem_base + a * 64, umma_desc_sw128(sQ + (k >> 2) * QA + (k & 3) * 32),
+                      umma_desc_sw128(sK + s * KV_BYTES + (k >> 2) * KA + (k & 3) * 32), idesc_s, k ? 1u : 0u);
+          umma_commit(b_sfull + 8 * a);
+          if (j == n_tiles - 1) umma_commit(b_qempty);     // the item's last product that reads Q
+          return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < n_tiles && ok; j++) {
+          if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
+          int Jg = J0 + j, s = Jg % FT_STAGES;
+          ok = mbar_wait(b_pfull, Jg & 1, abort);       // P of tile j is written, and O has been rescaled if it had to be
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int k = 0; k < FT_BK / 16; k++)
-          umma_bf16(tmem_base + 128, umma_desc_sw128(sP + k * 32), umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, NA > 1 ? KA : 0),
-                    idesc_o, (j | k) ? 1u : 0u);
-        umma_commit(b_ofull);
-        umma_commit(b_kvempty + 8 * s);
-        umma_commit(b_pempty);
+          for (int k = 0; k < FT_BK / 16; k++)
+            umma_bf16(tmem_base + 128, umma_desc_sw128(sP + k * 32), umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, NA > 1 ? KA : 0),
+                      idesc_o, (j | k) ? 1u : 0u);
+          umma_commit(b_ofull);
+          umma_commit(b_kvempty + 8 * s);
+          umma_commit(b_pempty);
+        }
+        J0 += n_tiles;
       }
     }
   } else {
     const int q = warp & 3;                        // tensor-memory quarter of this warp
     const int r = q * 32 + lane;                   // query row of this thread in the tile
-    const int qpos = pos0 + r0 + r;
     const float sc = p.scale * FT_LOG2E;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    float m_ref = -INFINITY, l = 0.f;              // reference maximum (raw score units) and sum relative to it
+    int J0 = 0;
+    FtItem it;
     bool ok = true;
+    for (int round = 0; ok && ft_item(p, round, it); round++) {
+    if (!it.valid) continue;
+    const int n_tiles = it.n_tiles, t_lo = it.t_lo, t_hi = it.t_hi, q_hi = it.q_hi, nq = it.nq, row0 = it.row0, r0 = it.r0, h = it.h;
+    const int qpos = it.pos0 + r0 + r;
+    float m_ref = -INFINITY, l = 0.f;              // reference maximum (raw score units) and sum relative to it
     for (int j = 0; j < n_tiles && ok; j++) {
-      int a = j & 1, t = t_lo + j;
-      ok = mbar_wait(b_sfull + 8 * a, (j >> 1) & 1, abort);
+      const int Jg = J0 + j;
+      int a = Jg & 1, t = t_lo + j;
+      ok = mbar_wait(b_sfull + 8 * a, (Jg >> 1) & 1, abort);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t s0[32], s1[32];
@@ -205,7 +255,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float factor = grow ? ((m_ref == -INFINITY) ? 0.f : ft_ex2((m_ref - mx) * sc)) : 1.f;
         if (j >= 1) {
           // O holds the products of tiles 0..j-1: they must be complete before it is rewritten
-          ok = mbar_wait(b_ofull, (j - 1) & 1, abort);
+          ok = mbar_wait(b_ofull, (Jg - 1) & 1, abort);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           uint32_t v[32];
@@ -238,13 +288,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       l += rsa + rsb;
       // ---- P into shared memory (the MMA must have finished reading the previous P)
-      ok = mbar_wait(b_pempty, (j & 1) ^ 1, abort);
+      ok = mbar_wait(b_pempty, (Jg & 1) ^ 1, abort);
       if (!ok) break;
       if (t == t_hi) {
         // keys of the last page beyond the last query's position hold whatever the page held before:
         // their probabilities are zero, but 0 * NaN is NaN, so their value rows are cleared
-        int s = j % FT_STAGES, n_valid = q_hi + 1 - t * FT_BK;
-        ok = mbar_wait(b_kvfull + 8 * s, (j / FT_STAGES) & 1, abort);
+        int s = Jg % FT_STAGES, n_valid = q_hi + 1 - t * FT_BK;
+        ok = mbar_wait(b_kvfull + 8 * s, (Jg / FT_STAGES) & 1, abort);
         if (!ok) break;
         for (int e = (warp - 2) * 32 + lane; e < (FT_BK - n_valid) * 8 * NA; e += 128) {
           int a = e / ((FT_BK - n_valid) * 8), e1 = e % ((FT_BK - n_valid) * 8);
@@ -262,7 +312,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(b_pfull);
     }
-    if (ok) ok = mbar_wait(b_ofull, (n_tiles - 1) & 1, abort);
+    if (ok) ok = mbar_wait(b_ofull, (J0 + n_tiles - 1) & 1, abort);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float inv = l > 0.f ? 1.f / l : 0.f;
@@ -285,6 +335,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       }
+    }
+    // the rows of O are read (the loads above were waited for) before this thread signals the next item's first P
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    J0 += n_tiles;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -330,7 +384,17 @@ SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* 
   if (rc) return rc;
   rc = tc_make_map(&mv, vpages, (int)kv_rows, hd, hd, FT_BK);
   if (rc) return rc;
-  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err};
-  dim3 grid(H, (max_new + FT_BQ - 1) / FT_BQ, B);
+  int n_qt = (max_new + FT_BQ - 1) / FT_BQ;
+  long long n_items = (long long)H * n_qt * B;
+  if (n_items > 0x7fffffffLL) return SLLM_ERR_ARG;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+  }
+  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, (int)n_items};
+  dim3 grid((unsigned)(n_items < 2LL * sm_count ? n_items : 2LL * sm_count));     // two blocks per SM that stay
   return hd == 64 ? ft_launch<64, 3>(mq, mk, mv, a, grid, stream) : ft_launch<128, 2>(mq, mk, mv, a, grid, stream);
 }
