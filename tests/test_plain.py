@@ -131,3 +131,62 @@ def test_generate_semantics(tmp_path):
     assert t1 == plain.generate(m, prompt, 8, "temperature", temperature=0.8, seed=5)
     assert t1 != plain.generate(m, prompt, 8, "temperature", temperature=0.8, seed=6)
     assert plain.generate(m, prompt, 6, "temperature", temperature=0.0) == out          # T = 0 is greedy
+
+
+def test_llama3_scaling_by_hand_and_the_librarys_table():
+    """The reference has no frequency rescaling, so nothing of its pins this rule; three values
+    worked out by hand do (theta 500000, 64 pairs, factor 8, low 1, high 4, original length 8192:
+    pair 27 has a wavelength of 1594 < 8192/4 and stays; pair 35 has 8219 > 8192/1 and is divided
+    by 8; pair 30 has 2948.3, in between, period count 8192/2948.3 = 2.77855, smooth =
+    (2.77855 - 1)/(4 - 1) = 0.592849, scale = (1 - 0.592849)/8 + 0.592849 = 0.643743) and so does a
+    second statement of the rule, the table builder of the library's rotary part."""
+    from scriptling_llm_lib_b200.config.llama import RopeScaling
+    from scriptling_llm_lib_b200.parts.rotary import inverse_frequencies
+    sc = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 8192}
+    f, g = plain.rope_inv_freq(128, 500000.0), plain.rope_inv_freq(128, 500000.0, sc)
+    assert abs(2 * math.pi / f[30].item() - 2948.3026) < 1e-3
+    assert g[27].item() == f[27].item() and abs(g[35].item() / f[35].item() - 0.125) < 1e-15
+    assert abs(g[30].item() / f[30].item() - 0.6437431331) < 1e-9
+    for scaling in (None, sc, dict(sc, factor=32.0), {"rope_type": "linear", "factor": 4.0}):
+        for dim, theta in ((128, 500000.0), (64, 130000.0), (16, 10000.0)):
+            lib = inverse_frequencies(dim, theta, RopeScaling(**scaling) if scaling else None)
+            assert np.allclose(lib, plain.rope_inv_freq(dim, theta, scaling).numpy(), rtol=1e-13, atol=0)
+
+
+def test_half_pairing_is_the_references_rotation_under_a_permutation_of_rows(tmp_path):
+    """The reference rotates adjacent pairs (float32_ops.go:174-188); checkpoints of the family pair
+    dimension i with i + width/2 instead. The two are one rotation seen through a permutation of the
+    query and key projections' rows inside each head (pairs 0,1 | 2,3 | ... -> first halves, then second
+    halves): a model with interleaved pairing and the same model with permuted rows and half pairing
+    give the same logits, which ties the half pairing to the formula the reference does have. Scores
+    are sums over a head's dimensions, so the order inside a head does not matter otherwise."""
+    raw, seed = TINY["A"]                                                # interleaved, full rotary width
+    assert raw["rope_pairing"] == "interleaved"
+    cfg, w = plain.load_folder(make_model_dir(tmp_path, raw, seed))
+    hd = cfg["head_dim"]
+    perm_in_head = list(range(0, hd, 2)) + list(range(1, hd, 2))
+    w2 = dict(w)
+    for i in range(cfg["num_hidden_layers"]):
+        for name, heads in (("q_proj", cfg["num_attention_heads"]), ("k_proj", cfg["num_key_value_heads"])):
+            key = f"model.layers.{i}.self_attn.{name}.weight"
+            rows = torch.tensor([h * hd + j for h in range(heads) for j in perm_in_head])
+            w2[key] = w[key][rows]
+    ids = random_ids(50, cfg["vocab_size"], 12)
+    a = plain.PlainLlama(cfg, w).logits(ids)
+    b = plain.PlainLlama(dict(cfg, rope_pairing="half"), w2).logits(ids)
+    assert rel_err(b, a) < 1e-12
+    assert rel_err(plain.PlainLlama(dict(cfg, rope_pairing="half"), w).logits(ids), a) > 1e-3    # without the permutation it is another model
+
+
+def test_tied_head_is_the_embedding_matrix_as_stored(tmp_path):
+    """With tie_word_embeddings the logits are the final norm times the embedding matrix itself
+    (model_f32.go:147-162 falls back to it; its re-quantisation of that matrix to 8 bits is a storage
+    choice of the reference's and is not reproduced): a tied model equals the untied model whose
+    lm_head.weight is a copy of the embedding."""
+    raw, seed = TINY["A"]
+    cfg, w = plain.load_folder(make_model_dir(tmp_path, raw, seed))
+    assert cfg["tie_word_embeddings"] and "lm_head.weight" not in w
+    ids = random_ids(20, cfg["vocab_size"], 4)
+    untied = plain.PlainLlama(dict(cfg, tie_word_embeddings=False), dict(w, **{"lm_head.weight": w["model.embed_tokens.weight"].clone()}))
+    assert torch.equal(untied.logits(ids), plain.PlainLlama(cfg, w).logits(ids))
