@@ -33,7 +33,15 @@ def _ptr(t: torch.Tensor | None, dtype=None, name="tensor"):
     return c_void_p(t.data_ptr())
 
 
+try:        # the raw handle of torch's current stream without building a Stream object (a launch costs microseconds)
+    _raw_stream, _current_device = torch._C._cuda_getCurrentRawStream, torch._C._cuda_getDevice
+except AttributeError:      # a torch without these entry points: the public, slower way
+    _raw_stream = _current_device = None
+
+
 def _stream():
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(_current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -70,10 +78,14 @@ class KernelSet:
         self.dtype = dtype
         self.suffix = _SUFFIX[dtype]
         self.lib = load_library(self.suffix)
+        self._fns: dict[str, object] = {}
 
     def _fn(self, name):
-        fn = getattr(self.lib, f"sllm_{name}_{self.suffix}")
-        fn.restype = c_int
+        fn = self._fns.get(name)
+        if fn is None:
+            fn = getattr(self.lib, f"sllm_{name}_{self.suffix}")
+            fn.restype = c_int
+            self._fns[name] = fn
         return fn
 
     # ------------------------------------------------------------------ embedding
@@ -227,15 +239,12 @@ class TensorCoreGemm:
         return (a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
                 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def gemm(self, a, w, out, err_flag, swiglu=False, accumulate=False):
+    def gemm(self, a, w, out, err_flag, swiglu=False):
         """out[M,N] = a @ w^T in bfloat16 or float32; swiglu: out[M,N/2] = silu(gate)*up for w's rows
-        tiled 8 gate / 8 up; accumulate: out (float32) += a @ w^T. `err_flag` (int32 on the device) is
-        set if a wait in the kernel timed out."""
+        tiled 8 gate / 8 up. `err_flag` (int32 on the device) is set if a wait in the kernel timed out."""
         M, K = a.shape
         N = w.shape[0]
         want = (M, N // 2) if swiglu else (M, N)
-        if accumulate and (swiglu or out.dtype != torch.float32):
-            raise KernelError("gemm_tc accumulates into a float32 matrix only")
         if tuple(out.shape) != want or w.shape[1] != K or out.stride(1) != 1:
             raise KernelError(f"gemm_tc shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
@@ -245,7 +254,7 @@ class TensorCoreGemm:
         _check(self.lib.sllm_gemm_tc_bf16(
             c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
             c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
-            c_int(2 if accumulate else (1 if swiglu else 0)), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
+            c_int(1 if swiglu else 0), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
 
 
     QKV_ROPE_HEAD_DIMS = (64, 128)

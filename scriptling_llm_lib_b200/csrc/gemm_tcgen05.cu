@@ -28,7 +28,6 @@
 
 #define TC_EPI_STORE 0
 #define TC_EPI_SWIGLU 1
-#define TC_EPI_RESIDUAL 2   // C is the float residual stream: C += A B^T
 #define TC_EPI_QKV_ROPE 3   // C's columns are [q heads | k heads | v heads]: rotate q and k, put k and v into the cache
 
 // What the q|k|v epilogue needs besides the product: where each row (token) sits, the rotary
@@ -73,20 +72,7 @@ __device__ __forceinline__ void qkv_store32(const TcRope& rp, void* C, int ldc, 
 // columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2).
 template <int EPI>
 __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, int ldc, int out_f32, const uint32_t (&r)[32]) {
-  if (EPI == TC_EPI_RESIDUAL) {
-    float* dst = (float*)C + (size_t)row * ldc + col;
-    if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 v = *(float4*)(dst + j);
-        v.x += __uint_as_float(r[j]); v.y += __uint_as_float(r[j + 1]); v.z += __uint_as_float(r[j + 2]); v.w += __uint_as_float(r[j + 3]);
-        *(float4*)(dst + j) = v;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; j++) if (col + j < N) dst[j] += __uint_as_float(r[j]);
-    }
-  } else if (EPI == TC_EPI_STORE) {
+  if (EPI == TC_EPI_STORE) {
     if (out_f32) {
       float* dst = (float*)C + (size_t)row * ldc + col;
       if (col + 32 <= N && ((uintptr_t)dst & 15) == 0) {
@@ -569,15 +555,12 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
   if (tc_use_pair(M, N)) {
     rc = tc_make_map(&mb, B, N, K, ldb, 128);
     if (rc) return rc;
-    if (epilogue == TC_EPI_RESIDUAL) return tc_pair_launch<6, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream);
     if (epilogue == TC_EPI_SWIGLU) return tc_pair_launch<6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);
     return tc_pair_launch<6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
   }
   rc = tc_make_map(&mb, B, N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
-  if (epilogue == TC_EPI_RESIDUAL)
-    return big ? tc_launch<256, 4, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream)
-               : tc_launch<128, 6, TC_EPI_RESIDUAL>(ma, mb, C, M, N, K, ldc, 1, err, stream);
+  if (epilogue != TC_EPI_SWIGLU && epilogue != TC_EPI_STORE) return SLLM_ERR_ARG;
   if (epilogue == TC_EPI_SWIGLU)
     return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream)
                : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);

@@ -153,7 +153,7 @@ def test_gemm_small_m(kernel_sets, M, N, K):
 @pytest.mark.parametrize("M, N, K", [(128, 128, 64), (100, 200, 72), (130, 264, 520), (2048, 2048, 2048), (65, 1003 * 8, 136),
                                      (300, 96, 8192), (257, 384, 136), (2304, 6400, 192), (1100, 4104, 2176)])
 def test_gemm_tensor_core(kernel_sets, M, N, K):
-    """The tcgen05 GEMM: bfloat16 and float outputs, the SiLU-gate epilogue, accumulation into a float matrix.
+    """The tcgen05 GEMM: bfloat16 and float outputs, the SiLU-gate epilogue.
     More than 128 rows and columns go to the kernel that pairs two SMs on a 256 x 256 tile: sizes with
     a ragged last tile, with several tiles to a pair (both accumulators, both phases), and with few
     and many k-blocks to a tile (eight or four epilogue warps)."""
@@ -168,10 +168,6 @@ def test_gemm_tensor_core(kernel_sets, M, N, K):
     out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
     tc.gemm(a, w, out32, err)
     assert rel_err(out32.cpu(), want) < 3e-5              # tensor-core accumulation over long K
-    base = dev(rand(M, N, seed=16))
-    acc = base.clone()
-    tc.gemm(a, w, acc, err, accumulate=True)
-    assert rel_err(acc.cpu(), f64(base) + want) < 3e-5
     if N % 16 == 0:
         F = N // 2
         tiled = w.view(2, F // 8, 8, K).permute(1, 0, 2, 3).reshape(N, K).contiguous()
