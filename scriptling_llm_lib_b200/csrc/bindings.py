@@ -186,9 +186,12 @@ class KernelSet:
         return head_dim % 4 == 0 and 4 <= head_dim <= 512 and q_ld % 4 == 0
 
     @staticmethod
-    def attn_decode_splits(n_seqs: int, n_heads: int, pages: int, sm_count: int) -> int:
-        """Blocks per (sequence, head): enough for about six blocks of four warps per SM, at most one per page."""
-        want = -(-6 * sm_count // max(1, n_seqs * n_heads))
+    def attn_decode_splits(n_seqs: int, n_heads: int, n_kv: int, pages: int, sm_count: int) -> int:
+        """Blocks per (sequence, key/value head, pass over the keys; a pass serves up to four of the
+        query heads that share the key/value head): enough for about six blocks of four warps per SM,
+        at most one per page."""
+        passes = -(-(n_heads // n_kv) // 4)       # (wide heads, above 128: two heads a pass; the estimate stays)
+        want = -(-6 * sm_count // max(1, n_seqs * n_kv * passes))
         return max(1, min(want, pages, 64))
 
     # ------------------------------------------------------------------ feed-forward

@@ -108,6 +108,19 @@ __device__ __forceinline__ float4 ld4(const bf16* p) {
   __nv_bfloat162 lo = *(__nv_bfloat162*)&r.x, hi = *(__nv_bfloat162*)&r.y;
   return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
 }
+// the same for data that is read once (weights streaming through): not kept in L1, so that what is
+// read again and again beside it (the step's few activation rows) stays there
+__device__ __forceinline__ float4 ld4_stream(const float* p) {
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float4 ld4_stream(const bf16* p) {
+  uint32_t a, b;
+  asm volatile("ld.global.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(a), "=r"(b) : "l"(p));
+  __nv_bfloat162 lo = *(__nv_bfloat162*)&a, hi = *(__nv_bfloat162*)&b;
+  return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
 __device__ __forceinline__ void st4(float* p, float4 v) { *(float4*)p = v; }
 __device__ __forceinline__ void st4(bf16* p, float4 v) {
   __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);

@@ -299,10 +299,10 @@ gemm_nt_regtile_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* _
 // blockIdx.y, block y takes the y-th contiguous part of K and C receives float partial sums at
 // C + y * M * ldc (the reader, a norm, adds them). Needs K, lda, ldb in multiples of 4 elements.
 template <typename TI, typename TO, int MT, int NC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 gemv_nt_block_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __restrict__ C, int M, int N, int K,
                      int lda, int ldb, int ldc, int k_per_split) {
-  constexpr int NV = MT * NC;                              // sums per thread; a power of two <= 32
+  constexpr int NV = MT * NC;                              // sums per thread; a power of two, 4..64
   __shared__ float red[8][NV];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * NC;
@@ -318,7 +318,7 @@ gemv_nt_block_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __r
   for (int k = k_begin + tid * 4; k < k_end; k += 256 * 4) {
     float4 b[NC];
 #pragma unroll
-    for (int c = 0; c < NC; c++) b[c] = ld4(brow[c] + k);
+    for (int c = 0; c < NC; c++) b[c] = ld4_stream(brow[c] + k);
 #pragma unroll
     for (int m = 0; m < MT; m++) {
       float4 a = (m < M) ? ld4(A + (size_t)m * lda + k) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -331,10 +331,15 @@ gemv_nt_block_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __r
     }
   }
   // reduce-scatter over the warp: after the step with offset o a lane keeps the half of its sums that
-  // its bit o selects; after log2(NV) steps it holds one sum, whose index its upper lane bits spell
+  // its bit o selects (a contiguous range of the original indices, starting at `held`); five steps
+  // leave NV / 32 sums per lane (one, or two when a thread had 64), fewer steps leave one that the
+  // lanes sharing it still have to add up
   int held = 0;
+  constexpr int STEPS = NV >= 32 ? 5 : (NV == 16 ? 4 : (NV == 8 ? 3 : 2));
+  constexpr int LEFT = NV >> STEPS;                            // sums per lane afterwards: 1 or 2
 #pragma unroll
-  for (int n = NV, o = 16; n > 1; n >>= 1, o >>= 1) {
+  for (int st = 0; st < STEPS; st++) {
+    const int n = NV >> st, o = 16 >> st;
     const bool up = (lane & o) != 0;
 #pragma unroll
     for (int i = 0; i < n / 2; i++) {
@@ -344,10 +349,14 @@ gemv_nt_block_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TO* __r
     }
     if (up) held += n / 2;
   }
-  float v = acc[0];
 #pragma unroll
-  for (int o = 16 / NV; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);   // lanes that hold the same index
-  if ((lane & (32 / NV - 1)) == 0) red[warp][held] = v;
+  for (int o = 16 >> STEPS; o > 0; o >>= 1)                    // lanes that hold the same index (fewer than 32 sums)
+#pragma unroll
+    for (int i = 0; i < LEFT; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+  if ((lane & ((32 >> STEPS) - 1)) == 0) {
+#pragma unroll
+    for (int i = 0; i < LEFT; i++) red[warp][held + i] = acc[i];
+  }
   __syncthreads();
   if (tid < NV) {
     float t = 0.f;
@@ -767,10 +776,11 @@ __global__ void __launch_bounds__(256) attn_paged_tiled_kernel(AttnArgs p) {
 }
 
 // ------------------------------------------------------------------ one query per sequence, keys split over blocks
-// The decode step of the generic path: block (split, head, sequence) streams its share of the
-// sequence's pages once, LPK lanes per key with 4 dims each per pass (NV passes for wide heads),
-// online softmax per lane group in float (exponentials as 2^x of scores scaled by log2 e), folded
-// over the warp and the block. With one split the block writes the output row; otherwise it leaves
+// The decode step of the generic path: block (split, key/value head, sequence) streams its share of
+// the sequence's pages once for up to NREP of the query heads that share the key/value head (more
+// heads: once per NREP of them), LPK lanes per key with 4 dims each per pass (NV passes for wide
+// heads), online softmax per lane group and head in float (exponentials as 2^x of scores scaled by
+// log2 e), folded over the warp and the block. With one split the block writes the output row; otherwise it leaves
 // (unnormalised sum, maximum, sum) in `part` [B][H][n_split][hd + 2] for the merge kernel below.
 struct AttnSplitArgs {
   const void* q;        // [B, q_ld] rotated queries of this step
@@ -787,14 +797,14 @@ struct AttnSplitArgs {
 };
 #define ATT_LOG2E 1.4426950408889634f
 
-template <typename A, int LPK, int NV>
+template <typename A, int LPK, int NV, int NREP>
 __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSplitArgs p) {
   constexpr int KPW = 32 / LPK;                 // keys a warp reads per load
   constexpr int UN = NV == 1 ? 4 : (NV == 2 ? 2 : 1);   // loads in flight per lane group
-  extern __shared__ __align__(16) float ad_sm[];        // [4][hd] partial outputs, then [4][2] (m, l)
+  extern __shared__ __align__(16) float ad_sm[];        // [4 warps][NREP][hd] partial outputs, then [4][NREP][2] (m, l)
   const int hd = p.hd;
-  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int g = h / (p.H / p.G);
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int nrep = p.H / p.G;                   // query heads that share this key/value head: served NREP at a time
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = lane / LPK, dl = (lane % LPK) * 4;
   const int pos = p.seq_pos0[b];
@@ -806,107 +816,129 @@ __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSpli
   const int* bt = p.block_table + (size_t)b * p.max_pages;
   const A* kp = (const A*)p.kpages;
   const A* vp = (const A*)p.vpages;
-  const A* qrow = (const A*)p.q + (size_t)b * p.q_ld + (size_t)h * hd;
+  float* sm_acc = ad_sm;                        // [4][NREP][hd]
+  float* sm_ml = ad_sm + 4 * NREP * hd;         // [4][NREP][2]
 
-  float qv[NV][4], acc[NV][4], m = -INFINITY, l = 0.f;
+  for (int r0 = 0; r0 < nrep; r0 += NREP) {
+    float qv[NREP][NV][4], acc[NREP][NV][4], m[NREP], l[NREP];
 #pragma unroll
-  for (int v = 0; v < NV; v++) {
-    int d = dl + v * LPK * 4;
-    float4 t = d < hd ? ld4(qrow + d) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float sc = p.scale * ATT_LOG2E;
-    qv[v][0] = t.x * sc; qv[v][1] = t.y * sc; qv[v][2] = t.z * sc; qv[v][3] = t.w * sc;
-    acc[v][0] = acc[v][1] = acc[v][2] = acc[v][3] = 0.f;
-  }
-  for (int kb = k_lo + warp * KPW * UN; kb < k_hi; kb += 4 * KPW * UN) {
-    float4 kr[UN][NV], vr[UN][NV];
-    bool ok[UN];
-#pragma unroll
-    for (int u = 0; u < UN; u++) {
-      int key = kb + u * KPW + slot;
-      ok[u] = key < k_hi;
-      int kk = ok[u] ? key : k_lo;
-      int page = bt[kk / SLLM_PAGE];
-      size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * hd;
+    for (int r = 0; r < NREP; r++) {
+      const int h = g * nrep + min(r0 + r, nrep - 1);           // heads past the group's last repeat it (not stored)
+      const A* qrow = (const A*)p.q + (size_t)b * p.q_ld + (size_t)h * hd;
 #pragma unroll
       for (int v = 0; v < NV; v++) {
         int d = dl + v * LPK * 4;
-        kr[u][v] = d < hd ? ld4(kp + off + d) : make_float4(0.f, 0.f, 0.f, 0.f);
-        vr[u][v] = d < hd ? ld4(vp + off + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 t = d < hd ? ld4(qrow + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float sc = p.scale * ATT_LOG2E;
+        qv[r][v][0] = t.x * sc; qv[r][v][1] = t.y * sc; qv[r][v][2] = t.z * sc; qv[r][v][3] = t.w * sc;
+        acc[r][v][0] = acc[r][v][1] = acc[r][v][2] = acc[r][v][3] = 0.f;
+      }
+      m[r] = -INFINITY;
+      l[r] = 0.f;
+    }
+    for (int kb = k_lo + warp * KPW * UN; kb < k_hi; kb += 4 * KPW * UN) {
+      float4 kr[UN][NV], vr[UN][NV];
+      bool ok[UN];
+#pragma unroll
+      for (int u = 0; u < UN; u++) {
+        int key = kb + u * KPW + slot;
+        ok[u] = key < k_hi;
+        int kk = ok[u] ? key : k_lo;
+        int page = bt[kk / SLLM_PAGE];
+        size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * hd;
+#pragma unroll
+        for (int v = 0; v < NV; v++) {
+          int d = dl + v * LPK * 4;
+          kr[u][v] = d < hd ? ld4(kp + off + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+          vr[u][v] = d < hd ? ld4(vp + off + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < NREP; r++) {
+        float s[UN], m_new = m[r];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+          float d = 0.f;
+#pragma unroll
+          for (int v = 0; v < NV; v++) {
+            d = fmaf(qv[r][v][0], kr[u][v].x, d); d = fmaf(qv[r][v][1], kr[u][v].y, d);
+            d = fmaf(qv[r][v][2], kr[u][v].z, d); d = fmaf(qv[r][v][3], kr[u][v].w, d);
+          }
+#pragma unroll
+          for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          s[u] = ok[u] ? d : -INFINITY;
+          m_new = fmaxf(m_new, s[u]);
+        }
+        if (m_new == -INFINITY) continue;
+        float corr = exp2f(m[r] - m_new);
+        m[r] = m_new;
+        l[r] *= corr;
+#pragma unroll
+        for (int v = 0; v < NV; v++) { acc[r][v][0] *= corr; acc[r][v][1] *= corr; acc[r][v][2] *= corr; acc[r][v][3] *= corr; }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+          float pr = exp2f(s[u] - m_new);
+          l[r] += pr;
+#pragma unroll
+          for (int v = 0; v < NV; v++) {
+            acc[r][v][0] = fmaf(pr, vr[u][v].x, acc[r][v][0]); acc[r][v][1] = fmaf(pr, vr[u][v].y, acc[r][v][1]);
+            acc[r][v][2] = fmaf(pr, vr[u][v].z, acc[r][v][2]); acc[r][v][3] = fmaf(pr, vr[u][v].w, acc[r][v][3]);
+          }
+        }
       }
     }
-    float s[UN], m_new = m;
+    // fold the key slots of the warp, then the warps
 #pragma unroll
-    for (int u = 0; u < UN; u++) {
-      float d = 0.f;
+    for (int r = 0; r < NREP; r++) {
 #pragma unroll
-      for (int v = 0; v < NV; v++) {
-        d = fmaf(qv[v][0], kr[u][v].x, d); d = fmaf(qv[v][1], kr[u][v].y, d);
-        d = fmaf(qv[v][2], kr[u][v].z, d); d = fmaf(qv[v][3], kr[u][v].w, d);
+      for (int o = LPK; o < 32; o <<= 1) {
+        float mo = __shfl_xor_sync(0xffffffffu, m[r], o), lo = __shfl_xor_sync(0xffffffffu, l[r], o);
+        float mn = fmaxf(m[r], mo);
+        float c1 = mn == -INFINITY ? 0.f : exp2f(m[r] - mn), c2 = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+        l[r] = l[r] * c1 + lo * c2;
+        m[r] = mn;
+#pragma unroll
+        for (int v = 0; v < NV; v++)
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            float ao = __shfl_xor_sync(0xffffffffu, acc[r][v][c], o);
+            acc[r][v][c] = acc[r][v][c] * c1 + ao * c2;
+          }
       }
+      if (lane < LPK) {
 #pragma unroll
-      for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      s[u] = ok[u] ? d : -INFINITY;
-      m_new = fmaxf(m_new, s[u]);
-    }
-    if (m_new == -INFINITY) continue;
-    float corr = exp2f(m - m_new);
-    m = m_new;
-    l *= corr;
-#pragma unroll
-    for (int v = 0; v < NV; v++) { acc[v][0] *= corr; acc[v][1] *= corr; acc[v][2] *= corr; acc[v][3] *= corr; }
-#pragma unroll
-    for (int u = 0; u < UN; u++) {
-      float pr = exp2f(s[u] - m_new);
-      l += pr;
-#pragma unroll
-      for (int v = 0; v < NV; v++) {
-        acc[v][0] = fmaf(pr, vr[u][v].x, acc[v][0]); acc[v][1] = fmaf(pr, vr[u][v].y, acc[v][1]);
-        acc[v][2] = fmaf(pr, vr[u][v].z, acc[v][2]); acc[v][3] = fmaf(pr, vr[u][v].w, acc[v][3]);
+        for (int v = 0; v < NV; v++) {
+          int d = dl + v * LPK * 4;
+          if (d < hd) *(float4*)(sm_acc + (warp * NREP + r) * hd + d) = make_float4(acc[r][v][0], acc[r][v][1], acc[r][v][2], acc[r][v][3]);
+        }
+        if (lane == 0) { sm_ml[(warp * NREP + r) * 2] = m[r]; sm_ml[(warp * NREP + r) * 2 + 1] = l[r]; }
       }
     }
-  }
-  // fold the key slots of the warp, then the warps
+    __syncthreads();
+    for (int e = threadIdx.x; e < NREP * hd; e += 128) {
+      const int r = e / hd, dd = e % hd;
+      if (r0 + r >= nrep) continue;
+      const int h = g * nrep + r0 + r;
+      float mn = -INFINITY;
 #pragma unroll
-  for (int o = LPK; o < 32; o <<= 1) {
-    float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
-    float mn = fmaxf(m, mo);
-    float c1 = mn == -INFINITY ? 0.f : exp2f(m - mn), c2 = mn == -INFINITY ? 0.f : exp2f(mo - mn);
-    l = l * c1 + lo * c2;
-    m = mn;
+      for (int w = 0; w < 4; w++) mn = fmaxf(mn, sm_ml[(w * NREP + r) * 2]);
+      float a = 0.f, ls = 0.f;
 #pragma unroll
-    for (int v = 0; v < NV; v++)
-#pragma unroll
-      for (int c = 0; c < 4; c++) {
-        float ao = __shfl_xor_sync(0xffffffffu, acc[v][c], o);
-        acc[v][c] = acc[v][c] * c1 + ao * c2;
+      for (int w = 0; w < 4; w++) {
+        float cw = mn == -INFINITY ? 0.f : exp2f(sm_ml[(w * NREP + r) * 2] - mn);
+        a += sm_acc[(w * NREP + r) * hd + dd] * cw;
+        ls += sm_ml[(w * NREP + r) * 2 + 1] * cw;
       }
-  }
-  float* sm_acc = ad_sm;                // [4][hd]
-  float* sm_ml = ad_sm + 4 * hd;        // [4][2]
-  if (lane < LPK) {
-#pragma unroll
-    for (int v = 0; v < NV; v++) {
-      int d = dl + v * LPK * 4;
-      if (d < hd) *(float4*)(sm_acc + warp * hd + d) = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      if (p.n_split == 1) {
+        ((A*)p.out)[((size_t)b * p.H + h) * hd + dd] = from_f32<A>(ls > 0.f ? a / ls : 0.f);
+      } else {
+        float* dst = p.part + (((size_t)b * p.H + h) * p.n_split + split) * (hd + 2);
+        dst[dd] = a;
+        if (dd == 0) { dst[hd] = mn; dst[hd + 1] = ls; }
+      }
     }
-    if (lane == 0) { sm_ml[warp * 2] = m; sm_ml[warp * 2 + 1] = l; }
+    __syncthreads();
   }
-  __syncthreads();
-  float mn = fmaxf(fmaxf(sm_ml[0], sm_ml[2]), fmaxf(sm_ml[4], sm_ml[6]));
-  float cw[4], ls = 0.f;
-#pragma unroll
-  for (int w = 0; w < 4; w++) {
-    cw[w] = mn == -INFINITY ? 0.f : exp2f(sm_ml[2 * w] - mn);
-    ls += sm_ml[2 * w + 1] * cw[w];
-  }
-  float* dst = p.part + (((size_t)b * p.H + h) * p.n_split + split) * (hd + 2);
-  A* orow = (A*)p.out + ((size_t)b * p.H + h) * hd;
-  for (int dd = threadIdx.x; dd < hd; dd += 128) {
-    float a = sm_acc[dd] * cw[0] + sm_acc[hd + dd] * cw[1] + sm_acc[2 * hd + dd] * cw[2] + sm_acc[3 * hd + dd] * cw[3];
-    if (p.n_split == 1) orow[dd] = from_f32<A>(ls > 0.f ? a / ls : 0.f);
-    else dst[dd] = a;
-  }
-  if (p.n_split > 1 && threadIdx.x == 0) { dst[hd] = mn; dst[hd + 1] = ls; }
 }
 
 // out[b, h*hd + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits added in order

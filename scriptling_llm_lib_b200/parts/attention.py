@@ -115,7 +115,7 @@ class Attention(Mixer):
                                                   self.window, self.scale, ctx.err_flag)
         elif ctx.is_decode and ctx.kernels.attn_decode_split_takes(self.head_dim, qkv.stride(0)):
             # one query per sequence on the generic path (the whole 32-bit decode step): keys split over blocks
-            n_split = ctx.kernels.attn_decode_splits(ctx.n_seqs, self.n_heads, ctx.max_pages, ctx.engine.sm_count)
+            n_split = ctx.kernels.attn_decode_splits(ctx.n_seqs, self.n_heads, self.n_kv_heads, ctx.max_pages, ctx.engine.sm_count)
             part = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                device=x.device) if n_split > 1 else None
             ctx.kernels.attn_decode_split(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, part, ctx.n_seqs,
