@@ -85,6 +85,28 @@ def test_add_rmsnorm(kernel_sets, dtype, d, eps, w32):
     assert rel_err(y3.cpu().float(), plain.rms_norm(want_p, f64(w), eps)[[6, 0, 3]]) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d, w32", [(128, False), (896, True), (2048, False), (2176, True), (4096, False), (2000, False)])
+def test_add_rmsnorm_many_rows(kernel_sets, dtype, d, w32):
+    """The many rows of a prompt step (512 or more: small blocks with four accesses in flight per
+    thread), with and without an addend, at widths that are and are not multiples of 128."""
+    ks = kernel_sets[dtype]
+    T, eps = 517, 1e-5
+    x = dev(rand(T, d, seed=2, scale=3.0))
+    delta = dev(rand(T, d, seed=3), dtype)
+    w = dev(1.0 + rand(d, seed=4, scale=0.1), torch.float32 if w32 else torch.bfloat16)
+    y = torch.full((T, d), float("nan"), dtype=dtype, device="cuda")
+    want_sum = f64(x) + f64(delta)
+    xs = x.clone()
+    ks.add_rmsnorm(xs, delta, None, w, y, eps)
+    assert rel_err(y.cpu().float(), plain.rms_norm(want_sum, f64(w), eps)) < TOL[dtype]
+    assert rel_err(xs.cpu(), want_sum) < 2e-7
+    xs = x.clone()
+    y.fill_(float("nan"))
+    ks.add_rmsnorm(xs, None, None, w, y, eps)
+    assert torch.equal(xs, x) and rel_err(y.cpu().float(), plain.rms_norm(f64(x), f64(w), eps)) < TOL[dtype]
+
+
 # --------------------------------------------------------------------------- matrix products
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M, N, K", [(1, 33, 19), (3, 100, 72), (8, 64, 1000), (9, 130, 65), (70, 257, 136), (200, 96, 520),
