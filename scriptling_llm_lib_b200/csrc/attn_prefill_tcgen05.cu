@@ -3,8 +3,8 @@
 // shared memory for Q, K and V alike, and O takes 128 columns of tensor memory).
 //
 // One work item: 128 consecutive queries of one sequence and one query head. The grid is two blocks
-// per SM that stay; items are numbered longest first (heads fastest, a sequence's query tiles from
-// the last to the first) and dealt to the blocks in rows that run forth and back (block k takes
+// per SM that stay; items are numbered longest first (heads fastest, then the sequences, query tiles
+// from the last to the first) and dealt to the blocks in rows that run forth and back (block k takes
 // items k, 2G-1-k, 2G+k, ... of G blocks), so that a block's long items are paired with short ones
 // and every block ends at about the same time; barriers, tensor memory and the key/value ring live
 // across a block's items. Warp 0 fetches the query
@@ -38,7 +38,7 @@ struct FtArgs {
   int H, G, window;
   float scale;
   int* err;
-  int n_qt, n_items;    // query tiles per sequence (of the longest), work items = H * n_qt * sequences
+  int n_qt, n_seqs, n_items;   // query tiles per sequence (of the longest), sequences, work items = H * n_qt * n_seqs
 };
 
 // What a block works on in its r-th round.
@@ -52,8 +52,8 @@ __device__ __forceinline__ bool ft_item(const FtArgs& p, int round, FtItem& it) 
   if (idx >= p.n_items) return false;
   it.h = idx % p.H;
   int rest = idx / p.H;
-  int qt = p.n_qt - 1 - rest % p.n_qt;
-  it.b = rest / p.n_qt;
+  it.b = rest % p.n_seqs;
+  int qt = p.n_qt - 1 - rest / p.n_seqs;
   it.row0 = p.seq_start[it.b];
   int S = p.seq_start[it.b + 1] - it.row0;
   it.r0 = qt * FT_BQ;
@@ -394,7 +394,7 @@ SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* 
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return (int)e;
   }
-  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, (int)n_items};
+  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, B, (int)n_items};
   dim3 grid((unsigned)(n_items < 2LL * sm_count ? n_items : 2LL * sm_count));     // two blocks per SM that stay
   return hd == 64 ? ft_launch<64, 3>(mq, mk, mv, a, grid, stream) : ft_launch<128, 2>(mq, mk, mv, a, grid, stream);
 }
