@@ -126,3 +126,38 @@ def test_window_group_gives_back_pages_no_later_query_can_see():
     assert list(bt[0][:3]) == [-1, -1, -1]
     c.close(a)
     assert win.pool.n_free == 8 and full.pool.n_free == 8
+
+
+def test_state_record_is_zeroed_at_open_and_seeded_per_sequence():
+    """Beside keys and values every slot has a record of eight words (tokens held, tokens generated,
+    last token, flags, sampling key x2, draw counter x2): zero when the slot is opened, whoever
+    held it before; `seed` sets the key of freshly opened sequences and nothing else."""
+    from scriptling_llm_lib_b200.cache.store import SEQ_COUNTER, SEQ_KEY, SEQ_STATE_WORDS
+    c = make_cache()
+    assert c.seq_state.shape == (4 + 1, SEQ_STATE_WORDS) and c.seq_state.dtype == torch.int32
+    a, b = c.open(), c.open()
+    c.seed([a, b], [7, (5 << 32) | 0xFFFFFFFE])
+    rec = c.seq_state.numpy().astype("int64") & 0xFFFFFFFF
+    assert list(rec[a]) == [0, 0, 0, 0, 7, 0, 0, 0]
+    assert list(rec[b]) == [0, 0, 0, 0, 0xFFFFFFFE, 5, 0, 0]
+    c.seq_state[a, SEQ_COUNTER] = 12                                      # as the sampling kernel would leave it
+    c.close(a)
+    again = c.open()
+    assert again == a and int(c.seq_state[a].abs().sum()) == 0 and int(c.seq_state[b, SEQ_KEY + 1]) == 5
+
+
+def test_cache_kinds_are_a_registry():
+    from scriptling_llm_lib_b200.cache import register_cache_kind
+    with pytest.raises(ValueError, match="known"):
+        CacheNeed("no_such_kind", 1, 16)
+    with pytest.raises(ValueError, match="already registered"):
+        register_cache_kind("full", lambda need, length: 0)
+    # a kind that keeps only the last two pages' worth of positions, whatever the need's window says
+    register_cache_kind("last_128", lambda need, length: length - 128, replace=True)
+    c = SequenceCache({0: CacheNeed("last_128", 1, 16)}, {0: None}, 2, 8, torch.float32, "cpu")
+    s = c.open()
+    c.reserve([(s, 300)])
+    c.advance([(s, 300)])
+    assert c.groups[0].pages[s][:2] == [-1, -1] and all(p >= 0 for p in c.groups[0].pages[s][2:])   # positions < 172: pages 0, 1 gone
+    c.close(s)
+    assert c.groups[0].pool.n_held == 0
