@@ -14,7 +14,6 @@ import torch
 
 from .build import load_library
 
-from ..cache.needs import PAGE  # tokens per cache page; load_library checks that the objects were built with it
 
 
 class KernelError(RuntimeError):

@@ -9,8 +9,7 @@ import pytest
 import torch
 
 import plain_llama as plain
-from helpers import (MEASURED, TINY, TOL_BF16, TOL_F32, check_logits, make_model_dir, plain_model, plain_model_bf16, random_ids,
-                     rel_err)
+from helpers import MEASURED, TINY, TOL_BF16, check_logits, make_model_dir, plain_model, plain_model_bf16, random_ids
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
