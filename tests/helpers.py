@@ -99,6 +99,62 @@ def check_logits(got, want, want16, dtype: str, what: str = "") -> None:
     MEASURED.append((what, e16, e))
 
 
+# --------------------------------------------------------------------------- the C++ statement
+_CPP_BINARY = None
+
+
+def cpp_plain_binary():
+    """tests/plain_cpp/plain_llama.cpp compiled with g++ (no fused multiply-add, no fast-math); None
+    where there is no compiler."""
+    global _CPP_BINARY
+    import shutil
+    import subprocess
+    import tempfile
+    if _CPP_BINARY is None:
+        gxx = shutil.which("g++")
+        if gxx is None:
+            return None
+        src = Path(__file__).resolve().parent / "plain_cpp" / "plain_llama.cpp"
+        out = Path(tempfile.mkdtemp(prefix="plain_cpp_")) / "plain_llama"
+        subprocess.run([gxx, "-O2", "-std=c++17", "-ffp-contract=off", "-o", str(out), str(src)], check=True)
+        _CPP_BINARY = out
+    return _CPP_BINARY
+
+
+def cpp_logits(model_dir, ids, tmp) -> np.ndarray:
+    """Logits [S, vocab] of the C++ plain statement (the reference's float32 arithmetic) for a model
+    folder: weights widened to float32 into one flat file, the configuration as numbers."""
+    import subprocess
+    cfg, w = plain.load_folder(model_dir)
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    sc = cfg.get("rope_scaling") or {}
+    kind = {None: 0, "default": 0, "linear": 1, "llama3": 2}[sc.get("rope_type", sc.get("type"))]
+    numbers = {
+        "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+        "kv_heads": cfg.get("num_key_value_heads") or cfg["num_attention_heads"], "head_dim": hd,
+        "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+        "rotary_dim": int(hd * cfg.get("partial_rotary_factor", 1.0)), "eps": cfg.get("rms_norm_eps", 1e-5),
+        "theta": cfg.get("rope_theta", 10000.0), "interleaved": int(cfg.get("rope_pairing", "half") == "interleaved"),
+        "tied": int(bool(cfg.get("tie_word_embeddings", False))), "window": cfg.get("sliding_window") or 0,
+        "scaling_kind": kind, "factor": sc.get("factor", 1.0), "low": sc.get("low_freq_factor", 1.0),
+        "high": sc.get("high_freq_factor", 4.0), "original": sc.get("original_max_position_embeddings", 8192),
+    }
+    tmp = Path(tmp)
+    tmp.mkdir(parents=True, exist_ok=True)
+    lines, off, chunks = [f"{k} {float(v)!r}" for k, v in numbers.items()], 0, []
+    for name, t in w.items():
+        a = t.to(torch.float32).numpy().ravel()
+        lines.append(f"tensor {name} {off} {a.size}")
+        chunks.append(a)
+        off += a.size
+    (tmp / "manifest.txt").write_text("\n".join(lines) + "\n")
+    np.concatenate(chunks).astype("<f4").tofile(tmp / "weights.f32")
+    np.asarray(ids, dtype="<i4").tofile(tmp / "tokens.i32")
+    subprocess.run([str(cpp_plain_binary()), str(tmp / "manifest.txt"), str(tmp / "weights.f32"), str(tmp / "tokens.i32"),
+                    str(tmp / "out.f32")], check=True)
+    return np.fromfile(tmp / "out.f32", dtype="<f4").reshape(len(ids), cfg["vocab_size"])
+
+
 MEASURED: list = []       # (what, error against the rounding oracle, against the unrounded): printed with -s
 
 
