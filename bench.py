@@ -167,7 +167,8 @@ class Bench:
         shape = SHAPE if shape_name == "smollm2-1.7b" else OTHER_SHAPES[shape_name]
         n_layers = layers or shape["num_hidden_layers"]
         raw = dict(shape, num_hidden_layers=n_layers,
-                   max_position_embeddings=max(shape["max_position_embeddings"], self.args.context + 64))
+                   max_position_embeddings=max(shape["max_position_embeddings"], self.args.context + 64,
+                                               self.args.prefill_tokens))
         path = os.path.join(self.tmp, f"{shape_name}-{n_layers}.json")
         if not os.path.isfile(path):
             with open(path, "w") as f:
@@ -300,8 +301,13 @@ def run(args):
         cfg, n_layers, spec = b.config(args.shape, args.layers)
         full_layers = (SHAPE if args.shape == "smollm2-1.7b" else OTHER_SHAPES[args.shape])["num_hidden_layers"]
         want_points = not args.no_points and args.only == "all" and args.prompts is None
-        biggest = max(64 if want_points else 1, args.batch)
-        eng, sampler = b.load(spec, dtype, biggest * args.context, biggest)
+        # the batch-64 point needs 64 contexts of cache: at long contexts that is more than the GPU has
+        kv_token = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * n_layers * WIDTH[dtype]
+        weights = WIDTH[dtype] * (model_numbers(cfg, n_layers)["layer_params"] * n_layers + 2 * model_numbers(cfg, n_layers)["head_params"])
+        free = torch.cuda.mem_get_info()[0]
+        point_batches = [bb for bb in (1, 64) if weights + bb * args.context * kv_token < 0.85 * free] if want_points else []
+        biggest = max(point_batches + [args.batch])
+        eng, sampler = b.load(spec, dtype, max(biggest * args.context, args.prefill_tokens + 64), biggest)
         V = cfg["vocab_size"]
 
         # ---- the prompt step: 2,048 tokens, or a batch of unequal prompts in one packed step
@@ -309,7 +315,7 @@ def run(args):
             lo, hi = parse_prompts(args.prompts)
             lengths = np.random.default_rng(7).integers(lo, hi + 1, args.batch).tolist()
         else:
-            lengths = [PREFILL_TOKENS]
+            lengths = [args.prefill_tokens]
         prefill = b.prefill_record(eng, cfg, n_layers, lengths, dtype) if args.only != "decode" else None
         if args.prompts is not None and prefill is not None:
             prefill["prompts"] = {"dist": args.prompts, "seed": 7, "n": len(lengths), "min": min(lengths), "max": max(lengths)}
@@ -362,7 +368,7 @@ def run(args):
 
         points = {}
         if want_points:
-            for bb in (1, 64):
+            for bb in point_batches:
                 k = max(8, args.steps // 4) if bb == 64 else args.steps
                 rec, _ = b.decode_record(eng, sampler, cfg, n_layers, b.equal_prompts(bb, k, args.warmup), k, args.warmup, 3 + bb, dtype)
                 points[f"decode_b{bb}"] = rec["value"]
@@ -447,6 +453,8 @@ def main():
                     help="run fewer layers of the same sizes (named in config as layers_run / layers_full)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--prefill-tokens", dest="prefill_tokens", type=int, default=PREFILL_TOKENS,
+                    help="length of the one prompt of the prompt step (the headline metric's is 2,048)")
     ap.add_argument("--prompts", default=None, metavar="uniform:LO-HI",
                     help="a batch of unequal prompts, lengths uniform in LO..HI (seeded): one packed prompt step, then "
                          "decoding from there (instead of equal prompts that end at --context)")
