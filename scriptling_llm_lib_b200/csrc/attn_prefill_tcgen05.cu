@@ -14,7 +14,11 @@
 // tensor memory, two buffers) and O += P V (128 x 64). Warps 2-5 are the softmax:
 // thread = query row = tensor-memory lane, so a row's maximum and sum need no shuffles. They read a
 // row of S, keep a reference maximum and the running sum (base 2, scale folded into one FFMA) and
-// write the probabilities as bfloat16 into shared memory in the swizzled operand layout. O stays in
+// write the probabilities as bfloat16 pairs back into tensor memory, from where P V takes them as its
+// A operand: P never passes through shared memory, whose bandwidth (128 bytes a clock) the operand
+// reads of these narrow products and the TMA writes already use to the full (two P buffers beside S
+// and O for a head of 64; for a head of 128, whose O takes 128 columns, P lies over the first half
+// of its own S). O stays in
 // tensor memory and is accumulated by the tensor core itself; the softmax threads rescale it (read,
 // multiply, write back) only when a row's maximum has grown by more than 2^8 since its reference
 // was set -- probabilities then stay below 2^8, and the final division by the row sum makes the
@@ -75,27 +79,41 @@ __device__ __forceinline__ float ft_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float ft_max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: A's row m in lane m, two bfloat16 of K per 32-bit column
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 template <int FT_HD, int FT_STAGES>
 __global__ void __launch_bounds__(FT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, FtArgs p, uint32_t smem_bytes) {
-  constexpr uint32_t Q_BYTES = FT_BQ * FT_HD * 2, KV_BYTES = FT_BK * FT_HD * 2, P_BYTES = FT_BQ * FT_BK * 2;
+  constexpr uint32_t Q_BYTES = FT_BQ * FT_HD * 2, KV_BYTES = FT_BK * FT_HD * 2;
+  constexpr bool P_OVER_S = FT_HD > 64;          // no columns left for P beside S0, S1 and O: P takes the place of its own S
+  constexpr uint32_t P_COL0 = P_OVER_S ? 0 : 192, P_STEP = P_OVER_S ? 64 : 32;
   constexpr uint32_t QA = FT_BQ * 128, KA = FT_BK * 128;       // bytes of one 64-wide block of Q and of a K or V page
   constexpr int NA = FT_HD / 64;                               // such blocks per head
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // [Q][P][K stages][V stages][barriers]
-  const uint32_t sQ = smem_u32(smem), sP = sQ + Q_BYTES, sK = sP + P_BYTES, sV = sK + FT_STAGES * KV_BYTES;
-  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + P_BYTES + 2 * FT_STAGES * KV_BYTES);
-  // q_full, kv_full[ST], kv_empty[ST], s_full[2], s_empty[2], p_full, p_empty, o_full, q_empty
+  // [Q][K stages][V stages][barriers]
+  const uint32_t sQ = smem_u32(smem), sK = sQ + Q_BYTES, sV = sK + FT_STAGES * KV_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + 2 * FT_STAGES * KV_BYTES);
+  // q_full, kv_full[ST], kv_empty[ST], s_full[2], p_full[2], o_full[2], q_empty. The barriers of S, P and O
+  // come in pairs, one for the tiles of each parity: a waiter is then never more than one phase behind.
   const uint32_t b_qfull = smem_u32(bars), b_kvfull = b_qfull + 8, b_kvempty = b_kvfull + 8 * FT_STAGES,
-                 b_sfull = b_kvempty + 8 * FT_STAGES, b_sempty = b_sfull + 16, b_pfull = b_sempty + 16, b_pempty = b_pfull + 8,
-                 b_ofull = b_pempty + 8, b_qempty = b_ofull + 8;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 1 + 1 + 1 + 1);
+                 b_sfull = b_kvempty + 8 * FT_STAGES, b_pfull = b_sfull + 16, b_ofull = b_pfull + 16, b_qempty = b_ofull + 16;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 1 + 2 * FT_STAGES + 2 + 2 + 2 + 1);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
   if ((uint8_t*)(abort + 1) > smem_raw + smem_bytes) {      // the 1 KB alignment took more than the launch left room for
     if (threadIdx.x == 0) atomicExch(p.err, 3);
@@ -107,10 +125,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
     for (int s = 0; s < FT_STAGES; s++) { mbar_init(b_kvfull + 8 * s, 1); mbar_init(b_kvempty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(b_sfull + 8 * a, 1); mbar_init(b_sempty + 8 * a, 4); }
-    mbar_init(b_pfull, 4);
-    mbar_init(b_pempty, 1);
-    mbar_init(b_ofull, 1);
+    for (int a = 0; a < 2; a++) { mbar_init(b_sfull + 8 * a, 1); mbar_init(b_pfull + 8 * a, 4); mbar_init(b_ofull + 8 * a, 1); }
     mbar_init(b_qempty, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -123,7 +138,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;          // columns: S0 0-63, S1 64-127, O from 128 (one column per dim)
+  const uint32_t tmem_base = *tmem_slot;          // columns: S0 0-63, S1 64-127, O from 128 (one column per dim), P0 and P1 from 192 or over S
 
   // Every role walks the same items in the same order and counts tiles (J) and items (I) by itself; a
   // barrier's phase follows from those counts, so nothing is set up again between items.
@@ -176,7 +191,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         auto issue_s = [&](int j) -> bool {
           int Jg = J0 + j, s = Jg % FT_STAGES, a = Jg & 1;
           if (!mbar_wait(b_kvfull + 8 * s, (Jg / FT_STAGES) & 1, abort)) return false;
-          if (!mbar_wait(b_sempty + 8 * a, ((Jg >> 1) & 1) ^ 1, abort)) return false;
+          // S(Jg) takes the place of S(Jg-2), which the softmax threads have read (their P(Jg-2) was waited
+          // for); where P lies over its S, the product that read P(Jg-2) must be complete as well
+          if (P_OVER_S && Jg >= 2 && !mbar_wait(b_ofull + 8 * a, ((Jg >> 1) & 1) ^ 1, abort)) return false;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
           for (int k = 0; k < FT_HD / 16; k++)      // 16 dims a step: four steps in each 64-wide block
@@ -189,17 +206,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok) ok = issue_s(0);
         for (int j = 0; j < n_tiles && ok; j++) {
           if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
-          int Jg = J0 + j, s = Jg % FT_STAGES;
-          ok = mbar_wait(b_pfull, Jg & 1, abort);       // P of tile j is written, and O has been rescaled if it had to be
+          int Jg = J0 + j, s = Jg % FT_STAGES, a = Jg & 1;
+          ok = mbar_wait(b_pfull + 8 * a, (Jg >> 1) & 1, abort);   // P of tile j is written, and O has been rescaled if it had to be
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
           for (int k = 0; k < FT_BK / 16; k++)
-            umma_bf16(tmem_base + 128, umma_desc_sw128(sP + k * 32), umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, NA > 1 ? KA : 0),
-                      idesc_o, (j | k) ? 1u : 0u);
-          umma_commit(b_ofull);
+            umma_bf16_ta(tmem_base + 128, tmem_base + P_COL0 + a * P_STEP + k * 8, umma_desc_sw128_mn(sV + s * KV_BYTES + k * 2048, NA > 1 ? KA : 0),
+                         idesc_o, (j | k) ? 1u : 0u);
+          umma_commit(b_ofull + 8 * a);
           umma_commit(b_kvempty + 8 * s);
-          umma_commit(b_pempty);
         }
         J0 += n_tiles;
       }
@@ -227,9 +243,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_ld32(t_lane + a * 64, s0);
       tmem_ld32(t_lane + a * 64 + 32, s1);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(b_sempty + 8 * a);
       // ---- mask, row maximum (raw scores; four independent chains)
       bool need_mask = (t * FT_BK + FT_BK - 1 > qpos) || (p.window > 0 && t * FT_BK <= qpos - p.window);
       if (need_mask) {
@@ -240,22 +253,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!(k1 <= qpos && (p.window == 0 || k1 > qpos - p.window))) s1[i] = 0xff800000u;
         }
       }
-      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+      float mxa = ft_max3(__uint_as_float(s0[0]), __uint_as_float(s0[1]), __uint_as_float(s0[2]));
+      float mxb = ft_max3(__uint_as_float(s0[3]), __uint_as_float(s0[4]), __uint_as_float(s0[5]));
+      float mxc = ft_max3(__uint_as_float(s1[0]), __uint_as_float(s1[1]), __uint_as_float(s1[2]));
+      float mxd = ft_max3(__uint_as_float(s1[3]), __uint_as_float(s1[4]), __uint_as_float(s1[5]));
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        mxa = fmaxf(mxa, __uint_as_float(s0[i]));
-        mxb = fmaxf(mxb, __uint_as_float(s0[i + 1]));
-        mxc = fmaxf(mxc, __uint_as_float(s1[i]));
-        mxd = fmaxf(mxd, __uint_as_float(s1[i + 1]));
+      for (int i = 6; i < 32; i += 4) {      // 6..29, then 30, 31
+        if (i + 3 < 32) {
+          mxa = ft_max3(mxa, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+          mxb = ft_max3(mxb, __uint_as_float(s0[i + 2]), __uint_as_float(s0[i + 3]));
+          mxc = ft_max3(mxc, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+          mxd = ft_max3(mxd, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
+        } else {
+          mxa = ft_max3(mxa, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+          mxc = ft_max3(mxc, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+        }
       }
-      float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+      float mx = fmaxf(ft_max3(mxa, mxb, mxc), mxd);
       // ---- move the reference maximum only when the row's maximum has outgrown it by 2^8
       bool grow = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > 8.0f);
       if (__any_sync(0xffffffffu, grow)) {
         float factor = grow ? ((m_ref == -INFINITY) ? 0.f : ft_ex2((m_ref - mx) * sc)) : 1.f;
         if (j >= 1) {
           // O holds the products of tiles 0..j-1: they must be complete before it is rewritten
-          ok = mbar_wait(b_ofull, (Jg - 1) & 1, abort);
+          ok = mbar_wait(b_ofull + 8 * (a ^ 1), ((Jg - 1) >> 1) & 1, abort);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           uint32_t v[32];
@@ -287,9 +308,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         pk[16 + i] = *(uint32_t*)&hi;
       }
       l += rsa + rsb;
-      // ---- P into shared memory (the MMA must have finished reading the previous P)
-      ok = mbar_wait(b_pempty, (Jg & 1) ^ 1, abort);
-      if (!ok) break;
+      // ---- P into tensor memory. The product that read this buffer's last P, two tiles ago, is complete:
+      // it was issued before S(Jg), and the commit that announced S(Jg) covers every product issued before it.
       if (t == t_hi) {
         // keys of the last page beyond the last query's position hold whatever the page held before:
         // their probabilities are zero, but 0 * NaN is NaN, so their value rows are cleared
@@ -297,22 +317,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ok = mbar_wait(b_kvfull + 8 * s, (Jg / FT_STAGES) & 1, abort);
         if (!ok) break;
         for (int e = (warp - 2) * 32 + lane; e < (FT_BK - n_valid) * 8 * NA; e += 128) {
-          int a = e / ((FT_BK - n_valid) * 8), e1 = e % ((FT_BK - n_valid) * 8);
+          int blk = e / ((FT_BK - n_valid) * 8), e1 = e % ((FT_BK - n_valid) * 8);
           int row = n_valid + e1 / 8, c = e1 % 8;
-          *(uint4*)(smem + Q_BYTES + P_BYTES + FT_STAGES * KV_BYTES + s * KV_BYTES + a * KA + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+          *(uint4*)(smem + Q_BYTES + FT_STAGES * KV_BYTES + s * KV_BYTES + blk * KA + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      {
-        uint8_t* prow = smem + Q_BYTES + r * 128;
-#pragma unroll
-        for (int c = 0; c < 8; c++)
-          *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tmem_st32(t_lane + P_COL0 + a * P_STEP, pk);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(b_pfull);
+      if (lane == 0) mbar_arrive(b_pfull + 8 * a);
     }
-    if (ok) ok = mbar_wait(b_ofull, (J0 + n_tiles - 1) & 1, abort);
+    if (ok) ok = mbar_wait(b_ofull + 8 * ((J0 + n_tiles - 1) & 1), ((J0 + n_tiles - 1) >> 1) & 1, abort);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float inv = l > 0.f ? 1.f / l : 0.f;
@@ -351,7 +368,7 @@ template <int HD, int STAGES>
 static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FtArgs& a, dim3 grid,
                      cudaStream_t stream) {
   // what the kernel lays out after aligning to 1 KB, and the most two blocks can have on an SM
-  constexpr size_t need = FT_BQ * HD * 2 + FT_BQ * FT_BK * 2 + 2 * STAGES * FT_BK * HD * 2 + 256;
+  constexpr size_t need = FT_BQ * HD * 2 + 2 * STAGES * FT_BK * HD * 2 + 256;
   constexpr size_t room = (233472 / 2 - 1024);
   constexpr size_t smem = need + 1024 <= room ? need + 1024 : room;     // the slack for the alignment, as far as it fits
   static_assert(need <= smem, "two blocks of this head width do not fit an SM");
