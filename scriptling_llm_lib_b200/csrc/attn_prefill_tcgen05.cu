@@ -13,7 +13,7 @@
 // issues the products: S = Q K^T (128 x 64, float, in tensor memory) and O += P V. Four softmax
 // warps: thread = query row = tensor-memory lane, so a row's maximum and sum need no shuffles. They
 // read a row of S, keep a reference maximum and the running sum (base 2, scale folded into one
-// FFMA) and write the probabilities as bfloat16 pairs back into tensor memory, from where P V takes
+// FFMA; the FFMAs and the sums two floats to an instruction) and write the probabilities as bfloat16 pairs back into tensor memory, from where P V takes
 // them as its A operand: P never passes through shared memory, whose bandwidth (128 bytes a clock)
 // the operand reads of these narrow products and the TMA writes already use to the full. O stays in
 // tensor memory and is accumulated by the tensor core itself; the softmax threads rescale it (read,
@@ -93,6 +93,25 @@ __device__ __forceinline__ float ft_max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
+}
+// two floats at once: d = a * b + c and d = a + b on pairs held in 64-bit registers
+__device__ __forceinline__ uint64_t ft_pack2(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void ft_unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ft_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t ft_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -303,19 +322,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (grow) m_ref = mx;
       }
       float msc = (m_ref == -INFINITY) ? 0.f : m_ref * sc;
-      float rsa = 0.f, rsb = 0.f;
+      uint64_t rs2 = 0ull;                          // two partial sums side by side
+      const uint64_t sc2 = ft_pack2(sc, sc), nm2 = ft_pack2(-msc, -msc);
       uint32_t pk[32];                              // 64 probabilities as bfloat16 pairs: keys 2i, 2i+1
 #pragma unroll
       for (int i = 0; i < 16; i++) {
-        float e0 = ft_ex2(fmaf(__uint_as_float(s0[2 * i]), sc, -msc)), e1 = ft_ex2(fmaf(__uint_as_float(s0[2 * i + 1]), sc, -msc));
-        float e2 = ft_ex2(fmaf(__uint_as_float(s1[2 * i]), sc, -msc)), e3 = ft_ex2(fmaf(__uint_as_float(s1[2 * i + 1]), sc, -msc));
-        rsa += e0 + e1;
-        rsb += e2 + e3;
+        float x0, x1, x2, x3;
+        ft_unpack2(ft_fma2(ft_pack2(__uint_as_float(s0[2 * i]), __uint_as_float(s0[2 * i + 1])), sc2, nm2), x0, x1);
+        ft_unpack2(ft_fma2(ft_pack2(__uint_as_float(s1[2 * i]), __uint_as_float(s1[2 * i + 1])), sc2, nm2), x2, x3);
+        float e0 = ft_ex2(x0), e1 = ft_ex2(x1), e2 = ft_ex2(x2), e3 = ft_ex2(x3);
+        rs2 = ft_add2(rs2, ft_add2(ft_pack2(e0, e1), ft_pack2(e2, e3)));
         __nv_bfloat162 lo = __floats2bfloat162_rn(e0, e1), hi = __floats2bfloat162_rn(e2, e3);
         pk[i] = *(uint32_t*)&lo;
         pk[16 + i] = *(uint32_t*)&hi;
       }
-      l += rsa + rsb;
+      {
+        float ra, rb;
+        ft_unpack2(rs2, ra, rb);
+        l += ra + rb;
+      }
       // ---- P into tensor memory. The product that read this buffer's last P, two tiles ago, is complete:
       // it was issued before S(Jg), and the commit that announced S(Jg) covers every product issued before it.
       if (t == t_hi) {
@@ -677,19 +702,25 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (grow) m_ref = mx;
       }
       const float msc = (m_ref == -INFINITY) ? 0.f : m_ref * sc;
-      float rsa = 0.f, rsb = 0.f;
+      uint64_t rs2 = 0ull;                          // two partial sums side by side
+      const uint64_t sc2 = ft_pack2(sc, sc), nm2 = ft_pack2(-msc, -msc);
       uint32_t pk[32];                              // 64 probabilities as bfloat16 pairs: keys 2i, 2i+1
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        float e0 = ft_ex2(fmaf(__uint_as_float(s[2 * i]), sc, -msc)), e1 = ft_ex2(fmaf(__uint_as_float(s[2 * i + 1]), sc, -msc));
-        float e2 = ft_ex2(fmaf(__uint_as_float(s[2 * i + 2]), sc, -msc)), e3 = ft_ex2(fmaf(__uint_as_float(s[2 * i + 3]), sc, -msc));
-        rsa += e0 + e1;
-        rsb += e2 + e3;
+        float x0, x1, x2, x3;
+        ft_unpack2(ft_fma2(ft_pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), sc2, nm2), x0, x1);
+        ft_unpack2(ft_fma2(ft_pack2(__uint_as_float(s[2 * i + 2]), __uint_as_float(s[2 * i + 3])), sc2, nm2), x2, x3);
+        float e0 = ft_ex2(x0), e1 = ft_ex2(x1), e2 = ft_ex2(x2), e3 = ft_ex2(x3);
+        rs2 = ft_add2(rs2, ft_add2(ft_pack2(e0, e1), ft_pack2(e2, e3)));
         __nv_bfloat162 lo = __floats2bfloat162_rn(e0, e1), hi = __floats2bfloat162_rn(e2, e3);
         pk[i] = *(uint32_t*)&lo;
         pk[i + 1] = *(uint32_t*)&hi;
       }
-      l += rsa + rsb;
+      {
+        float ra, rb;
+        ft_unpack2(rs2, ra, rb);
+        l += ra + rb;
+      }
       if (t * FT_BK + FT_BK - 1 > seq_end) {
         // keys of the sequence's last page beyond its last position hold whatever the page held before:
         // their probabilities are zero, but 0 * NaN is NaN, so their value rows are cleared -- by either
