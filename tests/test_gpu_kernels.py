@@ -431,6 +431,44 @@ def test_attn_prefill_tcgen05(kernel_sets, hd, H, G, window, lens, pos0):
     assert rel_err(out.cpu().float(), want) < 1.2e-2          # probabilities are rounded to bfloat16 before P V
 
 
+@pytest.mark.parametrize("hd, H, G, window", [(64, 40, 40, None), (64, 24, 6, 700), (128, 24, 6, None), (128, 15, 15, None), (128, 9, 3, 900)])
+def test_attn_prefill_tcgen05_long_prompts_many_items(kernel_sets, hd, H, G, window):
+    """Prompts of a few thousand tokens and more work items than resident blocks: every block walks several
+    items, the key/value ring wraps many times, and at head width 128 both ways of pairing query tiles are
+    taken (two heads of a group; two consecutive tiles of one head where the group is odd). Sampled rows
+    (the first, the last, the edges of the 64- and 128-row tiles) against the plain implementation, every
+    row against the generic kernel."""
+    ks = kernel_sets[torch.bfloat16]
+    fa = ks.prefill_attention_tc
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lens, pos0 = [2100, 1500], [0, 64]
+    g = torch.Generator().manual_seed(hd + H)
+    rnd = lambda t: t.bfloat16().float()
+    kk = [rnd(torch.randn(p + n, G, hd, generator=g)) for p, n in zip(pos0, lens)]
+    vv = [rnd(torch.randn(p + n, G, hd, generator=g)) for p, n in zip(pos0, lens)]
+    qs = [rnd(torch.randn(n, H, hd, generator=g)) for n in lens]
+    kp, vp, bt = paged(kk, vv, [p + n for p, n in zip(pos0, lens)], dtype=torch.bfloat16)
+    T = sum(lens)
+    q = dev(torch.cat([t.reshape(t.shape[0], -1) for t in qs]), torch.bfloat16)
+    seq_start = dev(np.concatenate([[0], np.cumsum(lens)]), torch.int32)
+    out = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fa.attn(q, out, seq_start, dev(pos0, torch.int32), bt, kp, vp, len(lens), max(lens), H, G, hd, window, 1.0 / math.sqrt(hd), err)
+    assert int(err) == 0
+    got = out.cpu().float()
+    assert torch.isfinite(got).all()
+    row0 = 0
+    for b, n in enumerate(lens):
+        rows = sorted({0, 1, 62, 63, 64, 65, 126, 127, 128, 129, 191, 192, 255, 256, 1023, 1024, n - 129, n - 128, n - 65, n - 64, n - 2, n - 1}
+                      | {int(x) for x in torch.randint(0, n, (24,), generator=g)})
+        idx = torch.tensor(rows)
+        want = plain.attention(f64(qs[b][idx]), f64(kk[b]), f64(vv[b]), pos0[b] + idx, torch.arange(pos0[b] + n), window).reshape(len(rows), -1)
+        assert rel_err(got[row0 + idx], want) < 1.2e-2, (b, hd, H, G)
+        row0 += n
+    other = torch.empty_like(out)
+    ks.attn_paged(q, other, seq_start, dev(pos0, torch.int32), bt, kp, vp, len(lens), max(lens), H, G, hd, window, 1.0 / math.sqrt(hd))
+    assert rel_err(got, other.cpu().float()) < 1.5e-2
+
+
 @pytest.mark.parametrize("H, G, hd, window", [(4, 2, 16, None), (3, 1, 32, None), (32, 32, 64, None), (8, 2, 128, 300),
                                               (4, 1, 64, 65), (2, 2, 256, None),
                                               # two or more query heads per key/value head at widths 64 and 128: the
