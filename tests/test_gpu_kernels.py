@@ -469,6 +469,33 @@ def test_attn_prefill_tcgen05_long_prompts_many_items(kernel_sets, hd, H, G, win
     assert rel_err(got, other.cpu().float()) < 1.5e-2
 
 
+@pytest.mark.parametrize("hd, H, G", [(64, 32, 32), (128, 32, 8), (128, 5, 5)])
+def test_attn_prefill_tcgen05_same_bits_every_launch(kernel_sets, hd, H, G):
+    """The hand-overs between the kernel's roles must not let timing into the result: twenty launches on
+    the same input, unequal prompts, give the same bits (a buffer reused a phase too early shows here)."""
+    fa = kernel_sets[torch.bfloat16].prefill_attention_tc
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lens = [1943, 560, 700, 65, 1, 1024]
+    g = torch.Generator().manual_seed(hd + H)
+    kk = [torch.randn(n, G, hd, generator=g) for n in lens]
+    vv = [torch.randn(n, G, hd, generator=g) for n in lens]
+    kp, vp, bt = paged(kk, vv, lens, dtype=torch.bfloat16)
+    T = sum(lens)
+    q = dev(torch.randn(T, H * hd, generator=g), torch.bfloat16)
+    seq_start = dev(np.concatenate([[0], np.cumsum(lens)]), torch.int32)
+    pos0 = dev([0] * len(lens), torch.int32)
+    first = None
+    for _ in range(20):
+        out = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        fa.attn(q, out, seq_start, pos0, bt, kp, vp, len(lens), max(lens), H, G, hd, None, 1.0 / math.sqrt(hd), err)
+        if first is None:
+            first = out
+            assert torch.isfinite(first.float()).all()
+        else:
+            assert torch.equal(out, first)
+    assert int(err) == 0
+
+
 @pytest.mark.parametrize("H, G, hd, window", [(4, 2, 16, None), (3, 1, 32, None), (32, 32, 64, None), (8, 2, 128, 300),
                                               (4, 1, 64, 65), (2, 2, 256, None),
                                               # two or more query heads per key/value head at widths 64 and 128: the
