@@ -356,8 +356,8 @@ class DecodeKernels:
 
     def __init__(self):
         self.lib = load_library("decode_bf16")
-        for n in ("sllm_gemm_small_m_bf16", "sllm_attn_decode_bf16", "sllm_attn_decode_merged_bf16",
-                  "sllm_attn_decode_rope_bf16"):
+        for n in ("sllm_gemm_small_m_bf16", "sllm_gemm_small_m_fold_bf16", "sllm_attn_decode_bf16",
+                  "sllm_attn_decode_merged_bf16", "sllm_attn_decode_rope_bf16"):
             getattr(self.lib, n).restype = c_int
         self.lib.sllm_attn_decode_scratch_bytes.restype = c_longlong
         self.lib.sllm_attn_decode_uses_mma.restype = c_int
@@ -396,11 +396,20 @@ class DecodeKernels:
             want, cap = -(-6 * sm_count // pairs), pages
         return max(1, min(want, cap, DecodeKernels.MAX_SPLITS))
 
-    def gemm_small_m(self, a, w, out, swiglu=False):
+    FOLD_MAX_M = 16      # rows up to which a product can take over one half of a norm
+
+    def gemm_small_m(self, a, w, out, swiglu=False, owed=None, fold=None):
         """out[M,N] = a @ w^T (bfloat16 or float32 out); swiglu: out[M,N/2] = silu(gate)*up for w rows
-        tiled 8 gate / 8 up; out float32 [P,M,N]: K split P ways, out receives the partial sums."""
+        tiled 8 gate / 8 up; out float32 [P,M,N]: K split P ways, out receives the partial sums.
+        `owed` = (sumsq float32 [P, M], width, eps): the rows of `a` are a norm's v * weight whose scale
+        rsqrt(sum of v^2 / width + eps) is applied to the output rows instead. `fold` = (norm_weight
+        float32 [N], xb bfloat16 [M, N], sumsq_out float32 [ceil(N / 16), M]): `out` is the float32
+        residual stream [M, N]; it receives the product, and xb and sumsq_out what the product after
+        the following norm is owed (M <= FOLD_MAX_M)."""
         M, K = a.shape
         N = w.shape[0]
+        if owed is not None or fold is not None:
+            return self._gemm_small_m_fold(a, w, out, swiglu, owed, fold)
         ksplit = out.shape[0] if out.dim() == 3 else 1
         want = (M, N // 2) if swiglu else ((ksplit, M, N) if out.dim() == 3 else (M, N))
         if out.dim() == 3 and out.dtype != torch.float32:
@@ -414,6 +423,39 @@ class DecodeKernels:
             _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
             c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
             c_int(1 if swiglu else 0), c_int(ksplit), _stream()), "gemm_small_m")
+
+    def _gemm_small_m_fold(self, a, w, out, swiglu, owed, fold):
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.dim() != 2 or (fold is not None and swiglu):
+            raise KernelError(f"gemm_small_m shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        sumsq_in, n_in, width, eps = c_void_p(None), 0, 0, 0.0
+        if owed is not None:
+            sq, width, eps = owed
+            if sq.dtype != torch.float32 or sq.dim() != 2 or sq.shape[1] != M or not sq.is_contiguous():
+                raise KernelError(f"gemm_small_m: sums of squares {tuple(sq.shape)} {sq.dtype} for {M} rows")
+            sumsq_in, n_in = _ptr(sq, torch.float32, "sumsq"), sq.shape[0]
+        if fold is not None:
+            norm_w, xb, sq_out = fold
+            tiles = -(-N // 16)
+            if (M > self.FOLD_MAX_M or out.dtype != torch.float32 or tuple(out.shape) != (M, N) or tuple(norm_w.shape) != (N,)
+                    or tuple(xb.shape) != (M, N) or not xb.is_contiguous() or tuple(sq_out.shape) != (tiles, M)
+                    or not sq_out.is_contiguous()):
+                raise KernelError(f"gemm_small_m fold: residual {tuple(out.shape)} {out.dtype}, norm weight {tuple(norm_w.shape)}, "
+                                  f"xb {tuple(xb.shape)}, sums {tuple(sq_out.shape)} for M={M}, N={N}")
+            tail = (_ptr(norm_w, torch.float32, "norm_w"), _ptr(xb, torch.bfloat16, "xb"), _ptr(sq_out, torch.float32, "sumsq_out"))
+            epilogue = 2
+        else:
+            want = (M, N // 2) if swiglu else (M, N)
+            if tuple(out.shape) != want or out.dtype not in (torch.bfloat16, torch.float32):
+                raise KernelError(f"gemm_small_m out {tuple(out.shape)} {out.dtype}, want {want}")
+            tail = (c_void_p(None), c_void_p(None), c_void_p(None))
+            epilogue = 1 if swiglu else 0
+        _check(self.lib.sllm_gemm_small_m_fold_bf16(
+            _ptr(a, torch.bfloat16, "a") if a.is_contiguous() else c_void_p(a.data_ptr()),
+            _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+            c_int(w.stride(0)), c_int(out.stride(-2)), c_int(1 if out.dtype == torch.float32 else 0),
+            c_int(epilogue), c_int(1), sumsq_in, c_int(n_in), c_int(width), c_float(eps), *tail, _stream()), "gemm_small_m")
 
     def attn_decode_rope(self, qkv, out, seq_pos0, block_table, kpages, vpages, scratch, tickets, cos_sin, rot,
                          interleaved, write_kv, n_seqs, n_heads, n_kv, head_dim, window, scale, n_split):

@@ -10,6 +10,12 @@
 //     (the next norm) to add. Replaces the reference's row matmul for one token
 //     (float32_ops.go:779-794) and its dense matmul for a few (float32_ops.go:462-482). An epilogue
 //     can apply the SiLU gate (model_f32.go:484-490) when gate and up rows are interleaved 8 and 8.
+//     An RMSNorm between two such products needs no kernel of its own: a row's 1/rms is one number,
+//     so (v / rms * w) W^T = (1 / rms) * ((v * w) W^T). The product before the norm adds its result
+//     to the residual stream in its epilogue, writes v * w in bfloat16 for the product after it and
+//     leaves each tile's sums of v^2; the product after it adds those up, and multiplies its output
+//     rows by rsqrt(sum / width + eps) (float32_ops.go:159-172 with the scale moved behind the sum
+//     over k). Sums of squares, residual and scale are float.
 //   attn_decode: grouped-query attention of one query per sequence over the paged cache, keys
 //     split over blocks (each block streams a contiguous run of pages once and serves all query
 //     heads of its key/value head), online softmax in float. The last block of a (sequence, head
@@ -45,12 +51,35 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 // same assignment, and a sum over k does not care which slot a k sits in.
 #define SM_EPI_STORE 0
 #define SM_EPI_SWIGLU 1
+#define SM_EPI_RESID 2
+
+// The two halves of a norm folded into its neighbours (all pointers null: nothing folded).
+struct SmFold {
+  // in: the rows of x are v * w of a norm whose scale is still owed: sumsq_in[n_in][M] are partial sums of
+  // v^2 over its `1 / inv_width` columns; the output rows are multiplied by rsqrt(sum * inv_width + eps)
+  const float* sumsq_in;
+  int n_in;
+  float inv_width, eps;
+  // out (SM_EPI_RESID): residual[M][ldy] += y; xb[M][N] = bfloat16(residual * norm_w); sumsq_out[tile][M] =
+  // this tile's sums of residual^2
+  float* residual;
+  const float* norm_w;
+  bf16* xb;
+  float* sumsq_out;
+};
+
+__device__ __forceinline__ float ld_dep_f32(const float* p) {      // of data an earlier kernel of the stream wrote
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
 
 template <int NT, int WARPS, int EPI, int UN>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ y, int M, int N, int K,
-                    int ldx, int ldw, int ldy, int out_f32) {
+                    int ldx, int ldw, int ldy, int out_f32, const SmFold f) {
   __shared__ float red[WARPS][NT][4][32];
+  __shared__ float row_scale[NT * 8];
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   int n0 = blockIdx.x * 16;
   const bf16* w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
@@ -109,6 +138,31 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
   int c = blockIdx.y * WARPS + warp;
   fetch(cur, c);
   pdl_wait();
+  // The scale each output row is owed: warp w adds up the partial sums of tokens w, w + WARPS, ... The
+  // first 128 of a token's partial sums are asked for now and added after the products, so that their way
+  // from L2 is not waited for.
+  constexpr int TPW = (NT * 8 + WARPS - 1) / WARPS;
+  float pre[TPW][4];
+  if (f.sumsq_in != nullptr) {
+#pragma unroll
+    for (int tt = 0; tt < TPW; tt++)
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        int tok = warp + tt * WARPS, pt = lane + 32 * k;
+        pre[tt][k] = (tok < M && pt < f.n_in) ? ld_dep_f32(f.sumsq_in + (size_t)pt * M + tok) : 0.f;
+      }
+  }
+  // the residual values this thread will add to are asked for now as well (one output slot per thread of
+  // the first NT * 128; the epilogue below walks the slots in the same order)
+  float resid_pre[(NT * 128 + WARPS * 32 - 1) / (WARPS * 32)];
+  if (EPI == SM_EPI_RESID) {
+#pragma unroll
+    for (int k = 0; k < (NT * 128 + WARPS * 32 - 1) / (WARPS * 32); k++) {
+      int v = threadIdx.x + k * WARPS * 32, i = v / 128, r = (v >> 5) & 3, ln = v & 31;
+      int feat = n0 + (ln >> 2) + 8 * (r >> 1), tok = 8 * i + 2 * (ln & 3) + (r & 1);
+      resid_pre[k] = (v < NT * 128 && feat < N && tok < M) ? ld_dep_f32(f.residual + (size_t)tok * ldy + feat) : 0.f;
+    }
+  }
   while (c < nchunks) {
     fetch(nxt, c + step);
     multiply(cur, c);
@@ -118,25 +172,63 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
     multiply(nxt, c);
     c += step;
   }
+  if (f.sumsq_in != nullptr) {
+    // added in a fixed order: a lane's partial sums in turn, then a tree over the lanes
+#pragma unroll
+    for (int tt = 0; tt < TPW; tt++) {
+      int tok = warp + tt * WARPS;
+      float sq = (pre[tt][0] + pre[tt][1]) + (pre[tt][2] + pre[tt][3]);
+      if (tok < M)
+        for (int pt = lane + 128; pt < f.n_in; pt += 32) sq += ld_dep_f32(f.sumsq_in + (size_t)pt * M + tok);
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (lane == 0 && tok < M) row_scale[tok] = rsqrtf(sq * f.inv_width + f.eps);
+    }
+  }
 #pragma unroll
   for (int i = 0; i < NT; i++)
 #pragma unroll
     for (int r = 0; r < 4; r++) red[warp][i][r][lane] = acc[i][r];
   __syncthreads();
   // acc slot r of lane (g,t): feature n0 + g + 8*(r>>1), token 8*i + 2t + (r&1)
-  for (int v = threadIdx.x; v < NT * 4 * 32; v += WARPS * 32) {
+  int v_slot = 0;
+#pragma unroll
+  for (int v = threadIdx.x; v < NT * 4 * 32; v += WARPS * 32, v_slot++) {
     int i = v / 128, r = (v >> 5) & 3, ln = v & 31;
     float s = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; w++) s += red[w][i][r][ln];
+    const int feat = n0 + (ln >> 2) + 8 * (r >> 1), tok = 8 * i + 2 * (ln & 3) + (r & 1);
+    if (f.sumsq_in != nullptr && tok < M) s *= row_scale[tok];
     if (EPI == SM_EPI_STORE) {
-      int feat = n0 + (ln >> 2) + 8 * (r >> 1), tok = 8 * i + 2 * (ln & 3) + (r & 1);
       if (feat < N && tok < M) {
         if (out_f32) ((float*)y)[((size_t)blockIdx.y * M + tok) * ldy + feat] = s;
         else ((bf16*)y)[(size_t)tok * ldy + feat] = __float2bfloat16_rn(s);
       }
+    } else if (EPI == SM_EPI_RESID) {
+      float sq = 0.f;
+      if (feat < N && tok < M) {
+        float* rp = f.residual + (size_t)tok * ldy + feat;
+        float v = resid_pre[v_slot] + s;
+        *rp = v;
+        f.xb[(size_t)tok * N + feat] = __float2bfloat16_rn(v * f.norm_w[feat]);
+        sq = v * v;
+      }
+      red[0][i][r][ln] = sq;      // slot (i, r, ln) is read by this thread only in the loop above
     } else {
       red[0][i][r][ln] = s;       // slot (i, r, ln) is read by this thread only in the loop above
+    }
+  }
+  if (EPI == SM_EPI_RESID) {
+    // a token's 16 columns of this tile lie in slots r = 2 rr + (tok & 1), ln = 4 gq + (tok % 8) / 2: added in that order
+    __syncthreads();
+    for (int tok = threadIdx.x; tok < NT * 8 && tok < M; tok += WARPS * 32) {
+      float sq = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < 2; rr++)
+#pragma unroll
+        for (int gq = 0; gq < 8; gq++) sq += red[0][tok >> 3][2 * rr + (tok & 1)][4 * gq + ((tok & 7) >> 1)];
+      f.sumsq_out[(size_t)blockIdx.x * M + tok] = sq;
     }
   }
   if (EPI == SM_EPI_SWIGLU) {
@@ -156,31 +248,52 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
 
 template <int NT, int EPI>
 static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
-                          int out_f32, int ksplit, cudaStream_t stream) {
+                          int out_f32, int ksplit, const SmFold& f, cudaStream_t stream) {
   dim3 grid((N + 15) / 16, ksplit);
   constexpr int UN = NT <= 2 ? 2 : 1;
-  return (int)sllm_launch(gemm_small_m_kernel<NT, 4, EPI, UN>, grid, dim3(128), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy, out_f32);
+  // The product that feeds a folded norm cannot split K over blocks (a block must hold whole sums to add them
+  // to the residual stream), so its blocks have 16 warps to split K among: as many loads in flight as 4 x 4.
+  constexpr int WARPS = (EPI == SM_EPI_RESID) ? 16 : 4;
+  return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, UN>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy,
+                          out_f32, f);
 }
 
 // epilogue 0: y[M,N] in bfloat16 (or float when out_f32); epilogue 1: y[M,N/2] = silu(gate)*up with
 // the rows of W interleaved 8 gate rows, 8 up rows. ksplit > 1 (float output only): K is split over
 // ksplit blocks and y receives their partial sums as y[ksplit][M][ldy]; the reader adds them.
-SLLM_EXPORT int sllm_gemm_small_m_bf16(const void* x, const void* W, void* y, int M, int N, int K, int ldx, int ldw,
-                                       int ldy, int out_f32, int epilogue, int ksplit, cudaStream_t stream) {
+// epilogue 2 (M <= 16): y is the float residual stream [M][ldy], which receives the product; xb[M][N] and
+// sumsq_out[ceil(N/16)][M] receive what the product after the following norm needs (see SmFold).
+// sumsq_in (or null), n_in, width_in, eps_in: the scale owed to the rows of x (see SmFold).
+SLLM_EXPORT int sllm_gemm_small_m_fold_bf16(const void* x, const void* W, void* y, int M, int N, int K, int ldx, int ldw,
+                                            int ldy, int out_f32, int epilogue, int ksplit, const float* sumsq_in, int n_in,
+                                            int width_in, float eps_in, const float* norm_w, void* xb, float* sumsq_out,
+                                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return SLLM_ERR_ARG;
   if (epilogue == SM_EPI_SWIGLU && ((N & 15) || out_f32 || ksplit != 1)) return SLLM_ERR_ARG;
+  if (epilogue == SM_EPI_RESID && (M > 16 || ksplit != 1 || !norm_w || !xb || !sumsq_out)) return SLLM_ERR_ARG;
+  if (epilogue < 0 || epilogue > SM_EPI_RESID) return SLLM_ERR_ARG;
   if (ksplit < 1 || ksplit > 64 || (ksplit > 1 && !out_f32)) return SLLM_ERR_ARG;
+  if (sumsq_in && (n_in < 1 || width_in < 1)) return SLLM_ERR_ARG;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-#define SM_CASE(NT)                                                                                                     \
-  return epilogue == SM_EPI_SWIGLU ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, stream) \
-                                   : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, stream)
+  SmFold f{sumsq_in, n_in, sumsq_in ? 1.0f / (float)width_in : 0.f, eps_in, (float*)y, norm_w, (bf16*)xb, sumsq_out};
+#define SM_CASE(NT)                                                                                                          \
+  return epilogue == SM_EPI_SWIGLU  ? small_m_launch<NT, SM_EPI_SWIGLU>(xp, wp, y, M, N, K, ldx, ldw, ldy, 0, 1, f, stream)  \
+         : epilogue == SM_EPI_RESID ? small_m_launch<(NT <= 2 ? NT : 2), SM_EPI_RESID>(xp, wp, y, M, N, K, ldx, ldw, ldy, 1, 1, f, stream) \
+                                    : small_m_launch<NT, SM_EPI_STORE>(xp, wp, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, f, stream)
   if (M <= 8) { SM_CASE(1); }
   if (M <= 16) { SM_CASE(2); }
   if (M <= 32) { SM_CASE(4); }
   SM_CASE(8);
 #undef SM_CASE
+}
+
+SLLM_EXPORT int sllm_gemm_small_m_bf16(const void* x, const void* W, void* y, int M, int N, int K, int ldx, int ldw,
+                                       int ldy, int out_f32, int epilogue, int ksplit, cudaStream_t stream) {
+  if (epilogue != SM_EPI_STORE && epilogue != SM_EPI_SWIGLU) return SLLM_ERR_ARG;
+  return sllm_gemm_small_m_fold_bf16(x, W, y, M, N, K, ldx, ldw, ldy, out_f32, epilogue, ksplit, nullptr, 0, 0, 0.f, nullptr,
+                                     nullptr, nullptr, stream);
 }
 
 // ------------------------------------------------------------------ decode attention, split over keys

@@ -374,8 +374,16 @@ class Engine:
         final norm and the output head."""
         residual = self.model.embedding.forward(ctx.token_ids, ctx)
         delta = None
-        for e in self.layout.schedule:
-            delta = self.model.blocks[e.layer].forward(residual, delta, ctx, e.cache_unit, e.writes_cache)
+        schedule, blocks, rows = self.layout.schedule, self.model.blocks, residual.shape[0]
+        for i, e in enumerate(schedule):
+            block = blocks[e.layer]
+            nxt = blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            if getattr(block, "folds_entry", False) and nxt is not None and getattr(nxt, "folds_entry", False):
+                # the layer behind this one says what its first norm would let this layer's last sublayer prepare
+                delta = block.forward(residual, delta, ctx, e.cache_unit, e.writes_cache,
+                                      next_fold=lambda before, nxt=nxt: nxt.entry_fold(ctx, rows, residual, before))
+            else:
+                delta = block.forward(residual, delta, ctx, e.cache_unit, e.writes_cache)
         if not want:
             return None
         normed = self.model.final_norm.forward(residual, delta, ctx, rows=ctx.want_rows)

@@ -21,7 +21,7 @@ import torch
 
 from ..cache.needs import CacheNeed
 from ..csrc.bindings import DecodeKernels, PrefillAttentionTC
-from .base import MIXERS, POSITION_ENCODINGS, Mixer, PartSpec
+from .base import MIXERS, POSITION_ENCODINGS, Folded, Mixer, PartSpec
 from .linear import Linear
 
 
@@ -73,7 +73,19 @@ class Attention(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x, ctx, unit, writes):
+    def takes_folded(self, ctx, rows: int) -> bool:
+        """The q|k|v product can scale its own output rows (the decode step's few-rows kernel)."""
+        return ctx.is_decode and self.qkv.folds(ctx, rows, ctx.dtype) and self.q_only.folds(ctx, rows, ctx.dtype)
+
+    def can_fold(self, ctx, rows: int) -> bool:
+        """The output product can finish the sublayer: add to the residual stream and prepare the next norm."""
+        return ctx.is_decode and self.out.folds(ctx, rows, ctx.dtype) and self.out.weight.shape[0] % 16 == 0
+
+    def forward(self, x, ctx, unit, writes, fold=None):
+        if isinstance(x, Folded):
+            folded, x = x, x.x
+        else:
+            folded = None
         kpages, vpages, block_table = ctx.unit_kv(unit)
         fast_decode = ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
         rotation = self.position.rotation() if self.position is not None else None
@@ -91,7 +103,8 @@ class Attention(Mixer):
             tc.gemm_qkv_rope(x, self.qkv.weight, qkv, ctx.err_flag, ctx.tok_pos, ctx.tok_seq, block_table, fused_product[0],
                              kpages, vpages, self.n_heads, self.n_kv_heads, self.head_dim, fused_product[1], fused_product[2])
         else:
-            qkv = (self.qkv if writes else self.q_only).forward(x, ctx)
+            proj = self.qkv if writes else self.q_only
+            qkv = proj.forward_folded(folded, ctx) if folded is not None else proj.forward(x, ctx)
             if fusion is None:
                 self._store(qkv, ctx, rotation, self.n_kv_heads if writes else 0, kpages if writes else None,
                             vpages if writes else None, block_table)
@@ -123,6 +136,8 @@ class Attention(Mixer):
         else:
             ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
                                    ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
+        if fold is not None:
+            return self.out.forward_folded(attn, ctx, fold=fold)
         return self.out.forward(attn, ctx, partials_ok=True)
 
 

@@ -28,6 +28,15 @@ Interfaces (duck-typed; the base classes document them):
                                               += delta when rows is None; rows picks rows to norm;
                                               delta: None or either form of y
   PositionEncoding.prepare(max_positions, device); .rotation() or .transform(...)   see below
+
+A norm between two products can be folded into them (optional, and only where all three agree): a
+row's 1/rms is one number, so (v / rms * w) W^T = (1 / rms) * ((v * w) W^T). A norm that can be
+folded says so with `fold_terms()`; a mixer or feed-forward whose last product can take the first
+half (add its result to the residual stream, write v * w, leave the sums of v^2) accepts
+`forward(..., fold=FoldRequest)` and says when with `can_fold(ctx, rows)`; one whose first product
+can take the second half (scale its output rows) accepts a `Folded` as its input and says when with
+`takes_folded(ctx, rows)`. A block asks all three before it requests anything; parts that say
+nothing are never handed either.
 """
 from __future__ import annotations
 
@@ -67,6 +76,27 @@ class Part:
         """Build host-made tables once the engine knows its longest sequence."""
 
 
+@dataclass
+class FoldRequest:
+    """Asks a part's last product to finish the sublayer itself: add the result to `residual`
+    (float32 [T, width], in place) and prepare the input of the product behind the norm with
+    this `weight` (float32 [width]) and `eps`."""
+    residual: Any
+    weight: Any
+    eps: float
+
+
+@dataclass
+class Folded:
+    """The input of the product behind a folded norm: x = (residual * norm weight) in the engine's
+    dtype [T, width], not yet divided by the rows' rms; sumsq float32 [P, T] partial sums of
+    residual^2 over the width. The product multiplies its output rows by rsqrt(sum / width + eps)."""
+    x: Any
+    sumsq: Any
+    width: int
+    eps: float
+
+
 class Mixer(Part):
     def cache_need(self) -> CacheNeed | None:
         return None
@@ -86,6 +116,11 @@ class FeedForward(Part):
 class Norm(Part):
     def forward(self, residual, delta, ctx, rows=None):
         raise NotImplementedError
+
+    def fold_terms(self):
+        """(weight float32 [width], eps) if this norm is y = v / sqrt(mean(v^2) + eps) * weight and may be
+        folded into the products around it; None otherwise."""
+        return None
 
 
 class PositionEncoding(Part):

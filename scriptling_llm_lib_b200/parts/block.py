@@ -11,6 +11,13 @@ feed-forward, two mixers, four norms) is a class of its own and nothing else cha
 hands its last sublayer's output on as a pending `delta`, which the next norm adds while it reads
 the row, so no separate pass over the stream is needed.
 
+Where the norm between two sublayers and the products on either side of it all agree (see base.py:
+FoldRequest, Folded), the norm needs no kernel: the block asks the sublayer before it to finish the
+residual sum and prepare the norm's output, and hands the result through the norm to the sublayer
+behind it. Across layers the same holds for a layer's first norm: a block that sets `folds_entry`
+tells through `entry_fold(ctx, rows, residual)` what the layer before it may prepare, and accepts
+that layer's request as `forward(..., next_fold=...)`.
+
 A block's interface:
   parts() -> list of its parts                  for tensor specs, bind, prepare
   forward(residual, delta, ctx, unit, writes) -> delta
@@ -23,7 +30,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Mapping
 
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, PartSpec
+from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, FoldRequest, PartSpec
 
 
 @dataclass(frozen=True)
@@ -38,10 +45,27 @@ def pre_norm_layer(mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec
                                       feed_forward_norm=feed_forward_norm))
 
 
+import os
+_NO_FOLD = bool(os.environ.get("SLLM_NO_FOLD"))
+
+
+def fold_request(norm, before, behind, ctx, rows: int, residual):
+    """A FoldRequest for `norm` if it, the part `before` it and the part `behind` it all can; else None."""
+    if _NO_FOLD:
+        return None
+    terms = norm.fold_terms() if hasattr(norm, "fold_terms") else None
+    can = getattr(before, "can_fold", None)
+    takes = getattr(behind, "takes_folded", None)
+    if terms is None or can is None or takes is None or not can(ctx, rows) or not takes(ctx, rows):
+        return None
+    return FoldRequest(residual, terms[0], terms[1])
+
+
 class Block:
     """Base of the arrangements: answers for the layer out of `parts()`; an arrangement with one
     mixer need only name it `self.mixer`."""
     mixer = None
+    folds_entry = False          # True: forward takes next_fold=..., and entry_fold says what may be prepared for it
 
     def parts(self) -> list:
         raise NotImplementedError
@@ -77,13 +101,27 @@ class PreNormBlock(Block):
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
-    def forward(self, residual, delta, ctx, unit, writes):
-        """residual float32 [T, hidden] (updated in place), delta: pending addend or None.
-        Returns the new pending addend."""
+    folds_entry = True
+
+    def entry_fold(self, ctx, rows: int, residual, before):
+        """What the sublayer `before` this layer may prepare of this layer's first norm (or None)."""
+        return fold_request(self.mixer_norm, before, self.mixer, ctx, rows, residual)
+
+    def last_part(self):
+        return self.feed_forward
+
+    def forward(self, residual, delta, ctx, unit, writes, next_fold=None):
+        """residual float32 [T, hidden] (updated in place), delta: pending addend or None (or the
+        prepared output of this layer's first norm). Returns the new pending addend; `next_fold`
+        (a function of the part that would do it) asks the last sublayer to prepare the next
+        layer's first norm instead."""
+        rows = residual.shape[0]
         n = self.mixer_norm.forward(residual, delta, ctx)
-        a = self.mixer.forward(n, ctx, unit, writes)
+        fold = fold_request(self.feed_forward_norm, self.mixer, self.feed_forward, ctx, rows, residual)
+        a = self.mixer.forward(n, ctx, unit, writes, fold=fold) if fold is not None else self.mixer.forward(n, ctx, unit, writes)
         n2 = self.feed_forward_norm.forward(residual, a, ctx)
-        return self.feed_forward.forward(n2, ctx)
+        fold = next_fold(self.feed_forward) if next_fold is not None else None
+        return self.feed_forward.forward(n2, ctx, fold=fold) if fold is not None else self.feed_forward.forward(n2, ctx)
 
 
 ARRANGEMENTS.register("pre_norm", PreNormBlock)

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import FEED_FORWARDS, FeedForward
+from .base import FEED_FORWARDS, FeedForward, Folded
 from .linear import Linear
 
 
@@ -31,7 +31,25 @@ class SwiGLU(FeedForward):
             w = self.gate_up.weight
             self.gate_up.weight = w.view(2, F // 8, 8, self.hidden).permute(1, 0, 2, 3).reshape(2 * F, self.hidden).contiguous()
 
-    def forward(self, x, ctx):
+    def takes_folded(self, ctx, rows: int) -> bool:
+        return self.tiled and self.gate_up.folds(ctx, rows, ctx.dtype)
+
+    def can_fold(self, ctx, rows: int) -> bool:
+        return self.down.folds(ctx, rows, ctx.dtype) and self.hidden % 16 == 0
+
+    def forward(self, x, ctx, fold=None):
+        if isinstance(x, Folded) or fold is not None:
+            plain = x.x if isinstance(x, Folded) else x
+            rows = plain.shape[0]
+            h = torch.empty((rows, self.intermediate), dtype=torch.bfloat16, device=plain.device)
+            if isinstance(x, Folded) or (self.tiled and self.gate_up.folds(ctx, rows, ctx.dtype)):
+                self.gate_up.forward_folded(x, ctx, swiglu_out=h)
+            else:
+                h = self._hidden(x, ctx)
+            return self.down.forward_folded(h, ctx, fold=fold) if fold is not None else self.down.forward(h, ctx, partials_ok=True)
+        return self.down.forward(self._hidden(x, ctx), ctx, partials_ok=True)
+
+    def _hidden(self, x, ctx):
         h = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
         w = self.gate_up.weight
         fast = self.tiled and x.dtype == torch.bfloat16 and w.dtype == x.dtype
@@ -44,7 +62,7 @@ class SwiGLU(FeedForward):
         else:
             gu = self.gate_up.forward(x, ctx)
             ctx.kernels.swiglu(gu, h, tiled=self.tiled)
-        return self.down.forward(h, ctx, partials_ok=True)
+        return h
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

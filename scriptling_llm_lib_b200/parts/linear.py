@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.spec import TensorSpec
+from .base import Folded, FoldRequest
 
 
 class Linear:
@@ -30,6 +31,34 @@ class Linear:
         sub = Linear([f"{self.names[0]}[{first}:{first + count}]"], [count], self.in_features)
         sub.weight = self.weight[first:first + count]
         return sub
+
+    def folds(self, ctx, rows: int, dtype) -> bool:
+        """Whether this product, on `rows` rows of `dtype`, can take over either half of a norm (the
+        few-rows kernel of the bfloat16 decode step does)."""
+        w = self.weight
+        return (dtype == torch.bfloat16 and w is not None and w.dtype == torch.bfloat16 and rows <= ctx.kernels.decode.FOLD_MAX_M
+                and w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0)
+
+    def forward_folded(self, x, ctx, fold: FoldRequest | None = None, swiglu_out=None):
+        """The product with one or both halves of a norm folded in (only where `folds` said yes).
+        `x`: a Folded (its rows are owed their scale) or a plain tensor. `fold`: finish the sublayer
+        (residual += y) and return the Folded input of the product behind the next norm; else
+        returns y, or with `swiglu_out` fills it with silu(gate) * up."""
+        owed = (x.sumsq, x.width, x.eps) if isinstance(x, Folded) else None
+        a = x.x if isinstance(x, Folded) else x
+        w = self.weight
+        if fold is not None:
+            n_out = w.shape[0]
+            xb = torch.empty((a.shape[0], n_out), dtype=torch.bfloat16, device=a.device)
+            sumsq = torch.empty((-(-n_out // 16), a.shape[0]), dtype=torch.float32, device=a.device)
+            ctx.kernels.decode.gemm_small_m(a, w, fold.residual, owed=owed, fold=(fold.weight, xb, sumsq))
+            return Folded(xb, sumsq, n_out, fold.eps)
+        if swiglu_out is not None:
+            ctx.kernels.decode.gemm_small_m(a, w, swiglu_out, swiglu=True, owed=owed)
+            return swiglu_out
+        out = torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=a.device)
+        ctx.kernels.decode.gemm_small_m(a, w, out, owed=owed)
+        return out
 
     def forward(self, x: torch.Tensor, ctx, out_dtype=None, partials_ok: bool = False) -> torch.Tensor:
         """y [T, out] in `out_dtype` (default: x's). With `partials_ok` the result may instead be

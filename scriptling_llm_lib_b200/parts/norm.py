@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.spec import TensorSpec
-from .base import NORMS, Norm
+from .base import NORMS, Folded, Norm
 
 
 class RMSNorm(Norm):
@@ -24,8 +24,14 @@ class RMSNorm(Norm):
 
     def bind(self, tensors, dtype, device):
         self.weight = tensors[self.weight_name]
+        self.weight_f32 = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
+
+    def fold_terms(self):
+        return self.weight_f32, self.eps
 
     def forward(self, residual, delta, ctx, rows=None):
+        if isinstance(delta, Folded):          # the product before this norm has done its work already
+            return delta
         n = residual.shape[0] if rows is None else rows.shape[0]
         y = torch.empty((n, self.width), dtype=ctx.dtype, device=residual.device)
         ctx.kernels.add_rmsnorm(residual, delta, rows, self.weight, y, self.eps)

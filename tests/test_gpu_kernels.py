@@ -172,6 +172,44 @@ def test_gemm_small_m(kernel_sets, M, N, K):
         assert rel_err(h.cpu().float(), plain.swiglu(want[:, :F], want[:, F:])) < TOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("M, N, K, eps", [(1, 64, 64, 1e-5), (3, 112, 72, 1e-6), (8, 2048, 8192, 1e-5), (13, 1008, 144, 1e-3),
+                                          (16, 2048, 2048, 1e-5), (5, 4096, 4104, 1e-5)])
+def test_gemm_small_m_takes_over_the_halves_of_a_norm(kernel_sets, M, N, K, eps):
+    """A norm folded into the products around it: the product before it adds to the residual stream,
+    writes (residual * weight) in bfloat16 and leaves each tile's sums of squares; the product behind
+    it scales its output rows by rsqrt(sum / width + eps). Both against the plain formulas, and the
+    pair against the plain norm between two plain products."""
+    dk = kernel_sets[torch.bfloat16].decode
+    a, w = dev(rand(M, K, seed=8), torch.bfloat16), dev(rand(N, K, seed=9, scale=0.05), torch.bfloat16)
+    resid0 = rand(M, N, seed=10, scale=2.0).float()
+    norm_w = (1.0 + 0.1 * rand(N, seed=11)).float()
+    y = plain.linear(f64(a), f64(w))
+    # ---- the first half: residual += y, xb, sums of squares
+    resid = dev(resid0, torch.float32)
+    xb = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    sumsq = torch.full((-(-N // 16), M), float("nan"), dtype=torch.float32, device="cuda")
+    dk.gemm_small_m(a, w, resid, fold=(dev(norm_w, torch.float32), xb, sumsq))
+    want_resid = resid0.double() + y
+    assert rel_err(resid.cpu(), want_resid) < 3e-6
+    assert rel_err(xb.cpu().float(), want_resid * norm_w.double()) < TOL[torch.bfloat16]
+    assert rel_err(sumsq.sum(0).cpu(), (want_resid ** 2).sum(1)) < 1e-5
+    # ---- the second half: a product whose input rows are owed their scale
+    w2 = dev(rand(48, N, seed=12, scale=0.05), torch.bfloat16)
+    out = torch.empty(M, 48, dtype=torch.bfloat16, device="cuda")
+    dk.gemm_small_m(xb, w2, out, owed=(sumsq, N, eps))
+    scale = torch.rsqrt((resid.cpu().double() ** 2).mean(1) + eps)
+    assert rel_err(out.cpu().float(), plain.linear(f64(xb), f64(w2)) * scale[:, None]) < TOL[torch.bfloat16]
+    # ---- the pair is the plain norm between two plain products, up to where bfloat16 rounds
+    normed = plain.rms_norm(want_resid, norm_w.double(), eps)
+    assert rel_err(out.cpu().float(), plain.linear(normed, f64(w2))) < 2 * TOL[torch.bfloat16]
+    # ---- the gated epilogue takes the scale too
+    tiled = w2.view(2, 3, 8, N).permute(1, 0, 2, 3).reshape(48, N).contiguous()
+    h = torch.empty(M, 24, dtype=torch.bfloat16, device="cuda")
+    dk.gemm_small_m(xb, tiled, h, swiglu=True, owed=(sumsq, N, eps))
+    full = plain.linear(f64(xb), f64(w2)) * scale[:, None]
+    assert rel_err(h.cpu().float(), plain.swiglu(full[:, :24], full[:, 24:])) < TOL[torch.bfloat16]
+
+
 @pytest.mark.parametrize("M, N, K", [(128, 128, 64), (100, 200, 72), (130, 264, 520), (2048, 2048, 2048), (65, 1003 * 8, 136),
                                      (300, 96, 8192), (257, 384, 136), (2304, 6400, 192), (1100, 4104, 2176)])
 def test_gemm_tensor_core(kernel_sets, M, N, K):

@@ -112,3 +112,34 @@ def test_many_sequences_decode_together(real_model, dtype, n):
         check_logits(torch.cat(rows[i]), pm.logits(r)[h - 1:], pm16.logits(r)[h - 1:], dtype, f"request {i} of {n}")
     assert int(eng.err_flag) == 0
     report(f"{n} rows {dtype}")
+
+
+def test_norms_folded_into_the_decode_products(real_model, monkeypatch):
+    """In a bfloat16 decode step of few rows the norms between two products have no kernel of their own
+    (the product before adds to the residual stream and prepares, the product behind scales its rows).
+    The same steps with every norm as a kernel give the same logits up to where bfloat16 rounds, and
+    take three launches more for these two layers (the first norm of the first layer and the final
+    norm are never folded)."""
+    from scriptling_llm_lib_b200.csrc import bindings
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    from scriptling_llm_lib_b200.parts import block
+    d, reqs, want, want16 = real_model
+    eng = Engine.from_folder(d, "bfloat16", max_tokens=1024)
+    eng.use_graphs = False                                   # count the launches of the steps themselves
+    runs = {}
+    for folded in (True, False):
+        monkeypatch.setattr(block, "_NO_FOLD", not folded)
+        seqs = [eng.open() for _ in reqs[:2]]
+        eng.step([StepEntry(s, r[:40], []) for s, r in zip(seqs, reqs)])
+        rows, n0 = [], bindings.LAUNCHES[0]
+        for t in range(40, 46):
+            rows.append(eng.step([StepEntry(s, [r[t]], [0]) for s, r in zip(seqs, reqs)]).cpu().double())
+        runs[folded] = (torch.stack(rows), (bindings.LAUNCHES[0] - n0) // 6)
+        for s in seqs:
+            s.close()
+    (a, n_a), (b, n_b) = runs[True], runs[False]
+    assert n_b - n_a == 3
+    for i in range(2):
+        check_logits(a[:, i], want[i][40:46], want16[i][40:46], "bfloat16", f"request {i}, norms folded")
+        check_logits(b[:, i], want[i][40:46], want16[i][40:46], "bfloat16", f"request {i}, norms as kernels")
+    assert int(eng.err_flag) == 0
