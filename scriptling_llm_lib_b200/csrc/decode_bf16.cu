@@ -246,16 +246,28 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
   }
 }
 
+template <int NT, int WARPS, int EPI>
+static int small_m_launch_w(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
+                            int out_f32, int ksplit, const SmFold& f, cudaStream_t stream) {
+  dim3 grid((N + 15) / 16, ksplit);
+  constexpr int UN = NT <= 2 ? 2 : 1;
+  return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, UN>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy,
+                          out_f32, f);
+}
+
 template <int NT, int EPI>
 static int small_m_launch(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
                           int out_f32, int ksplit, const SmFold& f, cudaStream_t stream) {
-  dim3 grid((N + 15) / 16, ksplit);
-  constexpr int UN = NT <= 2 ? 2 : 1;
-  // The product that feeds a folded norm cannot split K over blocks (a block must hold whole sums to add them
-  // to the residual stream), so its blocks have 16 warps to split K among: as many loads in flight as 4 x 4.
-  constexpr int WARPS = (EPI == SM_EPI_RESID) ? 16 : 4;
-  return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, UN>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy,
-                          out_f32, f);
+  if constexpr (EPI == SM_EPI_RESID) {
+    // The product that feeds a folded norm cannot split K over blocks (a block must hold whole sums to add
+    // them to the residual stream), so its blocks get the more warps to split K among the fewer they are:
+    // about two thousand warps in all, as many loads in flight as four blocks of four had (measured: 16
+    // warps win at 128 tiles, 8 at 256).
+    const int tiles = (N + 15) / 16;
+    if (tiles <= 160) return small_m_launch_w<NT, 16, EPI>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, f, stream);
+    if (tiles <= 384) return small_m_launch_w<NT, 8, EPI>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, f, stream);
+  }
+  return small_m_launch_w<NT, 4, EPI>(x, W, y, M, N, K, ldx, ldw, ldy, out_f32, ksplit, f, stream);
 }
 
 // epilogue 0: y[M,N] in bfloat16 (or float when out_f32); epilogue 1: y[M,N/2] = silu(gate)*up with
