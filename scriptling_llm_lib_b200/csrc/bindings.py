@@ -8,6 +8,7 @@ CUDA device is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -232,20 +233,52 @@ class TensorCoreGemm:
 
     def __init__(self):
         self.lib = load_library("gemm_tcgen05")
-        self.lib.sllm_gemm_tc_bf16.restype = c_int
-        self.lib.sllm_gemm_tc_skinny_bf16.restype = c_int
-        self.lib.sllm_gemm_tc_qkv_rope_bf16.restype = c_int
+        for n in ("sllm_gemm_tc_bf16", "sllm_gemm_tc_fold_bf16", "sllm_gemm_tc_skinny_bf16", "sllm_gemm_tc_qkv_rope_bf16",
+                  "sllm_gemm_tc_qkv_rope_fold_bf16"):
+            getattr(self.lib, n).restype = c_int
 
     @staticmethod
     def takes(a, w) -> bool:
         return (a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
                 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def gemm(self, a, w, out, err_flag, swiglu=False):
+    @staticmethod
+    def _owed_args(owed, M):
+        if owed is None:
+            return c_void_p(None), c_int(0), c_int(0), c_float(0.0)
+        sq, width, eps = owed
+        if sq.dtype != torch.float32 or sq.dim() != 2 or sq.shape[1] != M or not sq.is_contiguous():
+            raise KernelError(f"sums of squares {tuple(sq.shape)} {sq.dtype} for {M} rows")
+        return _ptr(sq, torch.float32, "sumsq"), c_int(sq.shape[0]), c_int(width), c_float(eps)
+
+    FOLD_SPAN = 128      # columns to a partial sum of squares that a folded product leaves
+    FOLD_MIN_M = 129     # the product that finishes a sublayer for a folded norm runs on the two-SM tiles only
+    ONE_SM_FORCED = os.environ.get("SLLM_GEMM_ONE_SM", "0") not in ("", "0")      # a debugging switch of the library
+
+    def gemm(self, a, w, out, err_flag, swiglu=False, owed=None, fold=None):
         """out[M,N] = a @ w^T in bfloat16 or float32; swiglu: out[M,N/2] = silu(gate)*up for w's rows
-        tiled 8 gate / 8 up. `err_flag` (int32 on the device) is set if a wait in the kernel timed out."""
+        tiled 8 gate / 8 up. `err_flag` (int32 on the device) is set if a wait in the kernel timed out.
+        `owed` = (sumsq float32 [P, M], width, eps): the rows of `a` are a norm's v * weight whose scale
+        rsqrt(sum of v^2 / width + eps) is applied to the output rows instead. `fold` = (norm_weight
+        float32 [N], xb bfloat16 [M, N], sumsq_out float32 [ceil(N / 128), M]): `out` is the float32
+        residual stream [M, N] (M >= FOLD_MIN_M, N > 128 and a multiple of 32); it receives the product,
+        and xb and sumsq_out what the product behind the following norm is owed."""
         M, K = a.shape
         N = w.shape[0]
+        if fold is not None:
+            norm_w, xb, sq_out = fold
+            if (swiglu or out.dtype != torch.float32 or tuple(out.shape) != (M, N) or N % 32 or N <= 128 or M < self.FOLD_MIN_M
+                    or tuple(norm_w.shape) != (N,) or norm_w.dtype != torch.float32 or tuple(xb.shape) != (M, N)
+                    or xb.dtype != torch.bfloat16 or not xb.is_contiguous() or tuple(sq_out.shape) != (-(-N // self.FOLD_SPAN), M)
+                    or not sq_out.is_contiguous() or w.shape[1] != K or out.stride(1) != 1):
+                raise KernelError(f"gemm_tc fold: residual {tuple(out.shape)} {out.dtype}, norm weight {tuple(norm_w.shape)}, "
+                                  f"xb {tuple(xb.shape)}, sums {tuple(sq_out.shape)} for M={M}, N={N}")
+            _check(self.lib.sllm_gemm_tc_fold_bf16(
+                c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
+                c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1), c_int(2), *self._owed_args(owed, M),
+                _ptr(norm_w, torch.float32, "norm_w"), _ptr(xb, torch.bfloat16, "xb"), _ptr(sq_out, torch.float32, "sumsq_out"),
+                _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
+            return
         want = (M, N // 2) if swiglu else (M, N)
         if tuple(out.shape) != want or w.shape[1] != K or out.stride(1) != 1:
             raise KernelError(f"gemm_tc shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
@@ -253,10 +286,11 @@ class TensorCoreGemm:
             raise KernelError(f"gemm_tc dtypes: a {a.dtype}, w {w.dtype}, out {out.dtype}")
         if not (a.is_cuda and w.is_cuda and out.is_cuda):
             raise KernelError("gemm_tc runs on a CUDA device only")
-        _check(self.lib.sllm_gemm_tc_bf16(
+        _check(self.lib.sllm_gemm_tc_fold_bf16(
             c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), c_int(M), c_int(N), c_int(K),
             c_int(a.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
-            c_int(1 if swiglu else 0), _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
+            c_int(1 if swiglu else 0), *self._owed_args(owed, M), c_void_p(None), c_void_p(None), c_void_p(None),
+            _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_tc")
 
 
     QKV_ROPE_HEAD_DIMS = (64, 128)
@@ -268,22 +302,22 @@ class TensorCoreGemm:
         return head_dim in cls.QKV_ROPE_HEAD_DIMS and (interleaved or rot == head_dim)
 
     def gemm_qkv_rope(self, a, w, qkv, err_flag, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv,
-                      head_dim, rot, interleaved):
+                      head_dim, rot, interleaved, owed=None):
         """qkv[:, :n_heads*head_dim] = rotated queries of a @ w^T (w rows: q | k | v heads); the rotated
-        keys and the values go to each row's place in the cache pages and not to `qkv`."""
+        keys and the values go to each row's place in the cache pages and not to `qkv`. `owed`: as in `gemm`."""
         M, K = a.shape
         N = (n_heads + 2 * n_kv) * head_dim
         if tuple(w.shape) != (N, K) or qkv.shape[0] != M or qkv.shape[1] < n_heads * head_dim or qkv.stride(1) != 1:
             raise KernelError(f"gemm_qkv_rope shapes: a {tuple(a.shape)}, w {tuple(w.shape)}, qkv {tuple(qkv.shape)}")
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16:
             raise KernelError("gemm_qkv_rope works in bfloat16")
-        _check(self.lib.sllm_gemm_tc_qkv_rope_bf16(
+        _check(self.lib.sllm_gemm_tc_qkv_rope_fold_bf16(
             c_void_p(a.data_ptr()), c_void_p(w.data_ptr()), c_void_p(qkv.data_ptr()), c_int(M), c_int(K), c_int(a.stride(0)),
             c_int(w.stride(0)), c_int(qkv.stride(0)), _ptr(tok_pos, torch.int32, "tok_pos"), _ptr(tok_seq, torch.int32, "tok_seq"),
             _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), _ptr(cos_sin, torch.float32, "cos_sin"),
             _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"), c_int(n_heads), c_int(n_kv),
-            c_int(head_dim), c_int(rot), c_int(1 if interleaved else 0), _ptr(err_flag, torch.int32, "err_flag"), _stream()),
-            "gemm_qkv_rope")
+            c_int(head_dim), c_int(rot), c_int(1 if interleaved else 0), *self._owed_args(owed, M),
+            _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_qkv_rope")
 
     SKINNY_MAX_M = 128
 

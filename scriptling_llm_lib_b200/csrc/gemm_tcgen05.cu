@@ -28,7 +28,36 @@
 
 #define TC_EPI_STORE 0
 #define TC_EPI_SWIGLU 1
+#define TC_EPI_RESID 2      // C is the float residual stream: it receives the product; TcFold says what else is written
 #define TC_EPI_QKV_ROPE 3   // C's columns are [q heads | k heads | v heads]: rotate q and k, put k and v into the cache
+
+// The two halves of an RMSNorm folded into the products around it (a row's 1/rms is one number, so
+// (v / rms * w) W^T = (1 / rms) * ((v * w) W^T); float32_ops.go:159-172 with the scale moved behind the
+// sum over k). All pointers null: nothing folded.
+struct TcFold {
+  // in: the rows of A are v * w of a norm whose scale is still owed: sumsq_in[n_in][M] are partial sums of v^2
+  // over its `1 / inv_width` columns; the accumulator's rows are multiplied by rsqrt(sum * inv_width + eps)
+  const float* sumsq_in;
+  int n_in;
+  float inv_width, eps;
+  // out (TC_EPI_RESID): C[M][ldc] += product; xb[M][N] = bfloat16(C * norm_w); sumsq_out[ceil(N/128)][M] = the
+  // sums of C^2 over each 128 columns
+  const float* norm_w;
+  bf16* xb;
+  float* sumsq_out;
+};
+
+// the scale a row is owed by a folded norm before the product: its partial sums added in their order
+__device__ __forceinline__ float tc_row_scale(const TcFold& fd, int row, int M) {
+  if (fd.sumsq_in == nullptr || row >= M) return 1.f;
+  float sq = 0.f;
+  for (int pt = 0; pt < fd.n_in; pt++) sq += fd.sumsq_in[(size_t)pt * M + row];
+  return rsqrtf(sq * fd.inv_width + fd.eps);
+}
+__device__ __forceinline__ void tc_scale32(uint32_t (&r)[32], float rs) {
+#pragma unroll
+  for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs);
+}
 
 // What the q|k|v epilogue needs besides the product: where each row (token) sits, the rotary
 // table, the paged cache of the layer. Queries are rotated and written to C; keys are rotated and
@@ -134,8 +163,11 @@ __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, i
 // head width in the q|k|v epilogue.
 template <int EPI>
 __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, int m0, int n0, int c_lo, int c_hi,
-                                                 void* __restrict__ C, int M, int N, int ldc, int out_f32, const TcRope& rp) {
+                                                 void* __restrict__ C, int M, int N, int ldc, int out_f32, const TcRope& rp,
+                                                 const TcFold& fd) {
   int row = m0 + q * 32 + lane;
+  const bool owed = fd.sumsq_in != nullptr;
+  const float rs = tc_row_scale(fd, row, M);
   if constexpr (EPI == TC_EPI_QKV_ROPE) {
     const uint32_t trow = acc + ((uint32_t)(q * 32) << 16);
     int pos = 0;
@@ -154,6 +186,7 @@ __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, 
         uint32_t r[32];
         tmem_ld32(trow + (uint32_t)c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (owed) tc_scale32(r, rs);
         if (row < M) {
           int col = n0 + c0, d0 = col % rp.hd;
           bool rotate = col / rp.hd < rp.H + rp.G;
@@ -186,6 +219,7 @@ __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, 
           tmem_ld32(trow + (uint32_t)(h0 + i0), r0);
           tmem_ld32(trow + (uint32_t)(h0 + half + i0), r1);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (owed) { tc_scale32(r0, rs); tc_scale32(r1, rs); }
           if (row < M) {
             int col = n0 + h0 + i0;
             bool rotate = col / rp.hd < rp.H + rp.G;
@@ -214,9 +248,89 @@ __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, 
       uint32_t r[32];
       tmem_ld32(acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (owed) tc_scale32(r, rs);
       if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
     }
   }
+}
+
+// TC_EPI_RESID for one warp's share of an accumulator (rows m0 + 32 q .., columns c_lo .. c_hi - 1, both
+// multiples of 128; N a multiple of 32): C += product, xb = bfloat16(C * norm_w), and the sums of C^2 of each
+// span of 128 columns. An accumulator row lives in one thread, but the float residual stream wants whole
+// rows of 128 bytes at a time: each chunk of 32 x 32 values goes through `stage` (4 KB of shared memory of
+// this warp, 16-byte groups swizzled by the row) and comes back with eight lanes to a row.
+// The first chunk's residual values are asked for before the wait for the accumulator (`acc_bar`, `parity`):
+// false if that wait gave up.
+__device__ __forceinline__ bool tc_epilogue_resid(uint32_t acc, int q, int lane, int m0, int n0, int c_lo, int c_hi,
+                                                  float* __restrict__ C, int M, int N, int ldc, const TcFold& fd, float* stage,
+                                                  uint32_t acc_bar, uint32_t parity, volatile int* abort) {
+  const int row_own = m0 + q * 32 + lane;
+  const float rs = tc_row_scale(fd, row_own, M);
+  const bool owed = fd.sumsq_in != nullptr;
+  const int sub = lane >> 3, gq = lane & 7;            // on the way back: row 4 it + sub of the chunk, columns 4 gq .. 4 gq + 3
+  float sq[8];
+#pragma unroll
+  for (int it = 0; it < 8; it++) sq[it] = 0.f;
+  // the residual values of a chunk are asked for a chunk ahead, all eight rows' at once: their way from L2
+  // is what this epilogue would otherwise spend its time on
+  auto load_res = [&](float4 (&v)[8], int c0) {
+#pragma unroll
+    for (int it = 0; it < 8; it++) {
+      const int row = m0 + q * 32 + 4 * it + sub;
+      v[it] = (row < M && n0 + c0 < N) ? *(const float4*)(C + (size_t)row * ldc + n0 + c0 + 4 * gq) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  float4 cur[8], nxt[8];
+  load_res(cur, c_lo);
+  if (!mbar_wait(acc_bar, parity, abort)) return false;
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+  for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+    if (c0 + 32 < c_hi) load_res(nxt, c0 + 32);
+    if (n0 + c0 < N) {                                   // uniform over the warp
+      uint32_t r[32];
+      tmem_ld32(acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (owed) tc_scale32(r, rs);
+#pragma unroll
+      for (int k = 0; k < 8; k++)
+        *(float4*)(stage + lane * 32 + ((k ^ (lane & 7)) << 2)) =
+            make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3]));
+      __syncwarp();
+      const int col = n0 + c0 + 4 * gq;
+      const float4 w = *(const float4*)(fd.norm_w + col);
+#pragma unroll
+      for (int it = 0; it < 8; it++) {
+        const int rr = 4 * it + sub, row = m0 + q * 32 + rr;
+        const float4 y = *(const float4*)(stage + rr * 32 + ((gq ^ (rr & 7)) << 2));
+        if (row < M) {
+          float4 v = cur[it];
+          v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+          *(float4*)(C + (size_t)row * ldc + col) = v;
+          sq[it] += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(v.x * w.x, v.y * w.y), p1 = __floats2bfloat162_rn(v.z * w.z, v.w * w.w);
+          *(uint2*)(fd.xb + (size_t)row * N + col) = make_uint2(*(uint32_t*)&p0, *(uint32_t*)&p1);
+        }
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int it = 0; it < 8; it++) cur[it] = nxt[it];
+    if (((c0 + 32) & 127) == 0) {                        // the end of a span of 128 columns: eight lanes hold a row's sum
+      const int span = (n0 + c0) >> 7;
+#pragma unroll
+      for (int it = 0; it < 8; it++) {
+        float t = sq[it];
+        t += __shfl_xor_sync(0xffffffffu, t, 1);
+        t += __shfl_xor_sync(0xffffffffu, t, 2);
+        t += __shfl_xor_sync(0xffffffffu, t, 4);
+        const int row = m0 + q * 32 + 4 * it + sub;
+        if (gq == 0 && row < M && span < ((N + 127) >> 7)) fd.sumsq_out[(size_t)span * M + row] = t;
+        sq[it] = 0.f;
+      }
+    }
+  }
+  return true;
 }
 
 // Persistent: each block walks over output tiles (tile = blockIdx.x, += gridDim.x; consecutive
@@ -226,7 +340,7 @@ __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, 
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ C,
-               int M, int N, int K, int ldc, int out_f32, int* __restrict__ err, const TcRope rp) {
+               int M, int N, int K, int ldc, int out_f32, int* __restrict__ err, const TcRope rp, const TcFold fd) {
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -313,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int a = i & 1;
       if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      tc_epilogue_tile<EPI>(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, 0, BN, C, M, N, ldc, out_f32, rp);
+      tc_epilogue_tile<EPI>(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, 0, BN, C, M, N, ldc, out_f32, rp, fd);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * a) : "memory");
@@ -330,7 +444,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ------------------------------------------------------------------ host side
 template <int BN, int STAGES, int EPI>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int out_f32,
-                     int* err, cudaStream_t stream, const TcRope& rp = TcRope{}) {
+                     int* err, cudaStream_t stream, const TcRope& rp = TcRope{}, const TcFold& fd = TcFold{}) {
   constexpr size_t smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
   static bool raised = false;
   if (!raised) {
@@ -346,7 +460,7 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int 
   }
   int n_tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
   dim3 grid(n_tiles < sms ? n_tiles : sms);
-  gemm_tc_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err, rp);
+  gemm_tc_kernel<BN, STAGES, EPI><<<grid, TC_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err, rp, fd);
   SLLM_RETURN_LAST();
 }
 
@@ -380,7 +494,7 @@ __device__ __forceinline__ void tc2_tile_origin(int tile, int tiles_m, int tiles
 template <int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC2_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ C,
-                    int M, int N, int K, int ldc, int out_f32, int* __restrict__ err, const TcRope rp) {
+                    int M, int N, int K, int ldc, int out_f32, int* __restrict__ err, const TcRope rp, const TcFold fd) {
   constexpr int BN = TC2_BN;
   constexpr uint32_t A_BYTES = 128 * TC_BK * 2, B_BYTES = 128 * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -399,7 +513,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // A read of tensor memory waits behind the products already queued, some thousands of clocks
   // each time, so with few k-blocks to a tile four warps would take longer over a tile's epilogue
   // than the products of the next tile take: then all eight work, each on half of the columns.
-  const bool wide = nkb <= TC2_WIDE_NKB;
+  const bool wide = nkb <= TC2_WIDE_NKB || EPI == TC_EPI_RESID;     // (the residual epilogue moves five times the bytes)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -487,9 +601,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc2_tile_origin(tile, tiles_m, tiles_n, tm, tn);
       const int m0 = tm * TC2_BM + (int)rank * 128, n0 = tn * BN;
       int a = i & 1;
-      if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      tc_epilogue_tile<EPI>(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, c_lo, c_hi, C, M, N, ldc, out_f32, rp);
+      if constexpr (EPI == TC_EPI_RESID) {
+        if (!tc_epilogue_resid(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, c_lo, c_hi, (float*)C, M, N, ldc, fd,
+                               (float*)(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * 1024, acc_full0 + 8 * a, (i >> 1) & 1, abort))
+          break;
+      } else {
+        if (!mbar_wait(acc_full0 + 8 * a, (i >> 1) & 1, abort)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tc_epilogue_tile<EPI>(tmem_base + (uint32_t)(a * BN), q, lane, m0, n0, c_lo, c_hi, C, M, N, ldc, out_f32, rp, fd);
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty0 + 8 * a, 0));
@@ -506,8 +626,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int STAGES, int EPI>
 static int tc_pair_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int out_f32,
-                          int* err, cudaStream_t stream, const TcRope& rp = TcRope{}) {
-  constexpr size_t smem = STAGES * (2 * 128 * TC_BK * 2) + 1024 + 256;
+                          int* err, cudaStream_t stream, const TcRope& rp = TcRope{}, const TcFold& fd = TcFold{}) {
+  // (the residual epilogue stages its chunks through 4 KB a warp behind the barriers)
+  constexpr size_t smem = STAGES * (2 * 128 * TC_BK * 2) + 1024 + 256 + (EPI == TC_EPI_RESID ? 8 * 4096 : 0);
   static int pairs = 0;                  // how many pairs of blocks the GPU holds at once
   if (!pairs) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -528,7 +649,7 @@ static int tc_pair_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C,
   }
   int n_tiles = ((N + TC2_BN - 1) / TC2_BN) * ((M + TC2_BM - 1) / TC2_BM);
   dim3 grid(2 * (n_tiles < pairs ? n_tiles : pairs));
-  gemm_tc_pair_kernel<STAGES, EPI><<<grid, TC2_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err, rp);
+  gemm_tc_pair_kernel<STAGES, EPI><<<grid, TC2_THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, out_f32, err, rp, fd);
   SLLM_RETURN_LAST();
 }
 
@@ -541,13 +662,23 @@ static bool tc_use_pair(int M, int N) {
 
 // C[M,N] = A[M,K] B[N,K]^T. epilogue 0: C bfloat16 (or float when out_f32), row stride ldc;
 // epilogue 1: C[M,N/2] = silu(gate) * up for B's rows in tiles of 16 (8 gate rows, 8 up rows);
-// epilogue 2: C is a float matrix and the product is added to it (the residual sum).
+// epilogue 2 (M > 128, N > 128 and a multiple of 32): C is the float residual stream and receives the product;
+// xb[M][N] and sumsq_out[ceil(N/128)][M] receive what the product behind the following norm needs (see TcFold).
+// sumsq_in (or null), n_in, width_in, eps_in: the scale owed to the rows of A (see TcFold).
 // *err is set to 2 if a wait inside the kernel ran out of time.
-SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                                  int out_f32, int epilogue, int* err, cudaStream_t stream) {
+SLLM_EXPORT int sllm_gemm_tc_fold_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                       int out_f32, int epilogue, const float* sumsq_in, int n_in, int width_in, float eps_in,
+                                       const float* norm_w, void* xb, float* sumsq_out, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return SLLM_ERR_ARG;
   if (epilogue == TC_EPI_SWIGLU && ((N & 15) || out_f32)) return SLLM_ERR_ARG;
+  if (epilogue != TC_EPI_SWIGLU && epilogue != TC_EPI_STORE && epilogue != TC_EPI_RESID) return SLLM_ERR_ARG;
+  if (epilogue == TC_EPI_RESID && (!tc_use_pair(M, N) || (N & 31) || (ldc & 3) || !norm_w || !xb || !sumsq_out ||
+                                   ((uintptr_t)C & 15) || ((uintptr_t)xb & 15) || ((uintptr_t)norm_w & 15)))
+    return SLLM_ERR_ARG;
+  if (sumsq_in && (n_in < 1 || width_in < 1)) return SLLM_ERR_ARG;
+  const TcFold fd{sumsq_in, n_in, sumsq_in ? 1.0f / (float)width_in : 0.f, eps_in, norm_w, (bf16*)xb, sumsq_out};
+  const TcRope rp{};
   CUtensorMap ma, mb;
   int big = N > 128;
   int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
@@ -555,32 +686,43 @@ SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, 
   if (tc_use_pair(M, N)) {
     rc = tc_make_map(&mb, B, N, K, ldb, 128);
     if (rc) return rc;
-    if (epilogue == TC_EPI_SWIGLU) return tc_pair_launch<6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);
-    return tc_pair_launch<6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
+    if (epilogue == TC_EPI_SWIGLU) return tc_pair_launch<6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);
+    if (epilogue == TC_EPI_RESID) return tc_pair_launch<6, TC_EPI_RESID>(ma, mb, C, M, N, K, ldc, 1, err, stream, rp, fd);
+    return tc_pair_launch<6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
   }
   rc = tc_make_map(&mb, B, N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
-  if (epilogue != TC_EPI_SWIGLU && epilogue != TC_EPI_STORE) return SLLM_ERR_ARG;
   if (epilogue == TC_EPI_SWIGLU)
-    return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream)
-               : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream);
-  return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream)
-             : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream);
+    return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd)
+               : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);
+  return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd)
+             : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
+}
+
+SLLM_EXPORT int sllm_gemm_tc_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                  int out_f32, int epilogue, int* err, cudaStream_t stream) {
+  if (epilogue != TC_EPI_SWIGLU && epilogue != TC_EPI_STORE) return SLLM_ERR_ARG;
+  return sllm_gemm_tc_fold_bf16(A, B, C, M, N, K, lda, ldb, ldc, out_f32, epilogue, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr,
+                                err, stream);
 }
 
 // C[M, (H + 2G) hd] = A[M,K] B^T with the q|k|v epilogue: rotated queries to C (bfloat16, row stride
 // ldc), rotated keys and raw values to the rows' places in the cache. Pairing "half" needs the whole
-// head rotated (rot == hd) and hd 64 or 128; "interleaved" any even rot.
-SLLM_EXPORT int sllm_gemm_tc_qkv_rope_bf16(const void* A, const void* B, void* C, int M, int K, int lda, int ldb, int ldc,
-                                           const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
-                                           const void* cos_sin, void* kpages, void* vpages, int H, int G, int hd, int rot,
-                                           int interleaved, int* err, cudaStream_t stream) {
+// head rotated (rot == hd) and hd 64 or 128; "interleaved" any even rot. sumsq_in (or null), n_in,
+// width_in, eps_in: the scale owed to the rows of A (see TcFold).
+SLLM_EXPORT int sllm_gemm_tc_qkv_rope_fold_bf16(const void* A, const void* B, void* C, int M, int K, int lda, int ldb, int ldc,
+                                                const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
+                                                const void* cos_sin, void* kpages, void* vpages, int H, int G, int hd, int rot,
+                                                int interleaved, const float* sumsq_in, int n_in, int width_in, float eps_in,
+                                                int* err, cudaStream_t stream) {
   if (M <= 0) return 0;
   int N = (H + 2 * G) * hd;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || (ldc & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
     return SLLM_ERR_ARG;
   if (H < 1 || G < 1 || (hd != 64 && hd != 128) || rot < 2 || rot > hd || (rot & 1) || (!interleaved && rot != hd)) return SLLM_ERR_ARG;
   if (!tok_pos || !tok_seq || !block_table || !cos_sin || !kpages || !vpages || ((uintptr_t)cos_sin & 15)) return SLLM_ERR_ARG;
+  if (sumsq_in && (n_in < 1 || width_in < 1)) return SLLM_ERR_ARG;
+  const TcFold fd{sumsq_in, n_in, sumsq_in ? 1.0f / (float)width_in : 0.f, eps_in, nullptr, nullptr, nullptr};
   CUtensorMap ma, mb;
   int rc = tc_make_map(&ma, A, M, K, lda, TC_BM);
   if (rc) return rc;
@@ -588,11 +730,19 @@ SLLM_EXPORT int sllm_gemm_tc_qkv_rope_bf16(const void* A, const void* B, void* C
   if (tc_use_pair(M, N)) {
     rc = tc_make_map(&mb, B, N, K, ldb, 128);
     if (rc) return rc;
-    return tc_pair_launch<6, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp);
+    return tc_pair_launch<6, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);
   }
   rc = tc_make_map(&mb, B, N, K, ldb, 256);
   if (rc) return rc;
-  return tc_launch<256, 4, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp);
+  return tc_launch<256, 4, TC_EPI_QKV_ROPE>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);
+}
+
+SLLM_EXPORT int sllm_gemm_tc_qkv_rope_bf16(const void* A, const void* B, void* C, int M, int K, int lda, int ldb, int ldc,
+                                           const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
+                                           const void* cos_sin, void* kpages, void* vpages, int H, int G, int hd, int rot,
+                                           int interleaved, int* err, cudaStream_t stream) {
+  return sllm_gemm_tc_qkv_rope_fold_bf16(A, B, C, M, K, lda, ldb, ldc, tok_pos, tok_seq, block_table, max_pages, cos_sin, kpages,
+                                         vpages, H, G, hd, rot, interleaved, nullptr, 0, 0, 0.f, err, stream);
 }
 
 // ------------------------------------------------------------------ few rows: the weights are the 128-row operand

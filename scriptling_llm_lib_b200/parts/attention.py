@@ -74,12 +74,15 @@ class Attention(Mixer):
         return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
 
     def takes_folded(self, ctx, rows: int) -> bool:
-        """The q|k|v product can scale its own output rows (the decode step's few-rows kernel)."""
-        return ctx.is_decode and self.qkv.folds(ctx, rows, ctx.dtype) and self.q_only.folds(ctx, rows, ctx.dtype)
+        """The q|k|v product can scale its own output rows: in a decode step of few rows, and in a long
+        prompt step (the tensor-core product, with or without the rotation in its epilogue)."""
+        path = self.qkv.fold_path(ctx, rows, ctx.dtype)
+        return path is not None and self.q_only.fold_path(ctx, rows, ctx.dtype) == path and (ctx.is_decode or path == "tiles")
 
     def can_fold(self, ctx, rows: int) -> bool:
         """The output product can finish the sublayer: add to the residual stream and prepare the next norm."""
-        return ctx.is_decode and self.out.folds(ctx, rows, ctx.dtype) and self.out.weight.shape[0] % 16 == 0
+        path = self.out.fold_path(ctx, rows, ctx.dtype, finishing=True)
+        return path is not None and (ctx.is_decode or path == "tiles")
 
     def forward(self, x, ctx, unit, writes, fold=None):
         if isinstance(x, Folded):
@@ -101,7 +104,8 @@ class Attention(Mixer):
             # a long prompt step: the q|k|v product rotates and fills the cache in its own epilogue
             qkv = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=x.dtype, device=x.device)
             tc.gemm_qkv_rope(x, self.qkv.weight, qkv, ctx.err_flag, ctx.tok_pos, ctx.tok_seq, block_table, fused_product[0],
-                             kpages, vpages, self.n_heads, self.n_kv_heads, self.head_dim, fused_product[1], fused_product[2])
+                             kpages, vpages, self.n_heads, self.n_kv_heads, self.head_dim, fused_product[1], fused_product[2],
+                             owed=(folded.sumsq, folded.width, folded.eps) if folded is not None else None)
         else:
             proj = self.qkv if writes else self.q_only
             qkv = proj.forward_folded(folded, ctx) if folded is not None else proj.forward(x, ctx)

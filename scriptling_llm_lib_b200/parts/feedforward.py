@@ -32,17 +32,17 @@ class SwiGLU(FeedForward):
             self.gate_up.weight = w.view(2, F // 8, 8, self.hidden).permute(1, 0, 2, 3).reshape(2 * F, self.hidden).contiguous()
 
     def takes_folded(self, ctx, rows: int) -> bool:
-        return self.tiled and self.gate_up.folds(ctx, rows, ctx.dtype)
+        return self.tiled and self.gate_up.fold_path(ctx, rows, ctx.dtype) is not None
 
     def can_fold(self, ctx, rows: int) -> bool:
-        return self.down.folds(ctx, rows, ctx.dtype) and self.hidden % 16 == 0
+        return self.down.fold_path(ctx, rows, ctx.dtype, finishing=True) is not None
 
     def forward(self, x, ctx, fold=None):
         if isinstance(x, Folded) or fold is not None:
             plain = x.x if isinstance(x, Folded) else x
             rows = plain.shape[0]
             h = torch.empty((rows, self.intermediate), dtype=torch.bfloat16, device=plain.device)
-            if isinstance(x, Folded) or (self.tiled and self.gate_up.folds(ctx, rows, ctx.dtype)):
+            if isinstance(x, Folded) or (self.tiled and self.gate_up.fold_path(ctx, rows, ctx.dtype) is not None):
                 self.gate_up.forward_folded(x, ctx, swiglu_out=h)
             else:
                 h = self._hidden(x, ctx)

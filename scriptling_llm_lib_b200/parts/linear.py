@@ -32,32 +32,47 @@ class Linear:
         sub.weight = self.weight[first:first + count]
         return sub
 
-    def folds(self, ctx, rows: int, dtype) -> bool:
-        """Whether this product, on `rows` rows of `dtype`, can take over either half of a norm (the
-        few-rows kernel of the bfloat16 decode step does)."""
+    def fold_path(self, ctx, rows: int, dtype, finishing: bool = False):
+        """Which kernel of this product, on `rows` rows of `dtype`, can take over a half of a norm:
+        "few" (the decode step's few-rows kernel), "tiles" (the tensor-core kernels of a long prompt
+        step) or None. `finishing`: the half that adds to the residual stream and prepares the norm's
+        output (needs whole tiles of output columns); else the half that scales its output rows."""
         w = self.weight
-        return (dtype == torch.bfloat16 and w is not None and w.dtype == torch.bfloat16 and rows <= ctx.kernels.decode.FOLD_MAX_M
-                and w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0)
+        if dtype != torch.bfloat16 or w is None or w.dtype != torch.bfloat16:
+            return None
+        if not (w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.stride(1) == 1 and w.data_ptr() % 16 == 0):
+            return None
+        tc = ctx.kernels.tensor_core
+        if rows <= ctx.kernels.decode.FOLD_MAX_M:
+            return "few" if not finishing or w.shape[0] % 16 == 0 else None
+        if rows >= tc.FOLD_MIN_M:
+            return "tiles" if not finishing or (w.shape[0] % 32 == 0 and w.shape[0] > 128 and not tc.ONE_SM_FORCED) else None
+        return None
 
     def forward_folded(self, x, ctx, fold: FoldRequest | None = None, swiglu_out=None):
-        """The product with one or both halves of a norm folded in (only where `folds` said yes).
+        """The product with one or both halves of a norm folded in (only where `fold_path` said so).
         `x`: a Folded (its rows are owed their scale) or a plain tensor. `fold`: finish the sublayer
         (residual += y) and return the Folded input of the product behind the next norm; else
         returns y, or with `swiglu_out` fills it with silu(gate) * up."""
         owed = (x.sumsq, x.width, x.eps) if isinstance(x, Folded) else None
         a = x.x if isinstance(x, Folded) else x
         w = self.weight
+        few = a.shape[0] <= ctx.kernels.decode.FOLD_MAX_M
+        tc = ctx.kernels.tensor_core
         if fold is not None:
             n_out = w.shape[0]
             xb = torch.empty((a.shape[0], n_out), dtype=torch.bfloat16, device=a.device)
-            sumsq = torch.empty((-(-n_out // 16), a.shape[0]), dtype=torch.float32, device=a.device)
-            ctx.kernels.decode.gemm_small_m(a, w, fold.residual, owed=owed, fold=(fold.weight, xb, sumsq))
+            sumsq = torch.empty((-(-n_out // (16 if few else tc.FOLD_SPAN)), a.shape[0]), dtype=torch.float32, device=a.device)
+            if few:
+                ctx.kernels.decode.gemm_small_m(a, w, fold.residual, owed=owed, fold=(fold.weight, xb, sumsq))
+            else:
+                tc.gemm(a, w, fold.residual, ctx.err_flag, owed=owed, fold=(fold.weight, xb, sumsq))
             return Folded(xb, sumsq, n_out, fold.eps)
-        if swiglu_out is not None:
-            ctx.kernels.decode.gemm_small_m(a, w, swiglu_out, swiglu=True, owed=owed)
-            return swiglu_out
-        out = torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=a.device)
-        ctx.kernels.decode.gemm_small_m(a, w, out, owed=owed)
+        out = swiglu_out if swiglu_out is not None else torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=a.device)
+        if few:
+            ctx.kernels.decode.gemm_small_m(a, w, out, swiglu=swiglu_out is not None, owed=owed)
+        else:
+            tc.gemm(a, w, out, ctx.err_flag, swiglu=swiglu_out is not None, owed=owed)
         return out
 
     def forward(self, x: torch.Tensor, ctx, out_dtype=None, partials_ok: bool = False) -> torch.Tensor:

@@ -210,6 +210,48 @@ def test_gemm_small_m_takes_over_the_halves_of_a_norm(kernel_sets, M, N, K, eps)
     assert rel_err(h.cpu().float(), plain.swiglu(full[:, :24], full[:, 24:])) < TOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("M, N, K, eps", [(130, 2048, 2048, 1e-5), (300, 1056, 520, 1e-6), (2048, 2048, 8192, 1e-5), (129, 160, 264, 1e-3),
+                                          (700, 4096, 1024, 1e-5)])
+def test_gemm_tc_takes_over_the_halves_of_a_norm(kernel_sets, M, N, K, eps):
+    """The same two halves in the tensor-core products of a long prompt step: the residual sum,
+    residual * weight and the sums of squares per 128 columns in the epilogue of one (staged through
+    shared memory so that the float stream is read and written in whole rows); the row scale in the
+    plain and the gated epilogue of the other, on the two-SM and the one-SM tiles."""
+    tc = kernel_sets[torch.bfloat16].tensor_core
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a, w = dev(rand(M, K, seed=8), torch.bfloat16), dev(rand(N, K, seed=9, scale=0.05), torch.bfloat16)
+    resid0 = rand(M, N, seed=10, scale=2.0).float()
+    norm_w = (1.0 + 0.1 * rand(N, seed=11)).float()
+    y = plain.linear(f64(a), f64(w))
+    resid = dev(resid0, torch.float32)
+    xb = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    sumsq = torch.full((-(-N // 128), M), float("nan"), dtype=torch.float32, device="cuda")
+    tc.gemm(a, w, resid, err, fold=(dev(norm_w, torch.float32), xb, sumsq))
+    want_resid = resid0.double() + y
+    assert int(err) == 0
+    assert rel_err(resid.cpu(), want_resid) < 3e-5             # tensor-core accumulation over long K, as in the plain product
+    assert rel_err(xb.cpu().float(), want_resid * norm_w.double()) < TOL[torch.bfloat16]
+    assert rel_err(sumsq.sum(0).cpu(), (want_resid ** 2).sum(1)) < 6e-5
+    # the second half: plain and gated epilogues (48 columns: the one-SM tile)
+    w2 = dev(rand(48, N, seed=12, scale=0.05), torch.bfloat16)
+    scale = torch.rsqrt((resid.cpu().double() ** 2).mean(1) + eps)
+    full = plain.linear(f64(xb), f64(w2)) * scale[:, None]
+    out = torch.empty(M, 48, dtype=torch.bfloat16, device="cuda")
+    tc.gemm(xb, w2, out, err, owed=(sumsq, N, eps))
+    assert rel_err(out.cpu().float(), full) < TOL[torch.bfloat16]
+    assert rel_err(out.cpu().float(), plain.linear(plain.rms_norm(want_resid, norm_w.double(), eps), f64(w2))) < 2 * TOL[torch.bfloat16]
+    tiled = w2.view(2, 3, 8, N).permute(1, 0, 2, 3).reshape(48, N).contiguous()
+    h = torch.empty(M, 24, dtype=torch.bfloat16, device="cuda")
+    tc.gemm(xb, tiled, h, err, swiglu=True, owed=(sumsq, N, eps))
+    assert rel_err(h.cpu().float(), plain.swiglu(full[:, :24], full[:, 24:])) < TOL[torch.bfloat16]
+    # a wide product (the two-SM tile): every column tile of a row takes the same scale
+    w3 = dev(rand(520, N, seed=13, scale=0.05), torch.bfloat16)
+    out3 = torch.empty(M, 520, dtype=torch.float32, device="cuda")
+    tc.gemm(xb, w3, out3, err, owed=(sumsq, N, eps))
+    assert rel_err(out3.cpu(), plain.linear(f64(xb), f64(w3)) * scale[:, None]) < 3e-5
+    assert int(err) == 0
+
+
 @pytest.mark.parametrize("M, N, K", [(128, 128, 64), (100, 200, 72), (130, 264, 520), (2048, 2048, 2048), (65, 1003 * 8, 136),
                                      (300, 96, 8192), (257, 384, 136), (2304, 6400, 192), (1100, 4104, 2176)])
 def test_gemm_tensor_core(kernel_sets, M, N, K):
