@@ -8,6 +8,8 @@ spare state slot of their own, so they change nothing a real row sees.
 """
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -57,8 +59,19 @@ class DecodeGraph:
         from ..csrc import bindings
         before = bindings.LAUNCHES[0]
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=engine.decode_graphs.pool):
-            self.logits = engine._forward(ctx, want=True)
+        # No garbage collection while the capture is under way: the graphs of an engine that is no longer
+        # in use (they hang in reference cycles) would be destroyed whenever the collector happens to
+        # run, and destroying a graph is not permitted while any stream captures; it invalidates the capture.
+        # What is garbage now is collected before.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=engine.decode_graphs.pool):
+                self.logits = engine._forward(ctx, want=True)
+        finally:
+            if collecting:
+                gc.enable()
         self.kernels_per_replay = bindings.LAUNCHES[0] - before
 
     def _fill_host(self, ids, pos0, slots, tables):

@@ -360,3 +360,30 @@ def test_long_batches_of_prompts_go_through_in_portions(tmp_path, dtype):
         gen_eng.PROMPT_TOKENS_PER_STEP = 64
         got = llm.generate(d, prompts, 6, "greedy", stop_ids=[], dtype="float32")
         assert got == [plain.generate(pm, p, 6, stop_ids=()) for p in prompts]
+
+
+def test_no_garbage_collection_while_a_step_is_captured(tmp_path):
+    """Graphs of an engine that is no longer in use hang in reference cycles; were the collector to
+    run while another engine captures a step, destroying them would invalidate that capture. So the
+    collector runs before a capture and is off during it (and on again afterwards)."""
+    import gc
+    from scriptling_llm_lib_b200.engine.step import Engine, StepEntry
+    raw, seed = TINY["D"]
+    d = make_model_dir(tmp_path / "m", raw, seed)
+    eng = Engine.from_folder(d, "bfloat16", max_tokens=256)
+    assert eng.use_graphs
+    seen = []
+    forward = eng._forward
+
+    def watched(ctx, want):
+        if torch.cuda.is_current_stream_capturing():
+            seen.append(gc.isenabled())
+        return forward(ctx, want)
+
+    eng._forward = watched
+    assert gc.isenabled()
+    s = eng.open()
+    eng.step([StepEntry(s, random_ids(5, raw["vocab_size"], 3), [])])
+    eng.step([StepEntry(s, [7], [0])])                      # the first decode step of this shape: captured here
+    s.close()
+    assert seen == [False] and gc.isenabled()
