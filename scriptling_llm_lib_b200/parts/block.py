@@ -50,15 +50,23 @@ _NO_FOLD = bool(os.environ.get("SLLM_NO_FOLD"))
 
 
 def fold_request(norm, before, behind, ctx, rows: int, residual):
-    """A FoldRequest for `norm` if it, the part `before` it and the part `behind` it all can; else None."""
+    """A FoldRequest for `norm` if it, the part `before` it and the part `behind` it all can; else None.
+    What the three answer depends on a step only through its kind (how many rows, decode or not), so
+    the answer is kept per kind, with the norm (which lives and dies with its neighbours)."""
     if _NO_FOLD:
         return None
-    terms = norm.fold_terms() if hasattr(norm, "fold_terms") else None
-    can = getattr(before, "can_fold", None)
-    takes = getattr(behind, "takes_folded", None)
-    if terms is None or can is None or takes is None or not can(ctx, rows) or not takes(ctx, rows):
-        return None
-    return FoldRequest(residual, terms[0], terms[1])
+    memo = norm.__dict__.setdefault("_fold_memo", {})
+    key = (id(before), id(behind), min(rows, 256), bool(ctx.is_decode), ctx.dtype)
+    try:
+        terms = memo[key]
+    except KeyError:
+        terms = norm.fold_terms() if hasattr(norm, "fold_terms") else None
+        can = getattr(before, "can_fold", None)
+        takes = getattr(behind, "takes_folded", None)
+        if terms is None or can is None or takes is None or not can(ctx, rows) or not takes(ctx, rows):
+            terms = None
+        memo[key] = terms
+    return None if terms is None else FoldRequest(residual, terms[0], terms[1])
 
 
 class Block:

@@ -16,6 +16,7 @@ class Linear:
     def __init__(self, names: list[str], out_features: list[int], in_features: int):
         self.names, self.out_features, self.in_features = list(names), list(out_features), in_features
         self.weight: torch.Tensor | None = None
+        self._fold_ok = None
 
     def tensor_specs(self) -> list[TensorSpec]:
         return [TensorSpec(n, (o, self.in_features)) for n, o in zip(self.names, self.out_features)]
@@ -25,6 +26,7 @@ class Linear:
         if len({p.dtype for p in parts}) != 1:
             raise ValueError(f"tensors {self.names} are stored in different precisions and cannot be stacked")
         self.weight = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0).contiguous()
+        self._fold_ok = None
 
     def rows(self, first: int, count: int) -> "Linear":
         """A view of `count` output rows from `first` (the query rows of a stacked q|k|v)."""
@@ -38,9 +40,12 @@ class Linear:
         step) or None. `finishing`: the half that adds to the residual stream and prepares the norm's
         output (needs whole tiles of output columns); else the half that scales its output rows."""
         w = self.weight
-        if dtype != torch.bfloat16 or w is None or w.dtype != torch.bfloat16:
+        if dtype != torch.bfloat16 or w is None:
             return None
-        if not (w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.stride(1) == 1 and w.data_ptr() % 16 == 0):
+        if self._fold_ok is None:       # what does not change once the weights are bound
+            self._fold_ok = bool(w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.stride(1) == 1
+                                 and w.data_ptr() % 16 == 0)
+        if not self._fold_ok:
             return None
         tc = ctx.kernels.tensor_core
         if rows <= ctx.kernels.decode.FOLD_MAX_M:

@@ -25,6 +25,7 @@ class RMSNorm(Norm):
     def bind(self, tensors, dtype, device):
         self.weight = tensors[self.weight_name]
         self.weight_f32 = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
+        self._fold_memo = {}
 
     def fold_terms(self):
         return self.weight_f32, self.eps
