@@ -60,6 +60,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // weights), and call pdl_wait() before they touch anything an earlier kernel wrote. Every kernel
 // launched this way calls pdl_launch_dependents() first and pdl_wait() before its first dependent
 // access, so completion stays transitive along the stream. Launched the ordinary way, both are no-ops.
+// The first kernel of a model step (the embedding) is launched the ordinary way: what earlier steps wrote
+// (the cached keys and values) is complete and visible to every kernel of the step, also before its wait.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -332,6 +332,7 @@ struct AttnDecodeArgs {
   // value at position seq_pos0[b] of the cache and uses them -- no separate rotary kernel
   const float2* cs;     // [positions][rot/2] (cos, sin)
   int rot, interleaved, write_kv;
+  int late;             // no key is asked for before the wait for the kernel in front (for comparisons)
 };
 
 // Eight consecutive dims [d0, d0+8) of a head's raw row, rotated for the position whose table row
@@ -447,14 +448,20 @@ __device__ __forceinline__ void ad_ticket_merge(const AttnDecodeArgs& p, int b, 
   }
 }
 
-template <int HD, int NREP, bool RAW>
-__global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDecodeArgs p) {
+template <bool FIRST, typename T>
+__device__ __forceinline__ T& ad_pick(T& a, T& b) {
+  if constexpr (FIRST) return a;
+  else return b;
+}
+
+template <int HD, int NREP, bool RAW, bool EARLY>
+__global__ void __launch_bounds__(AD_WARPS * 32, NREP == 1 ? 7 : 1) attn_decode_split_kernel(AttnDecodeArgs p) {
   constexpr int LPK = HD / 8;        // lanes that share one key (8 dims = 16 bytes each)
   constexpr int KPW = 32 / LPK;      // keys a warp reads per load
   __shared__ float sm_acc[AD_WARPS][NREP][HD];
   __shared__ float sm_ml[AD_WARPS][NREP][2];
   pdl_launch_dependents();
-  pdl_wait();
+  if (!RAW) pdl_wait();        // given finished queries, the kernel in front may have written any of its inputs
   int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int slot = lane / LPK, dl = (lane % LPK) * 8;
@@ -470,6 +477,33 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
   // holds it takes it from the step's raw row after the cached keys
   const bool has_new = RAW && p.write_kv && pos >= k_lo && pos < k_hi;
   const int k_end = has_new ? pos : k_hi;
+
+  auto fetch = [&](uint4 (&kr)[AD_UN], uint4 (&vr)[AD_UN], bool (&ok)[AD_UN], int kb) {
+#pragma unroll
+    for (int u = 0; u < AD_UN; u++) {
+      int key = kb + u * KPW + slot;
+      ok[u] = key < k_end;
+      int kk = ok[u] ? key : k_lo;
+      int page = bt[kk / SLLM_PAGE];
+      size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * HD + dl;
+      kr[u] = ld_dep16_stream(p.kpages + off);
+      vr[u] = ld_dep16_stream(p.vpages + off);
+    }
+  };
+  // The warp's first keys are asked for before the wait for the kernel in front (whose output is this step's
+  // q, k and v): keys before the query's position were cached by earlier steps, and a step's first kernel
+  // is launched the ordinary way, after everything before it. The sequence's length and page numbers are
+  // step inputs, copied in before the step. Not so the key at the query's own position.
+  // (EARLY is chosen where all blocks are resident at once: there nothing else hides that chain of loads;
+  // the registers it costs are spilled over the wait.)
+  const int kb0 = k_lo + warp * KPW * AD_UN;
+  const bool early = EARLY && kb0 < k_end && kb0 + KPW * AD_UN <= pos;
+  uint4 kr0[AD_UN], vr0[AD_UN];          // the loop's own buffers when EARLY (else unused: it declares its own)
+  bool ok0[AD_UN];
+  if constexpr (EARLY) {
+    if (early) fetch(kr0, vr0, ok0, kb0);
+  }
+  if (RAW) pdl_wait();
 
   for (int r0 = 0; r0 < nrep; r0 += NREP) {
     float q[NREP][8], acc[NREP][8], m[NREP], l[NREP];
@@ -490,19 +524,13 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_split_kernel(AttnDe
       m[r] = -INFINITY;
       l[r] = 0.f;
     }
-    for (int kb = k_lo + warp * KPW * AD_UN; kb < k_end; kb += AD_WARPS * KPW * AD_UN) {
-      uint4 kr[AD_UN], vr[AD_UN];
-      bool ok[AD_UN];
-#pragma unroll
-      for (int u = 0; u < AD_UN; u++) {
-        int key = kb + u * KPW + slot;
-        ok[u] = key < k_end;
-        int kk = ok[u] ? key : k_lo;
-        int page = bt[kk / SLLM_PAGE];
-        size_t off = (((size_t)page * p.G + g) * SLLM_PAGE + (kk % SLLM_PAGE)) * HD + dl;
-        kr[u] = ld_dep16_stream(p.kpages + off);
-        vr[u] = ld_dep16_stream(p.vpages + off);
-      }
+    for (int kb = kb0; kb < k_end; kb += AD_WARPS * KPW * AD_UN) {
+      uint4 kr1[AD_UN], vr1[AD_UN];
+      bool ok1[AD_UN];
+      uint4 (&kr)[AD_UN] = ad_pick<EARLY>(kr0, kr1);
+      uint4 (&vr)[AD_UN] = ad_pick<EARLY>(vr0, vr1);
+      bool (&ok)[AD_UN] = ad_pick<EARLY>(ok0, ok1);
+      if (!(EARLY && early && r0 == 0 && kb == kb0)) fetch(kr, vr, ok, kb);
       float s[AD_UN][NREP];
 #pragma unroll
       for (int u = 0; u < AD_UN; u++) {
@@ -925,6 +953,16 @@ static bool attn_decode_uses_mma(int B, int H, int G, int hd) {
 }
 SLLM_EXPORT int sllm_attn_decode_uses_mma(int B, int H, int G, int hd) { return attn_decode_uses_mma(B, H, G, hd) ? 1 : 0; }
 
+static int sllm_sm_count() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 1;
+  }
+  return sms;
+}
+
 template <int HD>
 static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStream_t stream) {
   dim3 grid(a.n_split, a.G, B);
@@ -944,13 +982,15 @@ static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStr
     }
   }
   if (a.cs != nullptr) {
-    if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-    else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-    else e = sllm_launch(attn_decode_split_kernel<HD, 1, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, true, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, true, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else if (!a.late && (long long)a.n_split * a.G * B <= 7LL * sllm_sm_count())       // all resident at once
+      e = sllm_launch(attn_decode_split_kernel<HD, 1, true, true>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else e = sllm_launch(attn_decode_split_kernel<HD, 1, true, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
   } else {
-    if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-    else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
-    else e = sllm_launch(attn_decode_split_kernel<HD, 1, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, false, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, false, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
+    else e = sllm_launch(attn_decode_split_kernel<HD, 1, false, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
   }
   if (e != cudaSuccess || a.tickets != nullptr) return (int)e;
   return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD < 32 ? 32 : HD), 0, stream,
@@ -971,7 +1011,9 @@ static int attn_decode_dispatch(const void* q, int q_ld, void* out, const int* s
   if (cos_sin != nullptr && (rot < 2 || rot > hd || (rot % (interleaved ? 8 : 16)) != 0 || tickets == nullptr)) return SLLM_ERR_ARG;
   AttnDecodeArgs a{(const bf16*)q, q_ld, seq_pos0, block_table, max_pages, (const bf16*)kpages, (const bf16*)vpages,
                    (float*)scratch, H, G, window, n_split, scale, (bf16*)out, tickets, (const float2*)cos_sin, rot, interleaved,
-                   write_kv};
+                   write_kv, 0};
+  static const int late = getenv("SLLM_DECODE_LATE_KEYS") != nullptr;   // for comparisons
+  a.late = late;
   switch (hd) {
     case 16: return attn_decode_launch<16>(a, (bf16*)out, B, stream);
     case 32: return attn_decode_launch<32>(a, (bf16*)out, B, stream);
