@@ -342,28 +342,29 @@ def run(args):
         e2e = None
         if not args.no_e2e:
             rng = np.random.default_rng(1)
-            e2e_lens = prompt_lens if args.prompts is not None else [args.context - args.steps - 2] * args.batch
+            n_gen = args.steps + args.warmup + 2          # the prompt's token, warm-up + 1 untimed decode steps, the timed ones
+            e2e_lens = prompt_lens if args.prompts is not None else [args.context - n_gen] * args.batch
             prompts = [rng.integers(0, V, n).tolist() for n in e2e_lens]
             marks = {}
 
             def on_step(i, toks):
-                # called when the first sampled token of every sequence has reached the host; the loop has
-                # already queued decode step 1 by then, and the synchronize lets it finish before the clock starts
-                if i == 0:
+                # called when token i of every sequence has reached the host; the loop has already queued
+                # decode step i + 1 by then, and the synchronize lets it finish before the clock starts
+                if i == args.warmup:
                     torch.cuda.synchronize()
                     marks["t0"] = time.perf_counter()
                 return False
-            # warm-up with the same lengths: the cache is sized and the step's graph captured before the timed call
-            llm.generate(spec, prompts, args.steps + 2, "greedy", temperature=0.0, stop_ids=[], dtype=dtype)
-            out = llm.generate(spec, prompts, args.steps + 2, "greedy", temperature=0.0, stop_ids=[], dtype=dtype, on_step=on_step)
+            # a first call with the same lengths: the cache is sized and the step's graph captured before the timed call
+            llm.generate(spec, prompts, n_gen, "greedy", temperature=0.0, stop_ids=[], dtype=dtype)
+            out = llm.generate(spec, prompts, n_gen, "greedy", temperature=0.0, stop_ids=[], dtype=dtype, on_step=on_step)
             torch.cuda.synchronize()
             dt = time.perf_counter() - marks["t0"]
-            assert all(len(o) == args.steps + 2 for o in out)
+            assert all(len(o) == n_gen for o in out)
             graph = llm.load(spec, dtype)[0].decode_graphs.last_graph      # the captured step the run ended on
             e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
                    "h2d_bytes_per_step": graph.h2d_bytes, "d2h_bytes_per_step": 4 * args.batch,
-                   "window": f"decode steps 2..{args.steps + 1} of a generation of {args.steps + 2} tokens: {args.steps} steps, "
-                             "wall clock, from after the first decode step to the last token on the host"}
+                   "window": f"decode steps {args.warmup + 2}..{n_gen - 1} of a generation of {n_gen} tokens: {args.steps} steps "
+                             f"after {args.warmup + 1} untimed ones, wall clock, to the last token on the host"}
         c1 = clocks.mark()          # the clock samples cover the device-timed steps and the end-to-end run
 
         points = {}
