@@ -74,8 +74,8 @@ __device__ __forceinline__ float ld_dep_f32(const float* p) {      // of data an
   return v;
 }
 
-template <int NT, int WARPS, int EPI, int UN>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int NT, int WARPS, int EPI, int UN, int MINB = 0>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ y, int M, int N, int K,
                     int ldx, int ldw, int ldy, int out_f32, const SmFold f) {
   __shared__ float red[WARPS][NT][4][32];
@@ -246,11 +246,43 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void
   }
 }
 
+static int sllm_sm_count() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 1;
+  }
+  return sms;
+}
+
 template <int NT, int WARPS, int EPI>
 static int small_m_launch_w(const bf16* x, const bf16* W, void* y, int M, int N, int K, int ldx, int ldw, int ldy,
                             int out_f32, int ksplit, const SmFold& f, cudaStream_t stream) {
   dim3 grid((N + 15) / 16, ksplit);
   constexpr int UN = NT <= 2 ? 2 : 1;
+  if constexpr (NT <= 2 && WARPS == 4) {
+    // Blocks are equal pieces of work, so a last wave that is nearly empty costs a whole one. With one chunk
+    // in flight per warp instead of two the kernel fits more blocks on an SM (seven instead of four at up to 8
+    // rows; five or seven instead of three at up to 16); those forms are slower while everything is resident
+    // at once and are taken where they fill their waves better: the cost of a form is its number of waves
+    // times the blocks a wave holds. Measured at 8 rows: 1,024 blocks 13.4 -> 12.3 us, 1,792 blocks 43.7 ->
+    // 41.3 us, 3,072 blocks 35.5 -> 34.4 us; at 16 rows: 512 blocks of K 8,192 13.1 -> 10.2 us, 1,024 blocks
+    // 18.1 -> 15.4 us.
+    const long long blocks = (long long)grid.x * grid.y, sms = sllm_sm_count();
+    auto cost = [&](int per_sm) { const long long wave = per_sm * sms; return (blocks + wave - 1) / wave * wave; };
+    const long long usual = cost(NT == 1 ? 4 : 3);
+    if (blocks > (NT == 1 ? 4 : 3) * sms) {
+      if (cost(7) < usual && (NT == 1 || cost(7) <= cost(5)))
+        return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, 1, 7>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx, ldw,
+                                ldy, out_f32, f);
+      if constexpr (NT == 2) {
+        if (cost(5) < usual)
+          return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, 1, 5>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx,
+                                  ldw, ldy, out_f32, f);
+      }
+    }
+  }
   return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, UN>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx, ldw, ldy,
                           out_f32, f);
 }
@@ -952,16 +984,6 @@ static bool attn_decode_uses_mma(int B, int H, int G, int hd) {
   return H >= 2 * G || (long long)B * G <= 64;
 }
 SLLM_EXPORT int sllm_attn_decode_uses_mma(int B, int H, int G, int hd) { return attn_decode_uses_mma(B, H, G, hd) ? 1 : 0; }
-
-static int sllm_sm_count() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 1;
-  }
-  return sms;
-}
 
 template <int HD>
 static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStream_t stream) {

@@ -147,8 +147,10 @@ def test_gemm_nt_generic_split_choice():
 
 
 @pytest.mark.parametrize("M, N, K", [(1, 64, 64), (3, 100, 72), (8, 176, 64), (9, 1003, 144), (16, 2048, 2048),
-                                     (33, 96, 200), (64, 640, 4096), (5, 49152 + 16, 256)])
+                                     (33, 96, 200), (64, 640, 4096), (5, 49152 + 16, 256), (12, 16384, 128)])
 def test_gemm_small_m(kernel_sets, M, N, K):
+    """(The last two sizes, and the K splits of (16, 2048, 2048), have more blocks than are resident at once:
+    they take the forms of the kernel with more blocks to an SM.)"""
     dk = kernel_sets[torch.bfloat16].decode
     a, w = dev(rand(M, K, seed=8), torch.bfloat16), dev(rand(N, K, seed=9, scale=0.05), torch.bfloat16)
     assert dk.takes(a, w)
