@@ -15,6 +15,7 @@ decoding at batch 1 and 64. The default run adds `f32`, the same measurements on
 path (its prompt step against a float fused-multiply-add rate measured here), and `shapes`: the
 Llama-3.2-1B sizes on a batch of unequal prompts (lengths uniform in 128..2048, seeded; one packed
 prompt step, then decoding) and the Llama-3.1-8B sizes at batch 1, 8 and 64. One JSON line on stdout.
+`--kernel attn_decode|gemm_small_m` times one decode kernel alone instead (a line per case).
 
 Weights are drawn on the device (`random:<config.json>:seed`), nothing is written but a config.json.
 """
@@ -440,6 +441,86 @@ def run(args):
     return 0
 
 
+def kernel_alone(args):
+    """One decode kernel by itself, as profiles/ quotes it: launched back to back in a CUDA graph over
+    inputs that rotate through more bytes than L2 holds, timed with CUDA events; one JSON line per case.
+    attn_decode: the decode attention of --shape for --batch sequences of --context keys, once per split
+    count. gemm_small_m: the four products of a layer of --shape (and the head) with --batch rows."""
+    import math
+    import torch
+    from scriptling_llm_lib_b200.csrc.bindings import DecodeKernels
+    dk = DecodeKernels()
+    cfg = dict(SHAPE if args.shape == "smollm2-1.7b" else OTHER_SHAPES[args.shape])
+    H, G = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // H
+    D, F, V, B = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], args.batch
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def timed(launch, n_sets, reps=24):
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for i in range(3):
+                launch(i % n_sets)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(reps):
+                    launch(i % n_sets)
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * reps) * 1e3
+
+    if args.kernel == "attn_decode":
+        pages = -(-args.context // 64)
+        layer_bytes = B * pages * G * 64 * hd * 4
+        n_sets = max(2, min(16, int(1.5e9 // layer_bytes)))
+        ks = [torch.randn(B * pages, G, 64, hd, device="cuda").bfloat16() for _ in range(n_sets)]
+        vs = [torch.randn(B * pages, G, 64, hd, device="cuda").bfloat16() for _ in range(n_sets)]
+        table = torch.randperm(B * pages, device="cuda").int().view(B, pages).contiguous()
+        pos0 = torch.full((B,), args.context - 1, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, H * hd, device="cuda").bfloat16()
+        out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
+        tickets = torch.zeros(B * G, dtype=torch.int32, device="cuda")
+        chosen = dk.attention_splits(B, H, G, hd, pages, sms)
+        for n in sorted({1, 2, 3, 4, 5, 6, 8, 12, 16, chosen}):
+            if n > pages:
+                continue
+            scratch = torch.empty(B * H * n * (hd + 2), dtype=torch.float32, device="cuda")
+            us = timed(lambda i: dk.attn_decode(q, out, pos0, table, ks[i], vs[i], scratch, B, H, G, hd, None,
+                                                1.0 / math.sqrt(hd), n, tickets=tickets), n_sets)
+            print(json.dumps({"kernel": "attn_decode", "shape": args.shape, "batch": B, "context": args.context, "splits": n,
+                              "chosen": n == chosen, "blocks": n * G * B, "us": round(us, 1),
+                              "tb_per_s": round(B * args.context * G * hd * 4 / us / 1e6, 2)}))
+        return 0
+    products = [("qkv", (H + 2 * G) * hd, D, False), ("o", D, H * hd, False), ("gate_up", 2 * F, D, True), ("down", D, F, False),
+                ("head", V, D, False)]
+    for name, N, K, gated in products:
+        n_sets = max(2, int(600e6 // (N * K * 2)) + 1)
+        ws = [torch.randn(N, K, device="cuda").bfloat16() for _ in range(n_sets)]
+        x = torch.randn(B, K, device="cuda").bfloat16()
+        if name in ("o", "down") and B <= dk.FOLD_MAX_M:
+            # as the step runs them: the product adds to the residual stream and prepares the next norm
+            resid = torch.zeros(B, N, dtype=torch.float32, device="cuda")
+            fold = (torch.ones(N, dtype=torch.float32, device="cuda"), torch.empty(B, N, dtype=torch.bfloat16, device="cuda"),
+                    torch.empty(-(-N // 16), B, dtype=torch.float32, device="cuda"))
+            us = timed(lambda i: dk.gemm_small_m(x, ws[i], resid, fold=fold), n_sets)
+            name += " (residual epilogue)"
+        else:
+            y = torch.empty(B, N // 2 if gated else N, dtype=torch.bfloat16, device="cuda")
+            us = timed(lambda i: dk.gemm_small_m(x, ws[i], y, swiglu=gated), n_sets)
+        print(json.dumps({"kernel": "gemm_small_m", "shape": args.shape, "product": name, "rows": B, "n": N, "k": K,
+                          "blocks": -(-N // 16), "us": round(us, 1), "tb_per_s": round(N * K * 2 / us / 1e6, 2)}))
+        del ws
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -465,6 +546,8 @@ def main():
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the Llama-3.2-1B and Llama-3.1-8B sizes")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
+    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m"],
+                    help="time one decode kernel alone at --shape, --batch (and --context) instead of the model")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go package (go.mod) with CPU-only code; "
@@ -474,6 +557,8 @@ def main():
         print(json.dumps({"error": "this library runs on one GPU; bench.py measures N=1 only", "n_gpus": args.gpus}))
         return 2
     args.warmup = max(3, args.warmup)
+    if args.kernel is not None:
+        return kernel_alone(args)
     return run(args)
 
 

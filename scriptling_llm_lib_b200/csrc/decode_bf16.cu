@@ -272,7 +272,8 @@ static int small_m_launch_w(const bf16* x, const bf16* W, void* y, int M, int N,
     const long long blocks = (long long)grid.x * grid.y, sms = sllm_sm_count();
     auto cost = [&](int per_sm) { const long long wave = per_sm * sms; return (blocks + wave - 1) / wave * wave; };
     const long long usual = cost(NT == 1 ? 4 : 3);
-    if (blocks > (NT == 1 ? 4 : 3) * sms) {
+    static const bool usual_only = getenv("SLLM_SMALL_M_USUAL") != nullptr;   // for comparisons
+    if (!usual_only && blocks > (NT == 1 ? 4 : 3) * sms) {
       if (cost(7) < usual && (NT == 1 || cost(7) <= cost(5)))
         return (int)sllm_launch(gemm_small_m_kernel<NT, WARPS, EPI, 1, 7>, grid, dim3(WARPS * 32), 0, stream, x, W, y, M, N, K, ldx, ldw,
                                 ldy, out_f32, f);
