@@ -146,6 +146,23 @@ def test_gemm_nt_generic_split_choice():
     assert KernelSet.gemm_nt_split(20, 96, 200, 148) == 1               # too shallow to cut
 
 
+def test_attention_split_choice(kernel_sets):
+    """About as many blocks as are resident at once (seven per SM for the one-head kernel, two or four
+    for the grouped-query one), a tenth more at most, never more splits than pages, none without a page."""
+    dk = kernel_sets[torch.bfloat16].decode
+    one_head = {b: dk.attention_splits(b, 32, 32, 64, 64, 148) for b in (3, 4, 6, 8, 12, 16, 32, 64)}
+    assert one_head == {3: 11, 4: 8, 6: 6, 8: 4, 12: 3, 16: 2, 32: 1, 64: 1}
+    for b, n in one_head.items():
+        assert n * 32 * b <= 1.12 * 7 * 148 or n == 1
+    assert dk.attention_splits(8, 32, 32, 64, 3, 148) == 3                 # never more than pages
+    assert dk.attention_splits(4, 32, 32, 64, 64, 148) * -(-64 // 8) == 64  # 9 were wanted: the ninth would be empty
+    assert dk.attention_splits(8, 32, 8, 128, 64, 148) == 4                # grouped queries, width 128: two blocks per SM
+    assert dk.attention_splits(8, 32, 8, 64, 64, 148) == 8                 # width 64: four (9 wanted, 8 pages each: 8)
+    assert dk.attention_splits(8, 32, 8, 128, 8, 148) == 2                 # at least four pages each
+    assert dk.attention_splits(1, 32, 32, 64, 64, 148) == 16               # a single sequence: the tensor-core kernel
+    assert dk.attention_splits(500, 32, 32, 64, 64, 148) == 1
+
+
 @pytest.mark.parametrize("M, N, K", [(1, 64, 64), (3, 100, 72), (8, 176, 64), (9, 1003, 144), (16, 2048, 2048),
                                      (33, 96, 200), (64, 640, 4096), (5, 49152 + 16, 256), (12, 16384, 128)])
 def test_gemm_small_m(kernel_sets, M, N, K):
