@@ -738,7 +738,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
   __shared__ float sm_acc[AD_WARPS][ROWS][HD + 1];
   __shared__ float sm_ml[AD_WARPS][ROWS][2];
   pdl_launch_dependents();
-  pdl_wait();
+  if (!RAW) pdl_wait();        // given finished queries, the kernel in front may have written any of its inputs
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = lane >> 2, t = lane & 3;
   const int pos = p.seq_pos0[b];
@@ -753,6 +753,36 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
   const float2* csr = RAW ? p.cs + (size_t)pos * (p.rot >> 1) : nullptr;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   const float sc = p.scale * AD_LOG2E;
+
+  auto fetch = [&](uint4 (&kr)[2][NJ], uint4 (&vr)[4][NC], int base) {
+    const size_t row0 = ((size_t)bt[base / SLLM_PAGE] * p.G + g) * SLLM_PAGE + (base % SLLM_PAGE);
+    const bf16* kp = p.kpages + row0 * HD;
+    const bf16* vp = p.vpages + row0 * HD;
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      int key = base + u * 8 + n;
+      bool ok = key >= k_lo && key < k_hi;
+#pragma unroll
+      for (int j = 0; j < NJ; j++) kr[u][j] = ok ? ld_dep16_stream(kp + (size_t)(u * 8 + n) * HD + (j * 4 + t) * 8) : zero;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      int kk = 2 * t + (i & 1) + (i >> 1) * 8;
+      bool ok = base + kk >= k_lo && base + kk < k_hi;
+#pragma unroll
+      for (int c = 0; c < NC; c++) vr[i][c] = ok ? ld_dep16_stream(vp + (size_t)kk * HD + (c * 8 + n) * 8) : zero;
+    }
+  };
+  // In raw mode (the kernel is part of a model step) the warp's first tile of keys is asked for before the
+  // wait for the kernel in front, as in attn_decode_split_kernel: keys before the query's position were
+  // cached by earlier steps. It pays where the blocks are few (one head per key/value head and few
+  // sequences); with grouped queries it changed nothing.
+  constexpr int STEP = AD_WARPS * 16;
+  const int base0 = (k_lo & ~15) + warp * 16;
+  const bool early = RAW && !p.late && base0 < k_hi && base0 + 16 <= pos;
+  uint4 ka[2][NJ], va[4][NC];
+  if (early) fetch(ka, va, base0);
+  if (RAW) pdl_wait();
 
   // raw mode: the block whose range holds the query's own position rotates the new key and appends
   // key and value to the cache; after the barrier below they are cached keys like the others
@@ -802,25 +832,6 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
     for (int i = 0; i < NC * 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    auto fetch = [&](uint4 (&kr)[2][NJ], uint4 (&vr)[4][NC], int base) {
-      const size_t row0 = ((size_t)bt[base / SLLM_PAGE] * p.G + g) * SLLM_PAGE + (base % SLLM_PAGE);
-      const bf16* kp = p.kpages + row0 * HD;
-      const bf16* vp = p.vpages + row0 * HD;
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        int key = base + u * 8 + n;
-        bool ok = key >= k_lo && key < k_hi;
-#pragma unroll
-        for (int j = 0; j < NJ; j++) kr[u][j] = ok ? ld_dep16_stream(kp + (size_t)(u * 8 + n) * HD + (j * 4 + t) * 8) : zero;
-      }
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        int kk = 2 * t + (i & 1) + (i >> 1) * 8;
-        bool ok = base + kk >= k_lo && base + kk < k_hi;
-#pragma unroll
-        for (int c = 0; c < NC; c++) vr[i][c] = ok ? ld_dep16_stream(vp + (size_t)kk * HD + (c * 8 + n) * 8) : zero;
-      }
-    };
     auto attend = [&](uint4 (&kr)[2][NJ], uint4 (&vr)[4][NC], int base) {
       float s[2][4];
 #pragma unroll
@@ -884,13 +895,13 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
     };
     // a warp takes every AD_WARPS-th tile of 16 keys; two register buffers used in turn, so the next
     // tile's keys and values are in flight while the current tile is multiplied
-    constexpr int STEP = AD_WARPS * 16;
-    int base = (k_lo & ~15) + warp * 16;
+    int base = base0;
+    const bool have = early && r0 == 0;        // the first tile is here already
     if constexpr (HD >= 128) {
       // two register buffers used in turn: the next tile is in flight while this one is multiplied.
       // (At width 64 a tile is too small for that to pay for the registers.)
-      uint4 ka[2][NJ], va[4][NC], kb[2][NJ], vb[4][NC];
-      if (base < k_hi) fetch(ka, va, base);
+      uint4 kb[2][NJ], vb[4][NC];
+      if (base < k_hi && !have) fetch(ka, va, base);
       while (base < k_hi) {
         if (base + STEP < k_hi) fetch(kb, vb, base + STEP);
         attend(ka, va, base);
@@ -901,9 +912,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
         base += STEP;
       }
     } else {
-      uint4 ka[2][NJ], va[4][NC];
       for (; base < k_hi; base += STEP) {
-        fetch(ka, va, base);
+        if (!(have && base == base0)) fetch(ka, va, base);
         attend(ka, va, base);
       }
     }
